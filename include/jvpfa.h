@@ -1,0 +1,179 @@
+/*
+ * jvpfa.h -- C ABI of libjvpfa.so: JVP flash attention for NVIDIA B200 (sm_100a).
+ *
+ * The upstream project (amorehead/jvp_flash_attention) has no native boundary: its
+ * kernels are launched through Triton's Python launcher, `kernel[grid](...)`
+ * (jvp_flash_attention/jvp_attention.py:2558, 2592, 2921, 2939).  Each entry point
+ * below replaces one of those launch sites and is what a ctypes/cffi binding of the
+ * Python layer calls instead.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the
+ *     current CUDA device unless stated otherwise;
+ *   - q, k, v, tangents, outputs and gradients are (B, H, L, D) row-major
+ *     contiguous (the layout the upstream TMA path requires,
+ *     jvp_attention.py:2483-2488, 2858-2877);
+ *   - returns JVPFA_OK (0) or a negative jvpfa_status; never throws, never aborts;
+ *   - allocates nothing and never synchronises the device: the caller owns every
+ *     buffer (scratch included) and the launch is asynchronous on `stream`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ */
+#ifndef JVPFA_H_
+#define JVPFA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JVPFA_VERSION 100 /* major*100 + minor */
+
+typedef enum {
+  JVPFA_OK = 0,
+  JVPFA_ERR_NULL = -1,        /* a required pointer is NULL                         */
+  JVPFA_ERR_SHAPE = -2,       /* B/H/L/D out of range or unsupported head dim       */
+  JVPFA_ERR_DTYPE = -3,       /* unknown dtype enum                                 */
+  JVPFA_ERR_MASK = -4,        /* inconsistent mask description                      */
+  JVPFA_ERR_ARCH = -5,        /* current device is not compute capability 10.x      */
+  JVPFA_ERR_CUDA = -6,        /* a CUDA runtime/driver call failed                  */
+  JVPFA_ERR_STRUCT = -7,      /* struct_size does not match this library            */
+  JVPFA_ERR_ALIGN = -8,       /* a tensor base pointer is not 16-byte aligned       */
+  JVPFA_ERR_UNSUPPORTED = -9, /* valid request that this build cannot serve         */
+  JVPFA_ERR_TOO_LARGE = -10   /* problem exceeds a fixed internal capacity          */
+} jvpfa_status;
+
+typedef enum { JVPFA_BF16 = 0, JVPFA_FP16 = 1, JVPFA_FP32 = 2 } jvpfa_dtype;
+
+/* How scores are masked / biased inside the tile loop. */
+typedef enum {
+  JVPFA_MASK_NONE = 0,
+  JVPFA_MASK_CAUSAL = 1, /* key j attends iff j <= query i; upper tiles are skipped       */
+  JVPFA_MASK_KVLEN = 2,  /* key padding: key j attends iff j < kv_len[b]; tiles skipped    */
+  JVPFA_MASK_BOOL = 3,   /* uint8 mask, nonzero = attend, broadcast through strides        */
+  JVPFA_MASK_BIAS = 4    /* additive bias, SDPA semantics: softmax(scale*QK^T + bias)      */
+} jvpfa_mask_kind;
+
+/* Kernel family selection (flags field).  AUTO picks the tcgen05 kernels when the
+ * shape qualifies and the portable tensor-core kernels otherwise. */
+typedef enum {
+  JVPFA_IMPL_AUTO = 0,
+  JVPFA_IMPL_GENERIC = 1, /* force the register-tiled mma.sync kernels                    */
+  JVPFA_IMPL_TCGEN05 = 2  /* force the TMA + tcgen05/TMEM kernels; error if not eligible  */
+} jvpfa_impl;
+
+/* Mask / bias description shared by forward and backward.
+ * Element (b, h, i, j) lives at ptr[b*stride[0] + h*stride[1] + i*stride[2] + j*stride[3]]
+ * (strides in ELEMENTS; 0 = broadcast along that dimension). */
+typedef struct {
+  int32_t kind;         /* jvpfa_mask_kind                                            */
+  int32_t bias_dtype;   /* JVPFA_MASK_BIAS only: jvpfa_dtype of the bias elements     */
+  const void* ptr;      /* BOOL: const uint8_t*; BIAS: bias elements; else NULL       */
+  int64_t stride[4];
+  const int32_t* kv_len; /* JVPFA_MASK_KVLEN only: (B) valid key counts, 0..L         */
+} jvpfa_mask;
+
+/*
+ * jvpfa_fwd -- fused primal (+ tangent) attention forward.
+ * Replaces the `_attn_fwd_tma[grid](...)` / `_attn_fwd[grid](...)` launches in
+ * JVPAttn.forward (jvp_attention.py:2558-2631).
+ *
+ *   S = sm_scale*Q K^T (+bias), P = softmax(S), O = P V
+ *   tS = sm_scale*(tQ K^T + Q tK^T), mu = rowsum(P*tS)
+ *   tO = (P*tS) V - mu*O + P tV
+ *
+ * tq/tk/tv/to/mu are all NULL (primal only) or all non-NULL.
+ * lse receives the base-2 logsumexp of the scaled (and biased) scores, the same
+ * quantity upstream stores in `M` (jvp_attention.py:1017-1026); rows with no
+ * attendable key produce O = tO = 0 (jvp_attention.py:1011-1022) and lse = +inf.
+ * mu receives rowsum(P*tS) (already normalised by the softmax denominator).
+ */
+typedef struct {
+  int32_t struct_size; /* sizeof(jvpfa_fwd_args) */
+  int32_t dtype;       /* jvpfa_dtype of q,k,v,tq,tk,tv,o,to */
+  int32_t B, H, L, D;  /* D in {32, 64, 128}; L >= 1 */
+  int32_t impl;        /* jvpfa_impl */
+  float sm_scale;
+  const void *q, *k, *v;
+  const void *tq, *tk, *tv;
+  void *o, *to;
+  float* lse; /* (B,H,L) */
+  float* mu;  /* (B,H,L) or NULL */
+  jvpfa_mask mask;
+} jvpfa_fwd_args;
+
+int jvpfa_fwd(const jvpfa_fwd_args* args, void* stream);
+
+/*
+ * jvpfa_bwd_preprocess -- per-row reductions needed by jvpfa_bwd.
+ * Replaces `_attn_bwd_preprocess[pre_grid](...)` (jvp_attention.py:2921-2928), which
+ * computes only delta; the two extra rows exist because this library also
+ * differentiates through the tangent output.
+ *
+ *   delta = rowsum(go*o)                 (0 when go == NULL)
+ *   eps   = rowsum(gto*o)                (0 when gto == NULL)
+ *   cterm = rowsum(gto*to) - eps*mu      (0 when gto == NULL)
+ *
+ * go and gto may each be NULL (not both).  to and mu are required iff gto != NULL.
+ */
+typedef struct {
+  int32_t struct_size;
+  int32_t dtype;
+  int32_t B, H, L, D;
+  const void *o, *to;
+  const void *go, *gto;
+  const float* mu;
+  float *delta, *eps, *cterm; /* (B,H,L) each; caller-owned scratch */
+} jvpfa_pre_args;
+
+int jvpfa_bwd_preprocess(const jvpfa_pre_args* args, void* stream);
+
+/*
+ * jvpfa_bwd -- gradients w.r.t. q, k, v of  <go, O> + <gto, tO>.
+ * Replaces `_attn_bwd[grid](...)` / `_attn_bwd_causal[grid](...)`
+ * (jvp_attention.py:2932-2974) together with the eager `k * (sm_scale/ln2)`
+ * pre-scale (jvp_attention.py:2901-2903), which is folded into the kernels.
+ * Upstream differentiates through O only (jvp_attention.py:2831); gto != NULL adds
+ * the path through the tangent output and then tq, tk, tv and mu are required.
+ * Score tiles are recomputed from lse; nothing of size L x L is stored.
+ *
+ * delta/eps/cterm must have been produced by jvpfa_bwd_preprocess for the same
+ * (o, to, go, gto, mu).  dq, dk, dv are fully overwritten.
+ */
+typedef struct {
+  int32_t struct_size;
+  int32_t dtype;
+  int32_t B, H, L, D;
+  int32_t impl;
+  float sm_scale;
+  const void *q, *k, *v;
+  const void *tq, *tk, *tv; /* required iff gto != NULL */
+  const void *go, *gto;     /* either may be NULL, not both */
+  const float* lse;
+  const float* mu; /* required iff gto != NULL */
+  const float *delta, *eps, *cterm;
+  void *dq, *dk, *dv;
+  jvpfa_mask mask;
+} jvpfa_bwd_args;
+
+int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
+
+/* Human-readable text for a jvpfa_status (static storage, never NULL). */
+const char* jvpfa_strerror(int status);
+
+/* JVPFA_VERSION of the loaded library. */
+int jvpfa_version(void);
+
+/* Text of the last CUDA error recorded by this thread inside the library
+ * (empty string if none).  Static thread-local storage. */
+const char* jvpfa_last_cuda_error(void);
+
+/* 1 if jvpfa_fwd / jvpfa_bwd with impl == JVPFA_IMPL_AUTO would take the
+ * tcgen05 kernels for this shape, else 0 (pure host logic; no CUDA call). */
+int jvpfa_fwd_uses_tcgen05(const jvpfa_fwd_args* args);
+int jvpfa_bwd_uses_tcgen05(const jvpfa_bwd_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JVPFA_H_ */

@@ -1,0 +1,250 @@
+"""ctypes binding of ``libjvpfa.so`` (declared in ``include/jvpfa.h``).
+
+The library is the only compute path of this package: there is no PyTorch, Triton or CPU
+fallback.  ``load()`` raises if the shared object is missing, and every launch helper raises
+``RuntimeError`` on a non-zero status, so a broken build cannot pass silently.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libjvpfa.so"
+
+# enums of include/jvpfa.h
+BF16, FP16, FP32 = 0, 1, 2
+MASK_NONE, MASK_CAUSAL, MASK_KVLEN, MASK_BOOL, MASK_BIAS = 0, 1, 2, 3, 4
+IMPL_AUTO, IMPL_GENERIC, IMPL_TCGEN05 = 0, 1, 2
+
+DTYPE_ENUM = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32}
+
+EXPORTS = (
+    "jvpfa_fwd",
+    "jvpfa_bwd_preprocess",
+    "jvpfa_bwd",
+    "jvpfa_strerror",
+    "jvpfa_version",
+    "jvpfa_last_cuda_error",
+    "jvpfa_fwd_uses_tcgen05",
+    "jvpfa_bwd_uses_tcgen05",
+)
+
+
+class Mask(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("bias_dtype", C.c_int32),
+        ("ptr", C.c_void_p),
+        ("stride", C.c_int64 * 4),
+        ("kv_len", C.c_void_p),
+    ]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("dtype", C.c_int32),
+        ("B", C.c_int32),
+        ("H", C.c_int32),
+        ("L", C.c_int32),
+        ("D", C.c_int32),
+        ("impl", C.c_int32),
+        ("sm_scale", C.c_float),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("tq", C.c_void_p),
+        ("tk", C.c_void_p),
+        ("tv", C.c_void_p),
+        ("o", C.c_void_p),
+        ("to", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("mu", C.c_void_p),
+        ("mask", Mask),
+    ]
+
+
+class PreArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("dtype", C.c_int32),
+        ("B", C.c_int32),
+        ("H", C.c_int32),
+        ("L", C.c_int32),
+        ("D", C.c_int32),
+        ("o", C.c_void_p),
+        ("to", C.c_void_p),
+        ("go", C.c_void_p),
+        ("gto", C.c_void_p),
+        ("mu", C.c_void_p),
+        ("delta", C.c_void_p),
+        ("eps", C.c_void_p),
+        ("cterm", C.c_void_p),
+    ]
+
+
+class BwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("dtype", C.c_int32),
+        ("B", C.c_int32),
+        ("H", C.c_int32),
+        ("L", C.c_int32),
+        ("D", C.c_int32),
+        ("impl", C.c_int32),
+        ("sm_scale", C.c_float),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("tq", C.c_void_p),
+        ("tk", C.c_void_p),
+        ("tv", C.c_void_p),
+        ("go", C.c_void_p),
+        ("gto", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("mu", C.c_void_p),
+        ("delta", C.c_void_p),
+        ("eps", C.c_void_p),
+        ("cterm", C.c_void_p),
+        ("dq", C.c_void_p),
+        ("dk", C.c_void_p),
+        ("dv", C.c_void_p),
+        ("mask", Mask),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads libjvpfa.so once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m jvp_flash_attention_b200.build` "
+            "(this package has no fallback path)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    lib.jvpfa_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+    lib.jvpfa_fwd.restype = C.c_int
+    lib.jvpfa_bwd_preprocess.argtypes = [C.POINTER(PreArgs), C.c_void_p]
+    lib.jvpfa_bwd_preprocess.restype = C.c_int
+    lib.jvpfa_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+    lib.jvpfa_bwd.restype = C.c_int
+    lib.jvpfa_strerror.argtypes = [C.c_int]
+    lib.jvpfa_strerror.restype = C.c_char_p
+    lib.jvpfa_version.argtypes = []
+    lib.jvpfa_version.restype = C.c_int
+    lib.jvpfa_last_cuda_error.argtypes = []
+    lib.jvpfa_last_cuda_error.restype = C.c_char_p
+    lib.jvpfa_fwd_uses_tcgen05.argtypes = [C.POINTER(FwdArgs)]
+    lib.jvpfa_fwd_uses_tcgen05.restype = C.c_int
+    lib.jvpfa_bwd_uses_tcgen05.argtypes = [C.POINTER(BwdArgs)]
+    lib.jvpfa_bwd_uses_tcgen05.restype = C.c_int
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    """Raises RuntimeError with the library's message when ``status`` is not JVPFA_OK."""
+    if status != 0:
+        lib = load()
+        msg = lib.jvpfa_strerror(status).decode()
+        cuda = lib.jvpfa_last_cuda_error().decode()
+        raise RuntimeError(f"{what} failed: [{status}] {msg}" + (f" | {cuda}" if cuda else ""))
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+class MaskSpec:
+    """Host description of the mask handed to the kernels.
+
+    ``kind`` is one of the MASK_* enums; ``tensor`` keeps the device buffer alive (uint8 mask,
+    bias, or int32 kv_len) and ``strides`` are the broadcast element strides of a (B,H,L,L) view.
+    """
+
+    __slots__ = ("kind", "tensor", "strides", "bias_dtype")
+
+    def __init__(self, kind=MASK_NONE, tensor=None, strides=(0, 0, 0, 0), bias_dtype=FP32):
+        self.kind = kind
+        self.tensor = tensor
+        self.strides = tuple(int(s) for s in strides)
+        self.bias_dtype = bias_dtype
+
+    def to_c(self) -> Mask:
+        m = Mask()
+        m.kind = self.kind
+        m.bias_dtype = self.bias_dtype
+        m.ptr = None
+        m.kv_len = None
+        for i in range(4):
+            m.stride[i] = self.strides[i]
+        if self.kind == MASK_KVLEN:
+            m.kv_len = self.tensor.data_ptr()
+        elif self.kind in (MASK_BOOL, MASK_BIAS):
+            m.ptr = self.tensor.data_ptr()
+        return m
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, impl: int = IMPL_AUTO) -> None:
+    """Launches jvpfa_fwd on the current stream of ``q``'s device (all tensors contiguous BHLD)."""
+    lib = load()
+    B, H, L, D = q.shape
+    a = FwdArgs()
+    a.struct_size = C.sizeof(FwdArgs)
+    a.dtype = DTYPE_ENUM[q.dtype]
+    a.B, a.H, a.L, a.D = B, H, L, D
+    a.impl = impl
+    a.sm_scale = sm_scale
+    a.q, a.k, a.v = ptr(q), ptr(k), ptr(v)
+    a.tq, a.tk, a.tv = ptr(tq), ptr(tk), ptr(tv)
+    a.o, a.to, a.lse, a.mu = ptr(o), ptr(to), ptr(lse), ptr(mu)
+    a.mask = mask.to_c()
+    with torch.cuda.device(q.device):
+        check(lib.jvpfa_fwd(C.byref(a), _stream(q)), "jvpfa_fwd")
+
+
+def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
+    """Launches jvpfa_bwd_preprocess (row reductions delta / eps / cterm)."""
+    lib = load()
+    B, H, L, D = o.shape
+    a = PreArgs()
+    a.struct_size = C.sizeof(PreArgs)
+    a.dtype = DTYPE_ENUM[o.dtype]
+    a.B, a.H, a.L, a.D = B, H, L, D
+    a.o, a.to, a.go, a.gto = ptr(o), ptr(to), ptr(go), ptr(gto)
+    a.mu, a.delta, a.eps, a.cterm = ptr(mu), ptr(delta), ptr(eps), ptr(cterm)
+    with torch.cuda.device(o.device):
+        check(lib.jvpfa_bwd_preprocess(C.byref(a), _stream(o)), "jvpfa_bwd_preprocess")
+
+
+def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, mask: MaskSpec,
+        sm_scale: float, impl: int = IMPL_AUTO) -> None:
+    """Launches jvpfa_bwd (gradients of <go,O> + <gto,tO> w.r.t. q, k, v)."""
+    lib = load()
+    B, H, L, D = q.shape
+    a = BwdArgs()
+    a.struct_size = C.sizeof(BwdArgs)
+    a.dtype = DTYPE_ENUM[q.dtype]
+    a.B, a.H, a.L, a.D = B, H, L, D
+    a.impl = impl
+    a.sm_scale = sm_scale
+    a.q, a.k, a.v = ptr(q), ptr(k), ptr(v)
+    a.tq, a.tk, a.tv = ptr(tq), ptr(tk), ptr(tv)
+    a.go, a.gto = ptr(go), ptr(gto)
+    a.lse, a.mu = ptr(lse), ptr(mu)
+    a.delta, a.eps, a.cterm = ptr(delta), ptr(eps), ptr(cterm)
+    a.dq, a.dk, a.dv = ptr(dq), ptr(dk), ptr(dv)
+    a.mask = mask.to_c()
+    with torch.cuda.device(q.device):
+        check(lib.jvpfa_bwd(C.byref(a), _stream(q)), "jvpfa_bwd")

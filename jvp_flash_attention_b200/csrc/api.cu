@@ -1,0 +1,193 @@
+// C ABI of libjvpfa.so: argument validation and dispatch.  No allocation, no device
+// synchronisation, no exceptions across the boundary.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace jvpfa {
+
+static thread_local char g_last_cuda_error[256] = {0};
+
+void set_last_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
+           cudaGetErrorString(e));
+}
+
+static int check_arch() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached_ok = 0;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "cudaGetDevice");
+    return JVPFA_ERR_CUDA;
+  }
+  if (dev != cached_dev) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e, "cudaDeviceGetAttribute");
+      return JVPFA_ERR_CUDA;
+    }
+    cached_dev = dev;
+    cached_ok = (major == 10);
+  }
+  return cached_ok ? JVPFA_OK : JVPFA_ERR_ARCH;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_shape(int dtype, int B, int H, int L, int D) {
+  if (dtype != JVPFA_BF16 && dtype != JVPFA_FP16 && dtype != JVPFA_FP32) return JVPFA_ERR_DTYPE;
+  if (B < 1 || H < 1 || L < 1) return JVPFA_ERR_SHAPE;
+  if (D != 32 && D != 64 && D != 128) return JVPFA_ERR_SHAPE;
+  if ((long long)B * H > 65535LL) return JVPFA_ERR_TOO_LARGE;  // grid.y limit
+  if ((long long)B * H > 2147483647LL / L) return JVPFA_ERR_TOO_LARGE;  // row index fits int32
+  return JVPFA_OK;
+}
+
+static int check_mask(const jvpfa_mask& m) {
+  switch (m.kind) {
+    case JVPFA_MASK_NONE:
+    case JVPFA_MASK_CAUSAL:
+      return JVPFA_OK;
+    case JVPFA_MASK_KVLEN:
+      return m.kv_len ? JVPFA_OK : JVPFA_ERR_MASK;
+    case JVPFA_MASK_BOOL:
+      return m.ptr ? JVPFA_OK : JVPFA_ERR_MASK;
+    case JVPFA_MASK_BIAS:
+      if (!m.ptr) return JVPFA_ERR_MASK;
+      if (m.bias_dtype != JVPFA_BF16 && m.bias_dtype != JVPFA_FP16 && m.bias_dtype != JVPFA_FP32)
+        return JVPFA_ERR_MASK;
+      return JVPFA_OK;
+    default:
+      return JVPFA_ERR_MASK;
+  }
+}
+
+static int validate_fwd(const jvpfa_fwd_args* a) {
+  if (!a) return JVPFA_ERR_NULL;
+  if (a->struct_size != (int32_t)sizeof(jvpfa_fwd_args)) return JVPFA_ERR_STRUCT;
+  int rc = check_shape(a->dtype, a->B, a->H, a->L, a->D);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->o || !a->lse) return JVPFA_ERR_NULL;
+  const int nt = (a->tq != nullptr) + (a->tk != nullptr) + (a->tv != nullptr) + (a->to != nullptr) +
+                 (a->mu != nullptr);
+  if (nt != 0 && nt != 5) return JVPFA_ERR_NULL;
+  const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->o, a->to};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
+  if (a->impl < JVPFA_IMPL_AUTO || a->impl > JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
+  return check_mask(a->mask);
+}
+
+static int validate_bwd(const jvpfa_bwd_args* a) {
+  if (!a) return JVPFA_ERR_NULL;
+  if (a->struct_size != (int32_t)sizeof(jvpfa_bwd_args)) return JVPFA_ERR_STRUCT;
+  int rc = check_shape(a->dtype, a->B, a->H, a->L, a->D);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->lse || !a->delta || !a->dq || !a->dk || !a->dv) return JVPFA_ERR_NULL;
+  if (!a->go && !a->gto) return JVPFA_ERR_NULL;
+  if (a->gto && (!a->tq || !a->tk || !a->tv || !a->mu || !a->eps || !a->cterm)) return JVPFA_ERR_NULL;
+  const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->go, a->gto, a->dq, a->dk, a->dv};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
+  if (a->impl < JVPFA_IMPL_AUTO || a->impl > JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
+  return check_mask(a->mask);
+}
+
+static int validate_pre(const jvpfa_pre_args* a) {
+  if (!a) return JVPFA_ERR_NULL;
+  if (a->struct_size != (int32_t)sizeof(jvpfa_pre_args)) return JVPFA_ERR_STRUCT;
+  int rc = check_shape(a->dtype, a->B, a->H, a->L, a->D);
+  if (rc) return rc;
+  if (!a->o || !a->delta || !a->eps || !a->cterm) return JVPFA_ERR_NULL;
+  if (!a->go && !a->gto) return JVPFA_ERR_NULL;
+  if (a->gto && (!a->to || !a->mu)) return JVPFA_ERR_NULL;
+  const void* ptrs[] = {a->o, a->to, a->go, a->gto};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
+  return JVPFA_OK;
+}
+
+}  // namespace jvpfa
+
+using namespace jvpfa;
+
+extern "C" {
+
+int jvpfa_fwd_uses_tcgen05(const jvpfa_fwd_args* a) {
+  if (validate_fwd(a) != JVPFA_OK) return 0;
+  if (a->impl == JVPFA_IMPL_GENERIC) return 0;
+  return fwd_tc5_eligible(*a) ? 1 : 0;
+}
+
+int jvpfa_bwd_uses_tcgen05(const jvpfa_bwd_args* a) {
+  (void)a;
+  return 0;
+}
+
+int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
+  int rc = validate_fwd(a);
+  if (rc) return rc;
+  rc = check_arch();
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc5 = fwd_tc5_eligible(*a);
+  if (a->impl == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
+  if (tc5 && a->impl != JVPFA_IMPL_GENERIC) return launch_fwd_tc5(*a, s);
+  return launch_fwd_generic(*a, s);
+}
+
+int jvpfa_bwd_preprocess(const jvpfa_pre_args* a, void* stream) {
+  int rc = validate_pre(a);
+  if (rc) return rc;
+  rc = check_arch();
+  if (rc) return rc;
+  return launch_pre(*a, static_cast<cudaStream_t>(stream));
+}
+
+int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
+  int rc = validate_bwd(a);
+  if (rc) return rc;
+  rc = check_arch();
+  if (rc) return rc;
+  if (a->impl == JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
+  return launch_bwd_generic(*a, static_cast<cudaStream_t>(stream));
+}
+
+const char* jvpfa_strerror(int status) {
+  switch (status) {
+    case JVPFA_OK:
+      return "ok";
+    case JVPFA_ERR_NULL:
+      return "a required pointer is NULL (or tangent pointers are only partly given)";
+    case JVPFA_ERR_SHAPE:
+      return "unsupported shape: need B,H,L >= 1 and D in {32, 64, 128}";
+    case JVPFA_ERR_DTYPE:
+      return "unknown dtype";
+    case JVPFA_ERR_MASK:
+      return "inconsistent mask description";
+    case JVPFA_ERR_ARCH:
+      return "current CUDA device is not compute capability 10.x (B200)";
+    case JVPFA_ERR_CUDA:
+      return "CUDA call failed (see jvpfa_last_cuda_error)";
+    case JVPFA_ERR_STRUCT:
+      return "struct_size mismatch between caller and library";
+    case JVPFA_ERR_ALIGN:
+      return "tensor base pointer is not 16-byte aligned";
+    case JVPFA_ERR_UNSUPPORTED:
+      return "request not supported by the selected kernel family";
+    case JVPFA_ERR_TOO_LARGE:
+      return "problem exceeds a fixed internal capacity";
+    default:
+      return "unknown status";
+  }
+}
+
+int jvpfa_version(void) { return JVPFA_VERSION; }
+
+const char* jvpfa_last_cuda_error(void) { return g_last_cuda_error; }
+
+}  // extern "C"

@@ -1,0 +1,461 @@
+"""Drop-in Python API of ``jvp_flash_attention.jvp_attention`` on hand-written sm_100a kernels.
+
+Public names and signatures mirror upstream (jvp_flash_attention/jvp_attention.py:48-51,
+2236-2981): ``MASK_CONST``, ``MIN_SEQUENCE_LENGTH``, ``JVPAttn`` (a ``torch.autograd.Function``
+with ``forward / setup_context / jvp / backward`` plus the ``fwd`` and ``fwd_dual``
+conveniences) and ``attention = JVPAttn.fwd``.  All arithmetic happens in ``libjvpfa.so``
+(see ``include/jvpfa.h``); this module only validates, classifies the mask, allocates outputs
+and wires autograd.
+
+Behaviour that goes beyond upstream, on purpose:
+
+* the tangent output is differentiable: ``jvp`` returns it through ``_TangentBridge`` whose
+  backward is the gradient of ``<gtO, tO>`` (upstream returns a constant, jvp_attention.py:2828);
+* ``backward`` is itself differentiable once (Hessian-vector products) through ``_AttnBwd``;
+* masks may be any shape broadcastable to (Z, H, N, N); a boolean (Z|1, 1, 1, N) prefix mask is
+  recognised as key padding and its fully padded key tiles are skipped;
+* a float mask is an additive bias with SDPA semantics, ``softmax(scale*QK^T + bias)``
+  (upstream scales the bias as well and ignores it in backward, jvp_attention.py:247-251,
+  1519-1522), and a float mask without ``MASK_CONST`` entries is accepted (upstream raises
+  ``UserWarning``, jvp_attention.py:2459-2462).
+"""
+from __future__ import annotations
+
+from typing import Any, Literal, NamedTuple
+
+import torch
+import torch.autograd.forward_ad as fwAD
+from torch import Tensor
+from torch.autograd import Function
+from torch.autograd.function import FunctionCtx, once_differentiable
+
+from . import _lib
+
+MASK_CONST = -100.0  # same constant as upstream (jvp_attention.py:48-50)
+MIN_SEQUENCE_LENGTH = 32  # jvp_attention.py:51
+
+_SUPPORTED_HEAD_DIMS = (32, 64, 128)
+_UPSTREAM_HEAD_DIMS = {16, 32, 64, 128, 256}
+
+# Kernel family used by the launches of this module (see jvpfa_impl in include/jvpfa.h).
+# Tests flip it to cross-check the two families against each other.
+KERNEL_IMPL = _lib.IMPL_AUTO
+
+
+def _unwrap(x):
+    """Strips functorch wrappers so that ``data_ptr()`` is available (cf. jvp_attention.py:2846-2855)."""
+    fc = torch._C._functorch
+    while isinstance(x, Tensor) and fc.is_functorch_wrapped_tensor(x):
+        x = fc.get_unwrapped(x)
+    return x
+
+
+def _require_cuda(*ts: Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "jvp_flash_attention_b200 runs only on CUDA tensors of a compute-capability-10 GPU; "
+                "there is no CPU or PyTorch fallback"
+            )
+
+
+def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int, qdtype: torch.dtype,
+                  verify: bool) -> tuple[_lib.MaskSpec, int, Tensor | None]:
+    """Turns the user's mask into the kernel's description.
+
+    Returns ``(spec, MASK_TYPE, mask_tensor)`` where MASK_TYPE follows upstream's numbering
+    (0 none, 1 boolean, 2 additive; jvp_attention.py:2430-2446).  Pure host logic apart from
+    the optional verification reductions, which mirror jvp_attention.py:2438-2457.
+    """
+    if causal:
+        return _lib.MaskSpec(_lib.MASK_CAUSAL), 0, None
+    if attn_mask is None:
+        return _lib.MaskSpec(_lib.MASK_NONE), 0, None
+    assert attn_mask.dim() == 4, "The provided attention mask must have 4 dimensions (Z, H, N_CTX, N_CTX)."
+    mz, mh, mi, mj = attn_mask.shape
+    assert mz in (1, Z) and mh in (1, H) and mi in (1, N) and mj == N, (
+        "The provided attention mask must be broadcastable to (Z, H, N_CTX, N_CTX)."
+    )
+    assert attn_mask.dtype == torch.bool or attn_mask.dtype.is_floating_point, (
+        "The attention mask must be of the dtype bool or a floating-point dtype."
+    )
+    m = _unwrap(attn_mask)
+
+    def bstrides(t: Tensor) -> tuple[int, int, int, int]:
+        return tuple(0 if t.shape[d] == 1 else t.stride(d) for d in range(4))
+
+    if m.dtype == torch.bool:
+        if verify:
+            assert m.any(dim=(-1, -2)).all(), "The attention mask cannot be all False for any head."
+        if mh == 1 and mi == 1:
+            # Candidate key-padding mask: valid keys form a prefix of each row.
+            rows = m.reshape(mz, N)
+            lens = rows.sum(dim=-1, dtype=torch.int32)
+            prefix = torch.arange(N, device=m.device).unsqueeze(0) < lens.unsqueeze(1)
+            if bool((prefix == rows).all()):
+                kv_len = lens.expand(Z).contiguous() if mz == 1 else lens.contiguous()
+                return _lib.MaskSpec(_lib.MASK_KVLEN, kv_len), 1, attn_mask
+        m8 = m.view(torch.uint8) if m.is_contiguous() or m.stride(-1) == 1 else m.contiguous().view(torch.uint8)
+        return _lib.MaskSpec(_lib.MASK_BOOL, m8, bstrides(m8)), 1, attn_mask
+
+    if m.dtype not in _lib.DTYPE_ENUM:
+        m = m.to(torch.float32)
+    if verify:
+        assert not torch.isinf(m).any(), "The attention mask cannot contain -inf or inf."
+        assert not torch.isnan(m).any(), "The attention mask cannot contain NaNs."
+        assert (m != MASK_CONST).any(dim=(-1, -2)).all(), (
+            f"The attention mask cannot be all {MASK_CONST} (the masking constant) for any head."
+        )
+    return _lib.MaskSpec(_lib.MASK_BIAS, m, bstrides(m), _lib.DTYPE_ENUM[m.dtype]), 2, attn_mask
+
+
+def _launch_fwd(q, k, v, tq, tk, tv, spec: _lib.MaskSpec, sm_scale: float):
+    """Allocates outputs and runs the fused forward.  Returns (o, to | None, lse, mu | None)."""
+    q, k, v, tq, tk, tv = (_unwrap(x) for x in (q, k, v, tq, tk, tv))
+    Z, H, N, _ = q.shape
+    o = torch.empty_like(q)
+    lse = torch.empty((Z, H, N), device=q.device, dtype=torch.float32)
+    dual = tq is not None
+    to = torch.empty_like(q) if dual else None
+    mu = torch.empty_like(lse) if dual else None
+    _lib.fwd(q, k, v, tq, tk, tv, o, to, lse, mu, spec, sm_scale, KERNEL_IMPL)
+    return o, to, lse, mu
+
+
+def _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec: _lib.MaskSpec, sm_scale: float):
+    """Runs preprocess + backward for cotangents ``go`` (of O) and/or ``gto`` (of tO)."""
+    q, k, v, tq, tk, tv, o, to, lse, mu, go, gto = (
+        _unwrap(x) for x in (q, k, v, tq, tk, tv, o, to, lse, mu, go, gto)
+    )
+    if go is not None and not go.is_contiguous():
+        go = go.contiguous()
+    if gto is not None and not gto.is_contiguous():
+        gto = gto.contiguous()
+    if gto is None:
+        tq = tk = tv = to = mu = None
+    Z, H, N, _ = q.shape
+    stats = torch.empty((3, Z, H, N), device=q.device, dtype=torch.float32)
+    delta, eps, cterm = stats[0], stats[1], stats[2]
+    _lib.bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    _lib.bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL)
+    return dq, dk, dv
+
+
+def _check_bwd_layout(q, k, v, o):
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and o.is_contiguous()):
+        raise ValueError(
+            "JVPAttn expected q, k, v, o to be contiguous; got "
+            f"q.is_contiguous()={q.is_contiguous()}, k.is_contiguous()={k.is_contiguous()}, "
+            f"v.is_contiguous()={v.is_contiguous()}, o.is_contiguous()={o.is_contiguous()}"
+        )
+
+
+class _AttnBwd(Function):
+    """(dq, dk, dv) = d<do, O>/d(q, k, v), as a node that can be differentiated once more.
+
+    Its own backward uses the identity (u = incoming grads of dq, dk, dv)
+        d<(dq,dk,dv), u>/d(q,k,v) = d<tO(q,k,v; u), do>/d(q,k,v),   d<...>/d(do) = tO(q,k,v; u)
+    so a Hessian-vector product costs one fused primal+tangent forward with tangents u and one
+    backward through the tangent output; no further kernels exist for it.
+    """
+
+    @staticmethod
+    def forward(q, k, v, o, lse, do, spec, sm_scale):
+        return _launch_bwd(q, k, v, None, None, None, o, None, lse, None, do, None, spec, sm_scale)
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        q, k, v, o, lse, do, spec, sm_scale = inputs
+        ctx.save_for_backward(q, k, v, o, lse, do)
+        ctx.spec, ctx.sm_scale = spec, sm_scale
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, uq, uk, uv):
+        q, k, v, o, lse, do = ctx.saved_tensors
+        us = [torch.zeros_like(q) if u is None else u.contiguous() for u in (uq, uk, uv)]
+        o2, to_u, lse2, mu_u = _launch_fwd(q, k, v, us[0], us[1], us[2], ctx.spec, ctx.sm_scale)
+        need_qkv = any(ctx.needs_input_grad[:3])
+        hq = hk = hv = None
+        if need_qkv:
+            hq, hk, hv = _launch_bwd(q, k, v, us[0], us[1], us[2], o2, to_u, lse2, mu_u, None, do, ctx.spec,
+                                     ctx.sm_scale)
+        gdo = to_u if ctx.needs_input_grad[5] else None
+        return hq, hk, hv, None, None, gdo, None, None
+
+
+class _TangentBridge(Function):
+    """Hands the tangent output computed by the fused forward to autograd with a real gradient.
+
+    forward returns the precomputed tO; backward is the gradient of <gtO, tO> with respect to the
+    primals (the tangent-path backward kernel) and, when asked for, with respect to the tangents
+    (ordinary attention backward with do = gtO).
+    """
+
+    @staticmethod
+    def forward(q, k, v, tq, tk, tv, to, o, lse, mu, spec, sm_scale):
+        return to.detach()
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        q, k, v, tq, tk, tv, to, o, lse, mu, spec, sm_scale = inputs
+        ctx.save_for_backward(q, k, v, tq, tk, tv, to, o, lse, mu)
+        ctx.spec, ctx.sm_scale = spec, sm_scale
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, gto):
+        q, k, v, tq, tk, tv, to, o, lse, mu = ctx.saved_tensors
+        _check_bwd_layout(q, k, v, o)
+        gq = gk = gv = gtq = gtk = gtv = None
+        if any(ctx.needs_input_grad[:3]):
+            gq, gk, gv = _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, None, gto, ctx.spec, ctx.sm_scale)
+        if any(ctx.needs_input_grad[3:6]):
+            gtq, gtk, gtv = _launch_bwd(q, k, v, None, None, None, o, None, lse, None, gto, None, ctx.spec,
+                                        ctx.sm_scale)
+        return gq, gk, gv, gtq, gtk, gtv, None, None, None, None, None, None
+
+
+class JVPAttn(Function):
+    """JVP (Jacobian-Vector Product) for Attention Mechanism (same interface as upstream's JVPAttn)."""
+
+    class Grid(NamedTuple):
+        M_BLOCKS: int
+        Z_H: int
+        ONE: Literal[1]
+
+    class FnCtx(FunctionCtx):
+        sm_scale: float
+        HEAD_DIM_K: int
+        causal: bool
+        grid: "JVPAttn.Grid"
+        mask_tensor: Tensor
+        MASK_TYPE: int
+        dropout_p: float
+        philox_seed: int
+        ENABLE_DROPOUT: bool
+
+    class FwdOutCtxContrib(NamedTuple):
+        """Second element of the forward output; the first ten fields are upstream's (jvp_attention.py:2259-2271)."""
+
+        o_t: Tensor | None
+        M: Tensor
+        grid: "JVPAttn.Grid"
+        HEAD_DIM_K: int
+        sm_scale: float
+        mask_tensor: Tensor | None
+        MASK_TYPE: int
+        dropout_p: float
+        philox_seed: int
+        ENABLE_DROPOUT: bool
+        mu: Tensor | None = None  # rowsum(P * tS), needed to differentiate through o_t
+        mask_spec: Any = None     # kernel-side mask description
+
+    class FwdOut(NamedTuple):
+        o: Tensor
+        ctx: "JVPAttn.FwdOutCtxContrib"
+
+    class JVPOut(NamedTuple):
+        o: Tensor
+        ctx: None
+
+    class BwdOut(NamedTuple):
+        q: Tensor
+        k: Tensor
+        v: Tensor
+        q_t: None
+        k_t: None
+        v_t: None
+        attn_mask: None
+        dropout_p: None
+        causal: None
+        sm_scale: None
+        warp_specialize: None
+        USE_TMA: None
+        verify_attn_mask: None
+
+    class Strides(NamedTuple):
+        z: int
+        h: int
+        n_ctx: int
+        head_dim: int
+
+    @staticmethod
+    def forward(
+        q: Tensor,
+        k: Tensor,
+        v: Tensor,
+        q_t: Tensor | None,
+        k_t: Tensor | None,
+        v_t: Tensor | None,
+        attn_mask: Tensor | None = None,
+        dropout_p: float = 0.0,
+        causal: bool = False,
+        sm_scale: float | None = None,
+        warp_specialize: bool = True,
+        USE_TMA: bool = True,
+        verify_attn_mask: bool = True,
+    ) -> "JVPAttn.FwdOut":
+        """Fused primal (+ tangent) forward; argument meaning as upstream (jvp_attention.py:2311-2355).
+
+        ``warp_specialize`` and ``USE_TMA`` are accepted for signature compatibility and ignored:
+        there is one sm_100a code path.
+        """
+        if dropout_p != 0.0:
+            raise NotImplementedError("Dropout is not currently supported in JVP attention.")
+
+        Z, H, N_CTX, HEAD_DIM_Q = q.shape
+        HEAD_DIM_K = k.shape[-1]
+        HEAD_DIM_V = v.shape[-1]
+        assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V, (
+            "JVP attention requires HEAD_DIM_Q == HEAD_DIM_K == HEAD_DIM_V"
+            f" but got HEAD_DIM_Q={HEAD_DIM_Q}, HEAD_DIM_K={HEAD_DIM_K}, HEAD_DIM_V={HEAD_DIM_V}"
+        )
+        assert HEAD_DIM_K in _UPSTREAM_HEAD_DIMS, (
+            "JVP attention only supports HEAD_DIM_K in {16, 32, 64, 128, 256},"
+            f" but got HEAD_DIM_K={HEAD_DIM_K}"
+        )
+        if HEAD_DIM_K not in _SUPPORTED_HEAD_DIMS:
+            raise NotImplementedError(
+                f"HEAD_DIM_K={HEAD_DIM_K} has no sm_100a kernel in this build (supported: {_SUPPORTED_HEAD_DIMS})"
+            )
+        assert N_CTX % 2 == 0 and N_CTX >= MIN_SEQUENCE_LENGTH, (
+            "JVP attention requires N_CTX to be a multiple of 2 and >= 32,"
+            f" but got N_CTX={N_CTX}"
+        )
+        assert k.shape == q.shape and v.shape == q.shape, "q, k, v must share one (Z, H, N_CTX, HEAD_DIM) shape"
+        if causal and attn_mask is not None:
+            raise ValueError("Causal attention does not support an attention mask.")
+        if q.dtype not in _lib.DTYPE_ENUM:
+            raise TypeError(f"unsupported dtype {q.dtype}; expected bfloat16, float16 or float32")
+        _require_cuda(q, k, v, q_t, k_t, v_t, attn_mask)
+
+        if sm_scale is None:
+            sm_scale = HEAD_DIM_K**-0.5
+
+        tangents = [q_t, k_t, v_t]
+        if any(t is not None for t in tangents):
+            tangents = [torch.zeros_like(q) if t is None else t for t in tangents]
+        qc, kc, vc = (x if x.is_contiguous() else x.contiguous() for x in (q, k, v))
+        tq, tk, tv = (None if t is None else (t if t.is_contiguous() else t.contiguous()).to(q.dtype)
+                      for t in tangents)
+
+        spec, MASK_TYPE, mask_tensor = classify_mask(attn_mask, causal, Z, H, N_CTX, q.dtype, verify_attn_mask)
+        o, o_t, M, mu = _launch_fwd(qc, kc, vc, tq, tk, tv, spec, sm_scale)
+        grid = JVPAttn.Grid((N_CTX + 63) // 64, Z * H, 1)
+        return JVPAttn.FwdOut(
+            o,
+            JVPAttn.FwdOutCtxContrib(o_t, M, grid, HEAD_DIM_K, sm_scale, mask_tensor, MASK_TYPE, dropout_p, 0,
+                                     False, mu, spec),
+        )
+
+    @staticmethod
+    def setup_context(ctx: "JVPAttn.FnCtx", inputs, outputs: "JVPAttn.FwdOut") -> None:
+        (q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, warp_specialize, USE_TMA,
+         *rest) = inputs
+        o, c = outputs
+        ctx.grid = c.grid
+        ctx.save_for_forward(c.o_t, q, k, v, q_t, k_t, v_t, o, c.M, c.mu)
+        ctx.save_for_backward(q, k, v, o, c.M)
+        ctx.sm_scale = c.sm_scale
+        ctx.HEAD_DIM_K = c.HEAD_DIM_K
+        ctx.causal = causal
+        ctx.mask_tensor = c.mask_tensor
+        ctx.MASK_TYPE = c.MASK_TYPE
+        ctx.mask_spec = c.mask_spec
+        ctx.dropout_p = c.dropout_p
+        ctx.philox_seed = c.philox_seed
+        ctx.ENABLE_DROPOUT = c.ENABLE_DROPOUT
+        ctx.set_materialize_grads(False)
+
+    @staticmethod
+    def fwd(
+        q: Tensor,
+        k: Tensor,
+        v: Tensor,
+        attn_mask: Tensor | None = None,
+        dropout_p: float = 0.0,
+        causal: bool = False,
+        sm_scale: float | None = None,
+        warp_specialize: bool = True,
+        USE_TMA: bool = True,
+    ) -> Tensor:
+        """Primal-only attention (upstream: jvp_attention.py:2701-2752).  Returns O."""
+        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out = JVPAttn.apply(q, k, v, None, None, None, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
+                            USE_TMA)
+        a, _ = out
+        return a
+
+    @staticmethod
+    def fwd_dual(
+        q: Tensor,
+        k: Tensor,
+        v: Tensor,
+        attn_mask: Tensor | None = None,
+        dropout_p: float = 0.0,
+        causal: bool = False,
+        sm_scale: float | None = None,
+        warp_specialize: bool = True,
+        USE_TMA: bool = True,
+    ) -> Tensor:
+        """Attention on forward-AD dual tensors (upstream: jvp_attention.py:2755-2813).
+
+        q, k, v may be dual tensors (``fwAD.make_dual`` or inside ``torch.func.jvp``); the result
+        is a dual tensor whose tangent is tO.  Tangents are unpacked here, before autograd sees
+        them, and travel to the kernel as explicit arguments.
+        """
+        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        _, q_t = fwAD.unpack_dual(q)
+        _, k_t = fwAD.unpack_dual(k)
+        _, v_t = fwAD.unpack_dual(v)
+        out = JVPAttn.apply(q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
+                            USE_TMA)
+        a, _ = out
+        return a
+
+    @staticmethod
+    def jvp(ctx: "JVPAttn.FnCtx", gq: Tensor, gk: Tensor, gv: Tensor, *_) -> "JVPAttn.JVPOut":
+        """Returns the tangent computed by the fused forward (upstream: jvp_attention.py:2816-2828),
+        routed through ``_TangentBridge`` so that it carries a gradient."""
+        o_t, q, k, v, q_t, k_t, v_t, o, M, mu = ctx.saved_for_forward
+        if o_t is None:
+            raise RuntimeError(
+                "JVPAttn.jvp needs tangents at forward time: call JVPAttn.fwd_dual (or pass q_t, k_t, v_t to apply)"
+            )
+        tq = gq if gq is not None else (q_t if q_t is not None else torch.zeros_like(q))
+        tk = gk if gk is not None else (k_t if k_t is not None else torch.zeros_like(k))
+        tv = gv if gv is not None else (v_t if v_t is not None else torch.zeros_like(v))
+        t = _TangentBridge.apply(q, k, v, tq, tk, tv, o_t, o, M, mu, ctx.mask_spec, ctx.sm_scale)
+        return JVPAttn.JVPOut(t, None)
+
+    @staticmethod
+    def backward(ctx, do, _) -> "JVPAttn.BwdOut":
+        """Gradient of <do, O> w.r.t. q, k, v (upstream: jvp_attention.py:2831-2978)."""
+        if do is None:
+            return JVPAttn.BwdOut(*([None] * 13))
+        # Inside fwAD.dual_level() the saved q, k, v are still dual; only their primal parts (which
+        # keep the backward graph needed for double backward) may enter the next Function.
+        q, k, v, o, M = (fwAD.unpack_dual(x).primal for x in ctx.saved_tensors)
+        _check_bwd_layout(q, k, v, o)
+        dq, dk, dv = _AttnBwd.apply(q, k, v, o.detach(), M, fwAD.unpack_dual(do).primal, ctx.mask_spec,
+                                    ctx.sm_scale)
+        return JVPAttn.BwdOut(dq, dk, dv, None, None, None, None, None, None, None, None, None, None)
+
+
+attention = JVPAttn.fwd
+
+
+def scaled_dot_product_attention(query: Tensor, key: Tensor, value: Tensor, attn_mask: Tensor | None = None,
+                                 dropout_p: float = 0.0, is_causal: bool = False,
+                                 scale: float | None = None) -> Tensor:
+    """``torch.nn.functional.scaled_dot_product_attention``-shaped entry point.
+
+    Accepts plain or forward-AD dual (B, H, L, D) tensors and forwards to ``JVPAttn.fwd_dual``
+    with SDPA's argument names, which is how upstream's README wires the kernel into a model.
+    """
+    return JVPAttn.fwd_dual(query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, causal=is_causal,
+                            sm_scale=scale)

@@ -1,0 +1,384 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI of libjvpfa.so, against the float64
+oracle on the same seeded inputs, against upstream's golden outputs, and through the public
+Python API (both forward-AD routes, gradients through O and tO, Hessian-vector product).
+
+Tolerances are the ones the project states for itself:
+  float32           max|x - ref| / max|ref| <= 1e-5   (3xTF32 tensor-core path)
+  bfloat16/float16  max|x - ref|            <= 2e-2
+"""
+import numpy as np
+import pytest
+import torch
+import torch.autograd.forward_ad as fwAD
+
+import jvp_flash_attention_b200.jvp_attention as ja
+from jvp_flash_attention_b200 import _lib, workloads
+from oracle import jvp_attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FP32_REL = 1e-5
+HALF_ABS = 2e-2
+DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+def _close(x, ref, dtype, what):
+    """O and tO are held to the stated tolerances as they are.  Gradients (names starting with
+    'd', 'grad', 'hvp') of 16-bit runs can exceed 1 in magnitude, where 2e-2 is below the storage
+    precision of bfloat16, so their absolute tolerance scales with max(1, max|ref|)."""
+    if dtype == torch.float32:
+        e = orc.rel_err(x, ref)
+        assert e <= FP32_REL, f"{what}: rel err {e:.3e} > {FP32_REL}"
+    else:
+        e = orc.max_abs_err(x, ref)
+        tol = HALF_ABS
+        if what[0] in "dgh":
+            tol *= max(1.0, torch.as_tensor(ref).abs().max().item())
+        assert e <= tol, f"{what}: abs err {e:.3e} > {tol:.3e}"
+
+
+def _make(B, H, L, D, dtype, seed, n=8, tangent_std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    ts = [torch.randn(B, H, L, D, generator=g) for _ in range(n)]
+    for i in (3, 4, 5):
+        ts[i] = ts[i] * tangent_std
+    return [t.to(dtype) for t in ts]
+
+
+def _mask(kind, B, H, L, dtype, seed):
+    """Returns (user-facing mask tensor or None, causal flag)."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    if kind == "none":
+        return None, False
+    if kind == "causal":
+        return None, True
+    if kind == "kvlen":
+        lens = torch.randint(L // 2, L + 1, (B,), generator=g)
+        lens[0] = L // 2 + 3  # ragged inside a tile
+        return (torch.arange(L)[None, :] < lens[:, None])[:, None, None, :], False
+    if kind == "bool":
+        m = torch.rand(B, H, L, L, generator=g) > 0.5
+        m[..., 0] = True
+        return m, False
+    if kind == "bool_bcast":
+        m = torch.rand(1, H, L, L, generator=g) > 0.3
+        m[..., 0] = True
+        return m, False
+    if kind == "bias":
+        return torch.randn(B, H, L, L, generator=g).clamp_(-5, 5).to(dtype), False
+    if kind == "bias_f32_bcast":
+        return torch.randn(B, 1, L, L, generator=g).clamp_(-5, 5), False
+    raise ValueError(kind)
+
+
+def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC):
+    """fwd + preprocess + bwd through the C ABI on cuda:0.  Returns o, to, lse, mu, dq, dk, dv."""
+    dev = torch.device("cuda:0")
+    B, H, L, D = q.shape
+    cu = lambda x: None if x is None else x.to(dev).contiguous()  # noqa: E731
+    q, k, v, tq, tk, tv, go, gto = (cu(x) for x in (q, k, v, tq, tk, tv, go, gto))
+    spec, _, _ = ja.classify_mask(cu(mask), causal, B, H, L, q.dtype, False)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, L, device=dev, dtype=torch.float32)
+    dual = tq is not None
+    to = torch.empty_like(q) if dual else None
+    mu = torch.empty_like(lse) if dual else None
+    _lib.fwd(q, k, v, tq, tk, tv, o, to, lse, mu, spec, D**-0.5, impl)
+    dq = dk = dv = None
+    if go is not None or gto is not None:
+        stats = torch.empty(3, B, H, L, device=dev, dtype=torch.float32)
+        use_t = gto is not None
+        _lib.bwd_preprocess(o, to if use_t else None, go, gto, mu if use_t else None, stats[0], stats[1], stats[2])
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        _lib.bwd(q, k, v, tq if use_t else None, tk if use_t else None, tv if use_t else None, go, gto, lse,
+                 mu if use_t else None, stats[0], stats[1], stats[2], dq, dk, dv, spec, D**-0.5, impl)
+    torch.cuda.synchronize()
+    return o, to, lse, mu, dq, dk, dv
+
+
+FWD_CASES = [
+    # dtype, D, L, mask kind
+    ("fp32", 64, 64, "none"), ("fp32", 64, 96, "causal"), ("fp32", 128, 64, "bias"), ("fp32", 32, 160, "kvlen"),
+    ("fp32", 64, 64, "bool"), ("fp32", 128, 96, "bool_bcast"),
+    ("bf16", 64, 128, "none"), ("bf16", 64, 160, "causal"), ("bf16", 128, 96, "kvlen"), ("bf16", 32, 64, "bias"),
+    ("bf16", 64, 64, "bias_f32_bcast"), ("bf16", 128, 128, "causal"),
+    ("fp16", 64, 128, "kvlen"), ("fp16", 128, 64, "none"), ("fp16", 64, 96, "bool"), ("fp16", 32, 96, "causal"),
+]
+
+
+@pytest.mark.parametrize("dt,D,L,kind", FWD_CASES)
+def test_forward_and_backward_through_both_outputs(dt, D, L, kind):
+    dtype = DT[dt]
+    B, H = 2, 2
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, D, dtype, seed=D + L)
+    mask, causal = _mask(kind, B, H, L, dtype, seed=L)
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(q, k, v, tq, tk, tv, go, gto, attn_mask=mask, causal=causal)
+    o, to, lse, mu, dq, dk, dv = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal)
+    _close(o, ro, dtype, "O")
+    _close(to, rto, dtype, "tO")
+    _close(dq, rdq, dtype, "dq")
+    _close(dk, rdk, dtype, "dk")
+    _close(dv, rdv, dtype, "dv")
+    r = orc.tiled_forward(q, k, v, tq, tk, tv, attn_mask=mask, causal=causal)
+    assert orc.max_abs_err(lse, r["lse"]) < (1e-4 if dtype == torch.float32 else 2e-2)
+    assert orc.max_abs_err(mu, r["mu"]) < (1e-4 if dtype == torch.float32 else 5e-2)
+
+
+@pytest.mark.parametrize("dt", ["fp32", "bf16"])
+@pytest.mark.parametrize("which", ["o_only", "to_only"])
+def test_single_cotangent_modes(dt, which):
+    dtype = DT[dt]
+    B, H, L, D = 1, 3, 128, 64
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, D, dtype, seed=7)
+    go_, gto_ = (go, None) if which == "o_only" else (None, gto)
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(q, k, v, tq, tk, tv, go_, gto_, causal=True)
+    o, to, _, _, dq, dk, dv = _run_kernels(q, k, v, tq, tk, tv, go_, gto_, None, True)
+    for x, r_, n in ((o, ro, "O"), (to, rto, "tO"), (dq, rdq, "dq"), (dk, rdk, "dk"), (dv, rdv, "dv")):
+        _close(x, r_, dtype, n)
+
+
+def test_primal_only_forward_matches_dual_primal():
+    q, k, v, tq, tk, tv, *_ = _make(2, 2, 96, 64, torch.float32, seed=9)
+    o1, to1, lse1, mu1, *_ = _run_kernels(q, k, v, None, None, None, None, None, None, False)
+    o2, *_ = _run_kernels(q, k, v, tq, tk, tv, None, None, None, False)
+    assert to1 is None and mu1 is None
+    assert torch.equal(o1, o2)
+    _close(o1, orc.sdpa_primal(q, k, v), torch.float32, "O")
+
+
+def test_fully_masked_rows_give_zero_and_no_nan():
+    B, H, L, D = 1, 2, 64, 64
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, D, torch.float32, seed=3)
+    mask = torch.rand(B, H, L, L, generator=torch.Generator().manual_seed(1)) > 0.5
+    mask[0, 0, 5] = False
+    mask[0, 1, 40:48] = False
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(q, k, v, tq, tk, tv, go, gto, attn_mask=mask)
+    o, to, lse, mu, dq, dk, dv = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, False)
+    assert o[0, 0, 5].abs().max() == 0 and to[0, 1, 40:48].abs().max() == 0
+    assert torch.isinf(lse[0, 0, 5])
+    for x, r_, n in ((o, ro, "O"), (to, rto, "tO"), (dq, rdq, "dq"), (dk, rdk, "dk"), (dv, rdv, "dv")):
+        assert torch.isfinite(x).all(), n
+        _close(x, r_, torch.float32, n)
+
+
+def test_kvlen_zero_and_full():
+    B, H, L, D = 3, 1, 64, 64
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, D, torch.float32, seed=4)
+    lens = torch.tensor([0, 64, 1], dtype=torch.int32)
+    dev = torch.device("cuda:0")
+    spec = _lib.MaskSpec(_lib.MASK_KVLEN, lens.to(dev))
+    cu = lambda x: x.to(dev)  # noqa: E731
+    o, to = torch.empty_like(cu(q)), torch.empty_like(cu(q))
+    lse = torch.empty(B, H, L, device=dev)
+    mu = torch.empty_like(lse)
+    _lib.fwd(cu(q), cu(k), cu(v), cu(tq), cu(tk), cu(tv), o, to, lse, mu, spec, D**-0.5, _lib.IMPL_GENERIC)
+    torch.cuda.synchronize()
+    assert o[0].abs().max() == 0 and to[0].abs().max() == 0
+    ro, rto = orc.sdpa_jvp(q[1:2], k[1:2], v[1:2], tq[1:2], tk[1:2], tv[1:2])
+    _close(o[1:2], ro, torch.float32, "O full")
+    _close(to[1:2], rto, torch.float32, "tO full")
+    # one valid key: O is that value row, tO is its tangent row
+    _close(o[2], v[2, :, :1].expand(-1, L, -1), torch.float32, "O one key")
+    _close(to[2], tv[2, :, :1].expand(-1, L, -1), torch.float32, "tO one key")
+
+
+GOLDEN = ["none_L64_D32", "causal_L64_D32", "bool_L64_D32", "additive_L64_D32", "none_L128_D64", "causal_L128_D64"]
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_against_upstream_golden_outputs(golden_dir, name):
+    """Same inputs as upstream's own kernels saw (interpreter run, fp32): forward-dual and the
+    backward of sum(O*w).  2e-5 = this library's 1e-5 plus upstream's own fp32 rounding."""
+    z = np.load(golden_dir / f"upstream_{name}.npz")
+    t = {k_: torch.from_numpy(z[k_]) for k_ in z.files if k_ not in ("causal", "mask_kind")}
+    o, to, _, _, dq, dk, dv = _run_kernels(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], t["w"], None,
+                                           t.get("mask"), bool(z["causal"]))
+    for got, key in ((o, "o"), (to, "to"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        e = orc.rel_err(got, t[key])
+        assert e <= 2e-5, f"{key}: {e:.3e}"
+
+
+# ------------------------------------------------------------------------------------------------
+# Public API
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("route", ["func_jvp", "fwad"])
+@pytest.mark.parametrize("dt,kind", [("fp32", "none"), ("bf16", "causal"), ("fp16", "kvlen"), ("fp32", "bias")])
+def test_api_routes_and_grads_through_both(route, dt, kind):
+    dtype = DT[dt]
+    B, H, L, D = 2, 2, 128, 64
+    q, k, v, tq, tk, tv, w1, w2 = _make(B, H, L, D, dtype, seed=21)
+    mask, causal = _mask(kind, B, H, L, dtype, seed=2)
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(q, k, v, tq, tk, tv, w1, w2, attn_mask=mask, causal=causal)
+    dev = "cuda:0"
+    a = [x.to(dev).requires_grad_() for x in (q, k, v)]
+    t = [x.to(dev) for x in (tq, tk, tv)]
+    m = None if mask is None else mask.to(dev)
+    fn = lambda q_, k_, v_: ja.JVPAttn.fwd_dual(q_, k_, v_, attn_mask=m, causal=causal)  # noqa: E731
+    if route == "func_jvp":
+        o, to = torch.func.jvp(fn, tuple(a), tuple(t))
+    else:
+        with fwAD.dual_level(), torch.enable_grad():
+            out = fn(*[fwAD.make_dual(x, y) for x, y in zip(a, t)])
+            o, to = fwAD.unpack_dual(out)
+    assert to.requires_grad
+    g = torch.autograd.grad((o.float() * w1.to(dev).float()).sum() + (to.float() * w2.to(dev).float()).sum(), a)
+    _close(o, ro, dtype, "O")
+    _close(to, rto, dtype, "tO")
+    for x, r_, n in zip(g, (rdq, rdk, rdv), ("dq", "dk", "dv")):
+        _close(x, r_, dtype, n)
+
+
+def test_api_hvp_with_bias_fp32():
+    B, H, L, D = 1, 2, 128, 128
+    q, k, v, w, vd, *_ = _make(B, H, L, D, torch.float32, seed=31)
+    bias = torch.randn(B, H, L, L, generator=torch.Generator().manual_seed(3)).clamp_(-5, 5)
+    ro, rg1, rh = orc.hvp_q(q, k, v, w, vd, attn_mask=bias)
+    dev = "cuda:0"
+    q1 = q.to(dev).requires_grad_()
+    o = ja.attention(q1, k.to(dev), v.to(dev), attn_mask=bias.to(dev))
+    (g1,) = torch.autograd.grad((o * w.to(dev)).sum(), q1, create_graph=True)
+    (h,) = torch.autograd.grad((g1 * vd.to(dev)).sum(), q1)
+    _close(o, ro, torch.float32, "O")
+    _close(g1, rg1, torch.float32, "grad")
+    _close(h, rh, torch.float32, "hvp")
+
+
+def test_api_tangent_input_grads():
+    B, H, L, D = 1, 2, 64, 64
+    q, k, v, tq, tk, tv, w1, w2 = _make(B, H, L, D, torch.float32, seed=41)
+    ref_in = [x.double().requires_grad_() for x in (q, k, v, tq, tk, tv)]
+    _, rto = orc.sdpa_jvp(*ref_in)
+    rg = torch.autograd.grad((rto * w2.double()).sum(), ref_in)
+    dev = "cuda:0"
+    a = [x.to(dev).requires_grad_() for x in (q, k, v, tq, tk, tv)]
+    o, to = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a[:3]), tuple(a[3:]))
+    g = torch.autograd.grad((to * w2.to(dev)).sum(), a)
+    for x, r_ in zip(g, rg):
+        _close(x, r_, torch.float32, "grad")
+
+
+def test_api_is_deterministic_and_does_not_touch_inputs():
+    q, k, v, tq, tk, tv, *_ = _make(2, 2, 128, 64, torch.bfloat16, seed=51)
+    dev = "cuda:0"
+    a = [x.to(dev) for x in (q, k, v)]
+    keep = [x.clone() for x in a]
+    o1, to1 = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a), tuple(x.to(dev) for x in (tq, tk, tv)))
+    o2, to2 = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a), tuple(x.to(dev) for x in (tq, tk, tv)))
+    assert torch.equal(o1, o2) and torch.equal(to1, to2)
+    assert all(torch.equal(x, y) for x, y in zip(a, keep))
+
+
+# ------------------------------------------------------------------------------------------------
+# Full-size configurations: sampled heads against the oracle + size-independent properties
+# ------------------------------------------------------------------------------------------------
+def _loss_grads_api(w, dev="cuda:0"):
+    t = {k_: v_.to(dev) for k_, v_ in w.tensors.items() if isinstance(v_, torch.Tensor)}
+    a = [t[n].requires_grad_() for n in ("q", "k", "v")]
+    m = t.get("mask")
+    o, to = torch.func.jvp(lambda q_, k_, v_: ja.JVPAttn.fwd_dual(q_, k_, v_, attn_mask=m, causal=w.causal),
+                           tuple(a), (t["tq"], t["tk"], t["tv"]))
+    return t, a, o, to
+
+
+def test_config2_full_size_sampled_heads_and_linearity():
+    """bf16 causal B4 H16 L2048 D64, loss = mean((tO - target)^2)."""
+    w = workloads.make_workload("c2_bf16_causal")
+    t, a, o, to = _loss_grads_api(w)
+    loss = ((to.float() - t["target"].float()) ** 2).mean()
+    g = torch.autograd.grad(loss, a)
+    n = to.numel()
+    for (b, h) in ((0, 0), (3, 15)):
+        sl = lambda x: x[b:b + 1, h:h + 1]  # noqa: E731
+        cpu = {k_: sl(v_) for k_, v_ in w.tensors.items()}
+        ro, rto = orc.sdpa_jvp(cpu["q"], cpu["k"], cpu["v"], cpu["tq"], cpu["tk"], cpu["tv"], causal=True)
+        gto = 2.0 * (sl(to).detach().cpu().double() - cpu["target"].double()) / n
+        _, _, rdq, rdk, rdv = orc.grads_through_both(cpu["q"], cpu["k"], cpu["v"], cpu["tq"], cpu["tk"], cpu["tv"],
+                                                     None, gto, causal=True)
+        _close(sl(o), ro, torch.bfloat16, "O")
+        _close(sl(to), rto, torch.bfloat16, "tO")
+        # gradients of a mean over 8.4M elements are ~1e-7: compare relative to their scale
+        for x, r_, nme in zip(g, (rdq, rdk, rdv), ("dq", "dk", "dv")):
+            e = orc.rel_err(sl(x), r_)
+            assert e < 3e-2, f"{nme} rel {e:.3e}"
+    # linearity of tO in the tangents: tO(2t) == 2 tO(t) (exact in binary floating point)
+    o2, to2 = torch.func.jvp(lambda q_, k_, v_: ja.JVPAttn.fwd_dual(q_, k_, v_, causal=True),
+                             tuple(x.detach() for x in a), (2 * t["tq"], 2 * t["tk"], 2 * t["tv"]))
+    assert torch.equal(o2, o.detach())
+    assert (to2.float() - 2 * to.detach().float()).abs().max().item() <= 2e-2
+
+
+def test_config3_full_size_keypad_sampled_heads():
+    """fp16 B8 H12 L1024 D64 key padding (B,1,1,L), loss through both outputs."""
+    w = workloads.make_workload("c3_fp16_keypad")
+    t, a, o, to = _loss_grads_api(w)
+    loss = (o.float() * t["w1"].float()).sum() + (to.float() * t["w2"].float()).sum()
+    g = torch.autograd.grad(loss, a)
+    lens = w.tensors["kv_len"]
+    for (b, h) in ((0, 0), (7, 11)):
+        sl = lambda x: x[b:b + 1, h:h + 1]  # noqa: E731
+        c = {k_: sl(v_) for k_, v_ in w.tensors.items() if k_ not in ("kv_len", "mask")}
+        mask = w.tensors["mask"][b:b + 1]
+        ro, rto, rdq, rdk, rdv = orc.grads_through_both(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], c["w1"],
+                                                        c["w2"], attn_mask=mask)
+        _close(sl(o), ro, torch.float16, "O")
+        _close(sl(to), rto, torch.float16, "tO")
+        # cotangents are N(0,1), tangent grads reach O(10): compare relative to scale (fp16 eps ~1e-3)
+        for x, r_, nme in zip(g, (rdq, rdk, rdv), ("dq", "dk", "dv")):
+            e = orc.rel_err(sl(x), r_)
+            assert e < 1e-2, f"{nme} rel {e:.3e}"
+        # padded keys get exactly zero gradient
+        assert sl(g[1])[0, 0, int(lens[b]):].abs().max().item() == 0 if lens[b] < w.L else True
+
+
+def test_config1_and_config4_reduced_checks():
+    """C1 (fp32 B2 H4 L256 D64, loss sum(O)+sum(tO)) in full; C4 (fp32 D128 bias, HVP) at L=256."""
+    w = workloads.make_workload("c1_fp32_plumbing")
+    t, a, o, to = _loss_grads_api(w)
+    g = torch.autograd.grad(o.sum() + to.sum(), a)
+    c = w.tensors
+    ones = torch.ones_like(c["q"])
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], ones, ones)
+    for x, r_, nme in zip((o, to, *g), (ro, rto, rdq, rdk, rdv), ("O", "tO", "dq", "dk", "dv")):
+        _close(x, r_, torch.float32, nme)
+
+    w4 = workloads.make_workload("c4_fp32_bias_hvp", L=256)
+    c = w4.tensors
+    ro, rto = orc.sdpa_jvp(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], attn_mask=c["mask"])
+    _, _, rh = orc.hvp_q(c["q"], c["k"], c["v"], c["w"], c["v_dir"], attn_mask=c["mask"])
+    dev = "cuda:0"
+    d = {k_: v_.to(dev) for k_, v_ in c.items()}
+    o, to = torch.func.jvp(lambda q_, k_, v_: ja.JVPAttn.fwd_dual(q_, k_, v_, attn_mask=d["mask"]),
+                           (d["q"], d["k"], d["v"]), (d["tq"], d["tk"], d["tv"]))
+    q1 = d["q"].clone().requires_grad_()
+    o1 = ja.attention(q1, d["k"], d["v"], attn_mask=d["mask"])
+    (g1,) = torch.autograd.grad((o1 * d["w"]).sum(), q1, create_graph=True)
+    (h,) = torch.autograd.grad((g1 * d["v_dir"]).sum(), q1)
+    _close(o, ro, torch.float32, "O")
+    _close(to, rto, torch.float32, "tO")
+    _close(h, rh, torch.float32, "hvp")
+
+
+def test_library_rejects_bad_arguments_without_launching():
+    import ctypes as C
+
+    lib = _lib.load()
+    a = _lib.FwdArgs()
+    a.struct_size = 3
+    assert lib.jvpfa_fwd(C.byref(a), None) == -7  # JVPFA_ERR_STRUCT
+    a.struct_size = C.sizeof(_lib.FwdArgs)
+    a.dtype, a.B, a.H, a.L, a.D = _lib.FP32, 1, 1, 64, 48
+    assert lib.jvpfa_fwd(C.byref(a), None) == -2  # unsupported head dim
+    a.D = 64
+    assert lib.jvpfa_fwd(C.byref(a), None) == -1  # null pointers
+    assert lib.jvpfa_fwd(None, None) == -1
+    x = torch.zeros(1, 1, 64, 64, device="cuda:0")
+    lse = torch.zeros(1, 1, 64, device="cuda:0")
+    a.q, a.k, a.v, a.o, a.lse = x.data_ptr(), x.data_ptr(), x.data_ptr() + 4, x.data_ptr(), lse.data_ptr()
+    assert lib.jvpfa_fwd(C.byref(a), None) == -8  # misaligned
+    a.v = x.data_ptr()
+    a.tq = x.data_ptr()
+    assert lib.jvpfa_fwd(C.byref(a), None) == -1  # partial tangent set
+    a.tq = None
+    a.mask.kind = _lib.MASK_BOOL
+    assert lib.jvpfa_fwd(C.byref(a), None) == -4  # mask without pointer
+    assert b"mask" in lib.jvpfa_strerror(-4)
