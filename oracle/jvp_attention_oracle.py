@@ -57,9 +57,15 @@ def sdpa_jvp(q, k, v, tq, tk, tv, attn_mask=None, causal=False, scale=None, dtyp
         m = m.cpu()
         if m.dtype != torch.bool:
             m = m.to(dtype)
-    o, to = torch.func.jvp(partial(_sdpa, attn_mask=m, causal=causal, scale=scale), (q, k, v), (tq, tk, tv))
+    dead = None
     if m is not None and m.dtype == torch.bool:
         dead = ~m.any(dim=-1, keepdim=True)
+        if bool(dead.any()):
+            m = m | dead  # let SDPA see finite rows there; the rows are zeroed below (keeps gradients finite)
+        else:
+            dead = None
+    o, to = torch.func.jvp(partial(_sdpa, attn_mask=m, causal=causal, scale=scale), (q, k, v), (tq, tk, tv))
+    if dead is not None:
         dead = dead.expand(*o.shape[:-1], 1)
         o = torch.where(dead, torch.zeros_like(o), o)
         to = torch.where(dead, torch.zeros_like(to), to)

@@ -37,7 +37,12 @@ def _close(x, ref, dtype, what):
         assert e <= tol, f"{what}: abs err {e:.3e} > {tol:.3e}"
 
 
-def _make(B, H, L, D, dtype, seed, n=8, tangent_std=1.0):
+def _make(B, H, L, D, dtype, seed, n=8, tangent_std=None):
+    """Seeded N(0,1) tensors q,k,v,tq,tk,tv,+2.  bfloat16 cases draw tangents from N(0, 0.1^2), the
+    distribution of the bf16 benchmark configurations: with unit tangents |tO| reaches 8, where the
+    spacing of bfloat16 itself (2^-5) exceeds the 2e-2 absolute tolerance."""
+    if tangent_std is None:
+        tangent_std = 0.1 if dtype == torch.bfloat16 else 1.0
     g = torch.Generator().manual_seed(seed)
     ts = [torch.randn(B, H, L, D, generator=g) for _ in range(n)]
     for i in (3, 4, 5):
