@@ -168,6 +168,14 @@ int jvpfa_version(void);
  * (empty string if none).  Static thread-local storage. */
 const char* jvpfa_last_cuda_error(void);
 
+/* Reads the device-side status word of the tcgen05 kernels on the current device into *status:
+ * 0 = every bounded wait completed; otherwise the code of the first wait that gave up (the
+ * kernels then drained and exited early, and their outputs are undefined).  clear != 0 resets
+ * the word.  This call synchronises with the device (it is a cudaMemcpyFromSymbol); it is meant
+ * for tests and post-mortems, not for the hot path.  No upstream counterpart: Triton kernels
+ * have no such waits. */
+int jvpfa_device_status(int* status, int clear);
+
 /* 1 if jvpfa_fwd / jvpfa_bwd with impl == JVPFA_IMPL_AUTO would take the
  * tcgen05 kernels for this shape, else 0 (pure host logic; no CUDA call). */
 int jvpfa_fwd_uses_tcgen05(const jvpfa_fwd_args* args);

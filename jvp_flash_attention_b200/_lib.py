@@ -29,6 +29,7 @@ EXPORTS = (
     "jvpfa_last_cuda_error",
     "jvpfa_fwd_uses_tcgen05",
     "jvpfa_bwd_uses_tcgen05",
+    "jvpfa_device_status",
 )
 
 
@@ -145,8 +146,18 @@ def load() -> C.CDLL:
     lib.jvpfa_fwd_uses_tcgen05.restype = C.c_int
     lib.jvpfa_bwd_uses_tcgen05.argtypes = [C.POINTER(BwdArgs)]
     lib.jvpfa_bwd_uses_tcgen05.restype = C.c_int
+    lib.jvpfa_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
+    lib.jvpfa_device_status.restype = C.c_int
     _lib = lib
     return lib
+
+
+def device_status(clear: bool = True) -> int:
+    """Synchronises and returns the status word of the tcgen05 kernels (0 = no wait gave up)."""
+    lib = load()
+    out = C.c_int(0)
+    check(lib.jvpfa_device_status(C.byref(out), 1 if clear else 0), "jvpfa_device_status")
+    return out.value
 
 
 def check(status: int, what: str) -> None:

@@ -73,7 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     raise RuntimeError(f"nvcc failed for {cmd[-3]}")
     objs = [str(OBJ / (s.stem + ".o")) for s in sources]
     if jobs or not LIB.exists():
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *objs, "-lcudart", "-lcuda"]
+        cmd = [_nvcc(), "-shared", "-o", str(LIB), *objs, "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

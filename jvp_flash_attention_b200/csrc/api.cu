@@ -157,6 +157,11 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   return launch_bwd_generic(*a, static_cast<cudaStream_t>(stream));
 }
 
+int jvpfa_device_status(int* status, int clear) {
+  if (!status) return JVPFA_ERR_NULL;
+  return tc5_read_status(status, clear);
+}
+
 const char* jvpfa_strerror(int status) {
   switch (status) {
     case JVPFA_OK:
