@@ -129,6 +129,69 @@ def test_forward_and_backward_through_both_outputs(dt, D, L, kind):
     assert orc.max_abs_err(mu, r["mu"]) < (1e-4 if dtype == torch.float32 else 5e-2)
 
 
+TC5_CASES = [
+    # dtype, B, H, L, D, mask kind, dual
+    ("bf16", 1, 1, 128, 64, "none", False), ("bf16", 1, 1, 128, 64, "none", True),
+    ("bf16", 2, 2, 256, 64, "causal", True), ("fp16", 2, 2, 192, 64, "kvlen", True),
+    ("bf16", 1, 2, 160, 64, "causal", True), ("bf16", 1, 2, 256, 128, "none", True),
+    ("fp16", 2, 1, 320, 128, "causal", True), ("fp16", 1, 3, 96, 128, "kvlen", False),
+    ("bf16", 2, 2, 1024, 64, "causal", True), ("fp16", 1, 2, 34, 64, "none", True),
+]
+
+
+@pytest.mark.parametrize("dt,B,H,L,D,kind,dual", TC5_CASES)
+def test_tcgen05_forward_against_oracle_and_generic_family(dt, B, H, L, D, kind, dual):
+    """The TMA + tcgen05/TMEM forward, forced through the C ABI, against the float64 oracle, and
+    the register-tiled family on the same inputs (the two must agree to 16-bit rounding)."""
+    dtype = DT[dt]
+    q, k, v, tq, tk, tv, *_ = _make(B, H, L, D, dtype, seed=L + D)
+    if not dual:
+        tq = tk = tv = None
+    mask, causal = _mask(kind, B, H, L, dtype, seed=L)
+    o, to, lse, mu, *_ = _run_kernels(q, k, v, tq, tk, tv, None, None, mask, causal, impl=_lib.IMPL_TCGEN05)
+    assert _lib.device_status() == 0, "a bounded wait inside the tcgen05 kernel gave up"
+    o2, to2, lse2, mu2, *_ = _run_kernels(q, k, v, tq, tk, tv, None, None, mask, causal, impl=_lib.IMPL_GENERIC)
+    if dual:
+        ro, rto = orc.sdpa_jvp(q, k, v, tq, tk, tv, attn_mask=mask, causal=causal)
+        _close(to, rto, dtype, "tO")
+        assert orc.max_abs_err(to, to2) <= HALF_ABS
+        assert orc.max_abs_err(mu, mu2) < 1e-3
+    else:
+        ro = orc.sdpa_primal(q, k, v, attn_mask=mask, causal=causal)
+        assert to is None
+    _close(o, ro, dtype, "O")
+    assert orc.max_abs_err(o, o2) <= HALF_ABS
+    assert orc.max_abs_err(lse, lse2) < 1e-4
+
+
+def test_tcgen05_dispatch_rules():
+    """AUTO takes the tcgen05 kernels exactly for 16-bit, D in {64,128}, none/causal/key-padding."""
+    import ctypes as C
+
+    lib = _lib.load()
+    x = torch.zeros(1, 1, 64, 64, device="cuda:0", dtype=torch.bfloat16)
+    lse = torch.zeros(1, 1, 64, device="cuda:0")
+    a = _lib.FwdArgs()
+    a.struct_size = C.sizeof(_lib.FwdArgs)
+    a.dtype, a.B, a.H, a.L, a.D = _lib.BF16, 1, 1, 64, 64
+    a.q = a.k = a.v = a.o = x.data_ptr()
+    a.lse = lse.data_ptr()
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 1
+    a.impl = _lib.IMPL_GENERIC
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.impl = _lib.IMPL_AUTO
+    a.D = 32
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.impl = _lib.IMPL_TCGEN05
+    assert lib.jvpfa_fwd(C.byref(a), None) == -9  # forcing an ineligible shape is an error, not a fallback
+    a.impl, a.D, a.dtype = _lib.IMPL_AUTO, 64, _lib.FP32
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.dtype = _lib.FP16
+    a.mask.kind = _lib.MASK_BOOL
+    a.mask.ptr = x.data_ptr()
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+
+
 @pytest.mark.parametrize("dt", ["fp32", "bf16"])
 @pytest.mark.parametrize("which", ["o_only", "to_only"])
 def test_single_cotangent_modes(dt, which):
