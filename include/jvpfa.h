@@ -158,6 +158,46 @@ typedef struct {
 
 int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
 
+/*
+ * jvpfa_bwd_noalloc -- jvpfa_bwd_preprocess + jvpfa_bwd in one call, with the three scratch rows
+ * kept inside the library.  It has no counterpart in the reference (whose backward allocates
+ * `delta` with torch, jvp_attention.py:2883); it exists for callers that cannot allocate device
+ * memory at all: programs whose own pool already owns the whole GPU, loops that must avoid
+ * cudaMalloc's device-wide synchronisation, and C-level users of this ABI with no tensor library
+ * to provide scratch.
+ *
+ * Inputs and outputs are the caller's, exactly as for jvpfa_bwd, plus o (and to when gto is
+ * given), which the row reductions read.  The scratch is a fixed device array of
+ * 3 * JVPFA_NOALLOC_MAX_ROWS floats (6 MiB) that every GPU loading the library holds until
+ * process exit.  Limits and rules:
+ *   - B*H*L <= JVPFA_NOALLOC_MAX_ROWS, otherwise JVPFA_ERR_TOO_LARGE and nothing is launched;
+ *   - all calls on one device share the array, so calls that can overlap on the GPU race:
+ *     issue them on one stream (or otherwise serialise them);
+ *   - the array keeps the last call's contents; no part of it needs to be zero beforehand;
+ *   - the first call on each device performs a one-time address look-up for that device and
+ *     should therefore be made before any stream capture is begun there;
+ *   - no cudaMalloc / cudaFree / allocating library routine is called, on any call.
+ */
+#define JVPFA_NOALLOC_MAX_ROWS 524288 /* 2^19 (batch*head*query) rows */
+
+typedef struct {
+  int32_t struct_size;
+  int32_t dtype;
+  int32_t B, H, L, D;
+  int32_t impl;
+  float sm_scale;
+  const void *q, *k, *v;
+  const void *tq, *tk, *tv; /* required iff gto != NULL */
+  const void *o, *to;       /* forward outputs; to required iff gto != NULL */
+  const void *go, *gto;     /* either may be NULL, not both */
+  const float* lse;
+  const float* mu; /* required iff gto != NULL */
+  void *dq, *dk, *dv;
+  jvpfa_mask mask;
+} jvpfa_bwd_noalloc_args;
+
+int jvpfa_bwd_noalloc(const jvpfa_bwd_noalloc_args* args, void* stream);
+
 /* Human-readable text for a jvpfa_status (static storage, never NULL). */
 const char* jvpfa_strerror(int status);
 

@@ -30,7 +30,10 @@ EXPORTS = (
     "jvpfa_fwd_uses_tcgen05",
     "jvpfa_bwd_uses_tcgen05",
     "jvpfa_device_status",
+    "jvpfa_bwd_noalloc",
 )
+
+NOALLOC_MAX_ROWS = 524288  # JVPFA_NOALLOC_MAX_ROWS
 
 
 class Mask(C.Structure):
@@ -116,6 +119,35 @@ class BwdArgs(C.Structure):
     ]
 
 
+class BwdNoAllocArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("dtype", C.c_int32),
+        ("B", C.c_int32),
+        ("H", C.c_int32),
+        ("L", C.c_int32),
+        ("D", C.c_int32),
+        ("impl", C.c_int32),
+        ("sm_scale", C.c_float),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("tq", C.c_void_p),
+        ("tk", C.c_void_p),
+        ("tv", C.c_void_p),
+        ("o", C.c_void_p),
+        ("to", C.c_void_p),
+        ("go", C.c_void_p),
+        ("gto", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("mu", C.c_void_p),
+        ("dq", C.c_void_p),
+        ("dk", C.c_void_p),
+        ("dv", C.c_void_p),
+        ("mask", Mask),
+    ]
+
+
 _lib = None
 
 
@@ -148,6 +180,8 @@ def load() -> C.CDLL:
     lib.jvpfa_bwd_uses_tcgen05.restype = C.c_int
     lib.jvpfa_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
     lib.jvpfa_device_status.restype = C.c_int
+    lib.jvpfa_bwd_noalloc.argtypes = [C.POINTER(BwdNoAllocArgs), C.c_void_p]
+    lib.jvpfa_bwd_noalloc.restype = C.c_int
     _lib = lib
     return lib
 
@@ -259,3 +293,29 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
     a.mask = mask.to_c()
     with torch.cuda.device(q.device):
         check(lib.jvpfa_bwd(C.byref(a), _stream(q)), "jvpfa_bwd")
+
+
+def bwd_noalloc(q, k, v, tq, tk, tv, o, to, go, gto, lse, mu, dq, dk, dv, mask: MaskSpec, sm_scale: float,
+                impl: int = IMPL_AUTO) -> None:
+    """Launches jvpfa_bwd_noalloc: the backward for callers that cannot allocate device memory.
+
+    Same gradients as ``bwd_preprocess`` + ``bwd``, but the three (B,H,L) scratch rows live in a
+    fixed 6 MiB array inside libjvpfa.so, so the caller passes only inputs and outputs.
+    B*H*L must not exceed ``NOALLOC_MAX_ROWS``; calls on one device share the array and must
+    not overlap on the GPU; the first call per device should precede any stream capture."""
+    lib = load()
+    B, H, L, D = q.shape
+    a = BwdNoAllocArgs()
+    a.struct_size = C.sizeof(BwdNoAllocArgs)
+    a.dtype = DTYPE_ENUM[q.dtype]
+    a.B, a.H, a.L, a.D = B, H, L, D
+    a.impl = impl
+    a.sm_scale = sm_scale
+    a.q, a.k, a.v = ptr(q), ptr(k), ptr(v)
+    a.tq, a.tk, a.tv = ptr(tq), ptr(tk), ptr(tv)
+    a.o, a.to, a.go, a.gto = ptr(o), ptr(to), ptr(go), ptr(gto)
+    a.lse, a.mu = ptr(lse), ptr(mu)
+    a.dq, a.dk, a.dv = ptr(dq), ptr(dk), ptr(dv)
+    a.mask = mask.to_c()
+    with torch.cuda.device(q.device):
+        check(lib.jvpfa_bwd_noalloc(C.byref(a), _stream(q)), "jvpfa_bwd_noalloc")
