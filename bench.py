@@ -54,7 +54,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -205,10 +205,10 @@ def run_ours(args, rank, world, local):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)  # runs through warm-up and the timed region (both under load)
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     for s, e in evs:
         flush.zero_()
@@ -233,11 +233,27 @@ def run_ours(args, rank, world, local):
             ts.append(s.elapsed_time(e))
         return sum(ts) / len(ts)
 
+    def k_bwd_only(flag):
+        def f():
+            _lib.bwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], None, gto, lse, mu, stats[0], stats[1],
+                     stats[2], dq, dk, dv, spec, scale, _lib.IMPL_AUTO | flag)
+        return f
+
     reps = max(3, min(args.steps, 20))
     br = {"fwd_dual": time_call(k_fwd, reps), "loss(torch)": time_call(k_loss, reps),
-          "bwd_preprocess": time_call(k_pre, reps), "bwd": time_call(k_bwd, reps)}
+          "bwd_preprocess": time_call(k_pre, reps), "bwd": time_call(k_bwd, reps),
+          "bwd_dkdv_only": time_call(k_bwd_only(_lib.IMPL_ONLY_DKDV), reps),
+          "bwd_dq_only": time_call(k_bwd_only(_lib.IMPL_ONLY_DQ), reps)}
+    step()  # leave dq, dk, dv complete again
 
     # ---- end to end through the public API, host buffers in, loss out ----
+    if args.skip_e2e:
+        if rank == 0:
+            print(json.dumps({"note": "--skip-e2e: profiling run, no bench line", "ms_per_step": ms,
+                              "breakdown_ms": br}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     copy_stream = torch.cuda.Stream(dev)
     bufs = [{k_: torch.empty_like(v_, device=dev) for k_, v_ in host.items()} for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
@@ -298,7 +314,21 @@ def run_ours(args, rank, world, local):
         stage_flops = {"fwd_dual": workloads.flops(w, ("fwd_dual",)), "bwd": workloads.flops(w, ("bwd_to",))}
         dom = max(("fwd_dual", "bwd"), key=lambda n: br[n])
         ach = stage_flops[dom] / (br[dom] * 1e-3) / 1e12
-        uses_tc5 = {"fwd_dual": False, "bwd": False}
+        n_pairs = w.attended_pairs()
+        mma = 2.0 * D * n_pairs  # flops of one L x L x D product over the attended pairs
+        kernels = [
+            {"name": "fwd_tc5_kernel (fwd_dual)", "ms": br["fwd_dual"], "mma_executed": 6, "mma_algorithmic": 6},
+            {"name": "bwd_tc5_kernel<own keys> (dK,dV)", "ms": br["bwd_dkdv_only"], "mma_executed": 8,
+             "mma_algorithmic": None},
+            {"name": "bwd_tc5_kernel<own queries> (dQ)", "ms": br["bwd_dq_only"], "mma_executed": 7,
+             "mma_algorithmic": None},
+            {"name": "pre_kernel (HBM bound)", "ms": br["bwd_preprocess"],
+             "gbs": (3 * n_el * 2 + 4 * B * H * L * 4) / (br["bwd_preprocess"] * 1e-3) / 1e9,
+             "frac_of_hbm_peak": (3 * n_el * 2 + 4 * B * H * L * 4) / (br["bwd_preprocess"] * 1e-3) / 1e9 / peaks["hbm"]},
+        ]
+        for kk in kernels[:3]:
+            kk["tflops_executed"] = kk["mma_executed"] * mma / (kk["ms"] * 1e-3) / 1e12
+            kk["frac_of_burst_peak"] = kk["tflops_executed"] / peaks["burst"]
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
@@ -314,11 +344,16 @@ def run_ours(args, rank, world, local):
                     "ms_per_step": e2e_max, "wall_ms_per_step": e2e_wall_ms,
                     "path": "torch.func.jvp(JVPAttn.fwd_dual) + autograd.grad; pinned host inputs, double-buffered H2D"},
             "gpu_launches": 4 * args.steps,
-            "roofline": {"bound": "tensor", "kernel": f"jvpfa_{dom}", "achieved": ach, "peak": peaks["burst"],
+            "roofline": {"bound": "tensor",
+                         "kernel": "jvpfa_fwd (fwd_tc5_kernel)" if dom == "fwd_dual" else
+                         "jvpfa_bwd (bwd_tc5_kernel own-keys + own-queries launches, timed as one call; "
+                         "10 algorithmic MMAs, 15 executed because both launches recompute the score tiles)",
+                         "achieved": ach, "peak": peaks["burst"],
                          "unit": "TFLOP/s", "frac": ach / peaks["burst"], "traffic": None,
                          "peak_source": f"{peaks['src']} bf16 burst (kernel timed alone)",
                          "ms_per_launch": br[dom], "algorithmic_flops_per_launch": stage_flops[dom]},
             "breakdown_ms": br,
+            "kernels": kernels,
             "last_loss": loss_host,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -333,8 +368,9 @@ def run_ours(args, rank, world, local):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--skip-e2e", action="store_true", help="stop after the device-resident part (profiling runs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_bf16_causal")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -17,6 +17,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libjvpfa.so"
 BF16, FP16, FP32 = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_KVLEN, MASK_BOOL, MASK_BIAS = 0, 1, 2, 3, 4
 IMPL_AUTO, IMPL_GENERIC, IMPL_TCGEN05 = 0, 1, 2
+IMPL_ONLY_DKDV, IMPL_ONLY_DQ = 0x100, 0x200  # measurement aids for jvpfa_bwd
 
 DTYPE_ENUM = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32}
 

@@ -82,6 +82,8 @@ static int validate_fwd(const jvpfa_fwd_args* a) {
   return check_mask(a->mask);
 }
 
+static int impl_family(int impl) { return impl & 0xff; }
+
 static int validate_bwd(const jvpfa_bwd_args* a) {
   if (!a) return JVPFA_ERR_NULL;
   if (a->struct_size != (int32_t)sizeof(jvpfa_bwd_args)) return JVPFA_ERR_STRUCT;
@@ -93,7 +95,7 @@ static int validate_bwd(const jvpfa_bwd_args* a) {
   const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->go, a->gto, a->dq, a->dk, a->dv};
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
-  if (a->impl < JVPFA_IMPL_AUTO || a->impl > JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
+  if (impl_family(a->impl) > JVPFA_IMPL_TCGEN05 || (a->impl & ~0x3ff) != 0) return JVPFA_ERR_UNSUPPORTED;
   return check_mask(a->mask);
 }
 
@@ -124,8 +126,9 @@ int jvpfa_fwd_uses_tcgen05(const jvpfa_fwd_args* a) {
 }
 
 int jvpfa_bwd_uses_tcgen05(const jvpfa_bwd_args* a) {
-  (void)a;
-  return 0;
+  if (validate_bwd(a) != JVPFA_OK) return 0;
+  if (impl_family(a->impl) == JVPFA_IMPL_GENERIC) return 0;
+  return bwd_tc5_eligible(*a) ? 1 : 0;
 }
 
 int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
@@ -153,8 +156,12 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   if (rc) return rc;
   rc = check_arch();
   if (rc) return rc;
-  if (a->impl == JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
-  return launch_bwd_generic(*a, static_cast<cudaStream_t>(stream));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc5 = bwd_tc5_eligible(*a);
+  const int fam = impl_family(a->impl);
+  if (fam == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
+  if (tc5 && fam != JVPFA_IMPL_GENERIC) return launch_bwd_tc5(*a, s);
+  return launch_bwd_generic(*a, s);
 }
 
 int jvpfa_device_status(int* status, int clear) {

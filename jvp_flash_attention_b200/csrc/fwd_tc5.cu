@@ -24,21 +24,21 @@
 namespace jvpfa {
 
 __device__ int g_tc5_status = 0;
+// Device address of the status word on the current device (other translation units receive it
+// as a kernel argument).  Looked up once per device.
+int* tc5_status_device_ptr() {
+  static int* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cache[dev]) {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc5_status) != cudaSuccess) return nullptr;
+    cache[dev] = p;
+  }
+  return cache[dev];
+}
 
 namespace tc5 {
-
-template <typename T>
-struct Fmt;
-template <>
-struct Fmt<__nv_bfloat16> {
-  static constexpr int kIdesc = 1;
-  static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-};
-template <>
-struct Fmt<__half> {
-  static constexpr int kIdesc = 0;
-  static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-};
 
 template <int D, bool DUAL>
 struct FwdCfg {
@@ -65,12 +65,6 @@ struct FwdCfg {
 struct FwdMaps {
   CUtensorMap q, tq, k, tk, v, tv;
 };
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 template <typename T, int D, bool DUAL>
 __global__ void __launch_bounds__(192, FwdCfg<D, DUAL>::MIN_CTAS)
@@ -425,8 +419,7 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// (D, L, B*H) view of a contiguous (B, H, L, D) 16-bit tensor; box = 64 columns x box_rows rows.
-static bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH,
+bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH,
                        int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;

@@ -26,7 +26,36 @@ enum AbortCode : int {
   kAbortPFull = 5,
   kAbortOFull = 6,
   kAbortAux = 7,
+  kAbortBwdOwn = 8,
+  kAbortBwdLoopFull = 9,
+  kAbortBwdLoopEmpty = 10,
+  kAbortBwdSFull = 11,
+  kAbortBwdPFull = 12,
+  kAbortBwdDone = 13,
 };
+
+template <typename T>
+struct Fmt;
+template <>
+struct Fmt<__nv_bfloat16> {
+  static constexpr int kIdesc = 1;
+  static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+};
+template <>
+struct Fmt<__half> {
+  static constexpr int kIdesc = 0;
+  static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Host: (D, L, B*H) view of a contiguous (B, H, L, D) 16-bit tensor, box = 64 columns x box_rows
+// rows, 128-byte swizzle, out-of-range rows read as zero.  Defined in fwd_tc5.cu.
+bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH, int box_rows);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -140,6 +169,20 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 
 // ---- UMMA descriptors ----------------------------------------------------------------------
