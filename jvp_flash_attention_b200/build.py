@@ -31,6 +31,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-I",
     str(INCLUDE),
+    *os.environ.get("JVPFA_EXTRA_NVCC_FLAGS", "").split(),
 ]
 
 

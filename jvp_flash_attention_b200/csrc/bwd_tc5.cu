@@ -516,6 +516,7 @@ bool bwd_tc5_eligible(const jvpfa_bwd_args& a) {
 }
 
 int launch_bwd_tc5(const jvpfa_bwd_args& a, cudaStream_t s) {
+  if (a.D == 64) return launch_bwd_tc5_d64(a, s);  // pipelined variant (bwd_tc5_d64.cu)
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);
 }
 
