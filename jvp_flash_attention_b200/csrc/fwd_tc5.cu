@@ -483,6 +483,7 @@ bool fwd_tc5_eligible(const jvpfa_fwd_args& a) {
 }
 
 int launch_fwd_tc5(const jvpfa_fwd_args& a, cudaStream_t s) {
+  if (a.D == 64) return launch_fwd_tc5_d64(a, s);  // two-issuer variant (fwd_tc5_d64.cu)
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);
 }
 

@@ -1,0 +1,528 @@
+// Fused primal (+ tangent) attention forward for head dimension 64 (bf16 / fp16; none, causal,
+// key padding) on tcgen05 / TMA / TMEM: the variant of fwd_tc5.cu tuned to how the B200 tensor
+// pipe is fed.  A single thread can issue a tcgen05.mma only about every 58-70 cycles whatever
+// N <= 128 is, so the kernel (a) halves the instruction count by letting one N=128 instruction
+// cover two accumulators that share the A operand and whose B tiles are neighbours in shared
+// memory, and (b) issues from two warps with disjoint accumulator chains:
+//
+//   issuer A:  [S | tS] = Q [K ; tK]^T  (N=128) ;  tS += tQ K^T  (N=64)         -> s_full
+//   issuer B:  [O | tO'] += P [V | tV]  (N=128) ;  tO' += W V    (N=64)         -> kv_empty[stage]
+//
+// CTA = one 128-row query tile of one (batch, head); 7 warps: TMA producer, issuer A, issuer B,
+// four softmax / epilogue warps (thread <-> query row <-> TMEM lane).  TMEM columns:
+//   S [64] | tS [64] | O [64] | tO' [64]   (256 columns -> two CTAs per SM)
+// P and W = P*tS*scale are written as packed 16-bit values over the head of S and tS and feed
+// issuer B's MMAs as TMEM A operands.  Online softmax with lazy rescaling as in fwd_tc5.cu; the
+// per-row arithmetic uses packed fp32x2 instructions.
+#include "tc5_common.cuh"
+
+namespace jvpfa {
+namespace tc5 {
+
+template <bool DUAL>
+struct Fwd64Cfg {
+  static constexpr int D = 64;
+  static constexpr int BM = 128;
+  static constexpr int BN = 64;
+  static constexpr int STAGES = 2;
+  static constexpr int NTHREADS = 224;
+  static constexpr int Q_BYTES = BM * D * 2;   // 16 KiB
+  static constexpr int KV_BYTES = BN * D * 2;  // 8 KiB
+  static constexpr int N_Q = DUAL ? 2 : 1;
+  static constexpr int N_KV = DUAL ? 4 : 2;
+  // stage layout: K, tK, V, tV (DUAL) or K, V
+  static constexpr int SLOT_K = 0, SLOT_TK = 1, SLOT_V = DUAL ? 2 : 1, SLOT_TV = 3;
+  static constexpr int TILE_BYTES = N_Q * Q_BYTES + STAGES * N_KV * KV_BYTES;
+  static constexpr int SMEM_BYTES = TILE_BYTES + 256 + 1024;
+  static constexpr int COL_S = 0;
+  static constexpr int COL_TS = 64;
+  static constexpr int COL_O = DUAL ? 128 : 64;
+  static constexpr int COL_TO = 192;
+  static constexpr int COLS_ALLOC = DUAL ? 256 : 128;
+};
+
+struct Fwd64Maps {
+  CUtensorMap q, tq, k, tk, v, tv;
+};
+
+#ifdef JVPFA_TC5_PROFILE
+__device__ unsigned long long g_fprof[32];
+#define FPROF_T0(v) long long v = clock64()
+#define FPROF_ACC(var, v) var += clock64() - (v)
+#else
+#define FPROF_T0(v)
+#define FPROF_ACC(var, v)
+#endif
+
+__device__ __forceinline__ float2 ff2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(224, 2)
+fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps maps, int* status) {
+  using C = Fwd64Cfg<DUAL>;
+  constexpr int D = 64, BM = C::BM, BN = C::BN, STAGES = C::STAGES;
+
+  if (*(volatile int*)status != 0) return;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* sQ = smem;
+  unsigned char* sTQ = sQ + C::Q_BYTES;  // DUAL only
+  unsigned char* sKV = smem + C::N_Q * C::Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::TILE_BYTES);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;            // [STAGES]
+  uint64_t* kv_empty = bars + 1 + STAGES;  // [STAGES]
+  uint64_t* s_full = bars + 1 + 2 * STAGES;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* o_full = s_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 3);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int L = a.L;
+  const int bh = blockIdx.y;
+  const int b = bh / a.H;
+  const int mt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
+  const int m0 = mt * BM;
+  const bool causal = a.mask.kind == JVPFA_MASK_CAUSAL;
+  int n_valid = L;
+  if (a.mask.kind == JVPFA_MASK_KVLEN) {
+    const int n = a.mask.kv_len[b];
+    n_valid = n < 0 ? 0 : (n > L ? L : n);
+  }
+  int n_end = n_valid;
+  if (causal) n_end = min(n_end, m0 + BM);
+  const int n_tiles = (n_end + BN - 1) / BN;
+
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::COLS_ALLOC);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const AbortState ab{abort_flag, status};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
+      tma_load_3d(sQ, &maps.q, q_full, 0, m0, bh);
+      if constexpr (DUAL) tma_load_3d(sTQ, &maps.tq, q_full, 0, m0, bh);
+      for (int it = 0; it < n_tiles; ++it) {
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(kv_empty + st, ph ^ 1, ab, kAbortKvEmpty)) break;
+        unsigned char* base = sKV + st * (C::N_KV * C::KV_BYTES);
+        mbar_expect_tx(kv_full + st, C::N_KV * C::KV_BYTES);
+        const int n0 = it * BN;
+        tma_load_3d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, bh);
+        tma_load_3d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, bh);
+        if constexpr (DUAL) {
+          tma_load_3d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, bh);
+          tma_load_3d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, bh);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ issuer A: scores
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kIdesc, BM, BN, 0, 0);       // 128 x 64
+      constexpr uint32_t idesc_s2 = make_idesc(Fmt<T>::kIdesc, BM, 2 * BN, 0, 0);  // 128 x 128: [S | tS]
+      const uint32_t aQ = smem_u32(sQ), aTQ = smem_u32(sTQ);
+      bool ok = mbar_wait(q_full, 0, ab, kAbortQFull);
+#ifdef JVPFA_TC5_PROFILE
+      long long a_w1 = 0, a_w2 = 0, a_is = 0;
+      const long long a_t0 = clock64();
+#endif
+      for (int it = 0; ok && it < n_tiles; ++it) {
+        const int st = it % STAGES;
+        FPROF_T0(ta1);
+        // S / tS still hold P / W of the previous tile until issuer B's chain for it has completed.
+        if (it > 0 && !mbar_wait(kv_empty + ((it - 1) % STAGES), ((it - 1) / STAGES) & 1, ab, kAbortKvEmpty)) break;
+        FPROF_ACC(a_w1, ta1);
+        FPROF_T0(ta2);
+        if (!mbar_wait(kv_full + st, (it / STAGES) & 1, ab, kAbortKvFull)) break;
+        FPROF_ACC(a_w2, ta2);
+        tc_fence_after();
+        FPROF_T0(ta3);
+        const uint32_t aK = smem_u32(sKV + st * (C::N_KV * C::KV_BYTES)) + C::SLOT_K * C::KV_BYTES;
+        if constexpr (DUAL) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)  // [S | tS] = Q [K ; tK]^T
+            umma_ss(tmem + C::COL_S, make_smem_desc(aQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
+                    idesc_s2, ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)  // tS += tQ K^T
+            umma_ss(tmem + C::COL_TS, make_smem_desc(aTQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
+                    idesc_s, 1);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)
+            umma_ss(tmem + C::COL_S, make_smem_desc(aQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
+                    idesc_s, ks > 0);
+        }
+        tc_commit(s_full);
+        FPROF_ACC(a_is, ta3);
+      }
+#ifdef JVPFA_TC5_PROFILE
+      atomicAdd(&g_fprof[0], (unsigned long long)(clock64() - a_t0));
+      atomicAdd(&g_fprof[1], (unsigned long long)a_w1);
+      atomicAdd(&g_fprof[2], (unsigned long long)a_w2);
+      atomicAdd(&g_fprof[3], (unsigned long long)a_is);
+      atomicAdd(&g_fprof[4], (unsigned long long)n_tiles);
+#endif
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ issuer B: outputs
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_o = make_idesc(Fmt<T>::kIdesc, BM, D, 0, 1);       // 128 x 64, B MN-major
+      constexpr uint32_t idesc_o2 = make_idesc(Fmt<T>::kIdesc, BM, 2 * D, 0, 1);  // 128 x 128: [O | tO']
+#ifdef JVPFA_TC5_PROFILE
+      long long b_w = 0, b_is = 0;
+      const long long b_t0 = clock64();
+#endif
+      for (int it = 0; it < n_tiles; ++it) {
+        const int st = it % STAGES;
+        FPROF_T0(tb1);
+        if (!mbar_wait(p_full, it & 1, ab, kAbortPFull)) break;
+        FPROF_ACC(b_w, tb1);
+        tc_fence_after();
+        FPROF_T0(tb2);
+        const uint32_t aV = smem_u32(sKV + st * (C::N_KV * C::KV_BYTES)) + C::SLOT_V * C::KV_BYTES;
+        if constexpr (DUAL) {
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)  // [O | tO'] += P [V | tV]   (64-column chunks KV_BYTES apart)
+            umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
+                    idesc_o2, (it > 0 || kk > 0));
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)  // tO' += W V
+            umma_ts(tmem + C::COL_TO, tmem + C::COL_TS + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
+                    idesc_o, 1);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
+                    idesc_o, (it > 0 || kk > 0));
+        }
+        tc_commit(kv_empty + st);
+        FPROF_ACC(b_is, tb2);
+      }
+      tc_commit(o_full);
+#ifdef JVPFA_TC5_PROFILE
+      atomicAdd(&g_fprof[8], (unsigned long long)(clock64() - b_t0));
+      atomicAdd(&g_fprof[9], (unsigned long long)b_w);
+      atomicAdd(&g_fprof[10], (unsigned long long)b_is);
+#endif
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int i = m0 + row;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_off + C::COL_S, tTS = tmem + lane_off + C::COL_TS;
+    const uint32_t tO = tmem + lane_off + C::COL_O, tTO = tmem + lane_off + C::COL_TO;
+    const float scale_log2 = a.sm_scale * kLog2e;
+    const float2 c2 = make_float2(scale_log2, scale_log2);
+    const float2 sc2 = make_float2(a.sm_scale, a.sm_scale);
+    float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
+    bool alive = true;
+
+#ifdef JVPFA_TC5_PROFILE
+    long long s_w = 0, s_ld = 0, s_mx = 0, s_ex = 0, s_ts = 0, s_st = 0;
+    const long long s_t0 = clock64();
+#endif
+    for (int it = 0; it < n_tiles; ++it) {
+      const int n0 = it * BN;
+      FPROF_T0(ts0);
+      if (!mbar_wait(s_full, it & 1, ab, kAbortSFull)) {
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+#ifdef JVPFA_EXP_SKIP_SOFTMAX
+      tc_fence_before();
+      mbar_arrive(p_full);
+      l_run = 1.f;
+      continue;
+#endif
+      FPROF_ACC(s_w, ts0);
+      FPROF_T0(ts1);
+      uint32_t x0[32], x1[32];
+      tmem_ld32(tS, x0);
+      tmem_ld32(tS + 32, x1);
+      tmem_wait_ld();
+      FPROF_ACC(s_ld, ts1);
+      FPROF_T0(ts2);
+      // live key columns of this row inside the tile: col < col_hi
+      int col_hi = min(BN, n_valid - n0);
+      if (causal) col_hi = min(col_hi, i - n0 + 1);
+      const bool partial = (n0 + BN > n_valid) || (causal && n0 + BN - 1 > m0);
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        float2 v0 = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), c2);
+        float2 v1 = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), c2);
+        if (partial) {
+          if (2 * c >= col_hi) v0.x = -INFINITY;
+          if (2 * c + 1 >= col_hi) v0.y = -INFINITY;
+          if (32 + 2 * c >= col_hi) v1.x = -INFINITY;
+          if (33 + 2 * c >= col_hi) v1.y = -INFINITY;
+        }
+        x0[2 * c] = __float_as_uint(v0.x), x0[2 * c + 1] = __float_as_uint(v0.y);
+        x1[2 * c] = __float_as_uint(v1.x), x1[2 * c + 1] = __float_as_uint(v1.y);
+        mx0 = fmaxf(mx0, v0.x), mx1 = fmaxf(mx1, v0.y), mx2 = fmaxf(mx2, v1.x), mx3 = fmaxf(mx3, v1.y);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // Lazy running max: keep the old reference while the new maximum is at most 2^8 above it.
+      const bool grow = mx > m_used + 8.f;
+      float alpha = 1.f;
+      if (grow) {
+        alpha = fast_exp2(m_used - mx);
+        m_used = mx;
+      }
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      if (it > 0 && __any_sync(0xffffffffu, grow)) {
+        const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + 32 * c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float2 v = __fmul2_rn(ff2(r[2 * e], r[2 * e + 1]), al2);
+            r[2 * e] = __float_as_uint(v.x), r[2 * e + 1] = __float_as_uint(v.y);
+          }
+          tmem_st32(tO + 32 * c, r);
+          if constexpr (DUAL) {
+            tmem_ld32(tTO + 32 * c, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float2 v = __fmul2_rn(ff2(r[2 * e], r[2 * e + 1]), al2);
+              r[2 * e] = __float_as_uint(v.x), r[2 * e + 1] = __float_as_uint(v.y);
+            }
+            tmem_st32(tTO + 32 * c, r);
+          }
+        }
+      }
+      FPROF_ACC(s_mx, ts2);
+      FPROF_T0(ts3);
+      const float2 nm2 = make_float2(-m_eff, -m_eff);
+      float2 ls2a = make_float2(0.f, 0.f), ls2b = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const float2 e0 = __fadd2_rn(ff2(x0[2 * c], x0[2 * c + 1]), nm2);
+        const float2 e1 = __fadd2_rn(ff2(x1[2 * c], x1[2 * c + 1]), nm2);
+        const float2 p0 = make_float2(fast_exp2(e0.x), fast_exp2(e0.y));
+        const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
+        x0[2 * c] = __float_as_uint(p0.x), x0[2 * c + 1] = __float_as_uint(p0.y);
+        x1[2 * c] = __float_as_uint(p1.x), x1[2 * c + 1] = __float_as_uint(p1.y);
+        ls2a = __fadd2_rn(ls2a, p0);
+        ls2b = __fadd2_rn(ls2b, p1);
+      }
+      l_run = l_run * alpha + ((ls2a.x + ls2a.y) + (ls2b.x + ls2b.y));
+      FPROF_ACC(s_ex, ts3);
+      FPROF_T0(ts4);
+      if constexpr (DUAL) {
+        float2 ms2a = make_float2(0.f, 0.f), ms2b = make_float2(0.f, 0.f);
+        uint32_t t[32];
+        uint32_t wp[16];
+        tmem_ld32(tTS, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float2 w = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), __fmul2_rn(ff2(t[2 * c], t[2 * c + 1]), sc2));
+          ms2a = __fadd2_rn(ms2a, w);
+          wp[c] = Elem<T>::pack(w.x, w.y);
+        }
+        tmem_ld32(tTS + 32, t);  // second half is read before the first packed half is written below
+        tmem_wait_ld();
+        tmem_st16(tTS, wp);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float2 w = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), __fmul2_rn(ff2(t[2 * c], t[2 * c + 1]), sc2));
+          ms2b = __fadd2_rn(ms2b, w);
+          wp[c] = Elem<T>::pack(w.x, w.y);
+        }
+        tmem_st16(tTS + 16, wp);
+        mu_run = mu_run * alpha + ((ms2a.x + ms2a.y) + (ms2b.x + ms2b.y));
+      }
+      FPROF_ACC(s_ts, ts4);
+      FPROF_T0(ts5);
+      {
+        uint32_t pp[32];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          pp[c] = Elem<T>::pack(__uint_as_float(x0[2 * c]), __uint_as_float(x0[2 * c + 1]));
+          pp[16 + c] = Elem<T>::pack(__uint_as_float(x1[2 * c]), __uint_as_float(x1[2 * c + 1]));
+        }
+        tmem_st32(tS, pp);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+      FPROF_ACC(s_st, ts5);
+    }
+#ifdef JVPFA_TC5_PROFILE
+    if (row == 0) {
+      atomicAdd(&g_fprof[16], (unsigned long long)(clock64() - s_t0));
+      atomicAdd(&g_fprof[17], (unsigned long long)s_w);
+      atomicAdd(&g_fprof[18], (unsigned long long)s_ld);
+      atomicAdd(&g_fprof[19], (unsigned long long)s_mx);
+      atomicAdd(&g_fprof[20], (unsigned long long)s_ex);
+      atomicAdd(&g_fprof[21], (unsigned long long)s_ts);
+      atomicAdd(&g_fprof[22], (unsigned long long)s_st);
+    }
+#endif
+
+    // ---- epilogue ----
+    if (alive && n_tiles > 0) alive = mbar_wait(o_full, 0, ab, kAbortOFull);
+    if (alive) {
+      tc_fence_after();
+      const bool empty = !(l_run > 0.f);
+      const float inv_l = empty ? 0.f : 1.f / l_run;
+      const float mu_n = mu_run * inv_l;
+      const bool in_range = i < L;
+      if (in_range) {
+        a.lse[(size_t)bh * L + i] = empty ? INFINITY : (m_used + log2f(l_run));
+        if constexpr (DUAL) a.mu[(size_t)bh * L + i] = mu_n;
+      }
+      T* gO = reinterpret_cast<T*>(a.o) + ((size_t)bh * L + i) * D;
+      T* gTO = DUAL ? reinterpret_cast<T*>(a.to) + ((size_t)bh * L + i) * D : nullptr;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ro[32];
+        uint32_t po[16];
+        if (n_tiles > 0) {
+          tmem_ld32(tO + 32 * c, ro);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ro[e] = 0u;
+        }
+#pragma unroll
+        for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * inv_l);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) po[e] = Elem<T>::pack(__uint_as_float(ro[2 * e]), __uint_as_float(ro[2 * e + 1]));
+        if (in_range) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            reinterpret_cast<uint4*>(gO + 32 * c)[e] = make_uint4(po[4 * e], po[4 * e + 1], po[4 * e + 2], po[4 * e + 3]);
+        }
+        if constexpr (DUAL) {
+          uint32_t rt[32];
+          if (n_tiles > 0) {
+            tmem_ld32(tTO + 32 * c, rt);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) rt[e] = 0u;
+          }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float t0 = __uint_as_float(rt[2 * e]) * inv_l - mu_n * __uint_as_float(ro[2 * e]);
+            const float t1 = __uint_as_float(rt[2 * e + 1]) * inv_l - mu_n * __uint_as_float(ro[2 * e + 1]);
+            po[e] = Elem<T>::pack(t0, t1);
+          }
+          if (in_range) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              reinterpret_cast<uint4*>(gTO + 32 * c)[e] =
+                  make_uint4(po[4 * e], po[4 * e + 1], po[4 * e + 2], po[4 * e + 3]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    if (*abort_flag != 0) {
+      const long long t0 = clock64();
+      while (clock64() - t0 < (1ll << 22)) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem, C::COLS_ALLOC);
+  }
+}
+
+template <typename T, bool DUAL>
+static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
+  using C = Fwd64Cfg<DUAL>;
+  int* status = tc5_status_device_ptr();
+  if (!status) {
+    set_last_cuda_error(cudaErrorUnknown, "status word address");
+    return JVPFA_ERR_CUDA;
+  }
+  Fwd64Maps maps;
+  const long long BH = (long long)a.B * a.H;
+  const CUtensorMapDataType dt = Fmt<T>::kTma;
+  bool ok = encode_map(&maps.q, dt, a.q, 64, a.L, BH, C::BM) && encode_map(&maps.k, dt, a.k, 64, a.L, BH, C::BN) &&
+            encode_map(&maps.v, dt, a.v, 64, a.L, BH, C::BN);
+  if (DUAL)
+    ok = ok && encode_map(&maps.tq, dt, a.tq, 64, a.L, BH, C::BM) && encode_map(&maps.tk, dt, a.tk, 64, a.L, BH, C::BN) &&
+         encode_map(&maps.tv, dt, a.tv, 64, a.L, BH, C::BN);
+  else
+    maps.tq = maps.tk = maps.tv = maps.q;
+  if (!ok) {
+    set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(fwd d64)");
+    return JVPFA_ERR_CUDA;
+  }
+  auto kern = fwd_tc5_d64_kernel<T, DUAL>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "cudaFuncSetAttribute(fwd_tc5_d64)");
+    return JVPFA_ERR_CUDA;
+  }
+  dim3 grid((a.L + C::BM - 1) / C::BM, a.B * a.H);
+  kern<<<grid, C::NTHREADS, C::SMEM_BYTES, stream>>>(a, maps, status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "launch fwd_tc5_d64");
+    return JVPFA_ERR_CUDA;
+  }
+  return JVPFA_OK;
+}
+
+}  // namespace tc5
+
+#ifdef JVPFA_TC5_PROFILE
+extern "C" int jvpfa_debug_read_fprof(unsigned long long* out, int clear) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, tc5::g_fprof, sizeof(unsigned long long) * 32);
+  if (clear) {
+    unsigned long long z[32] = {};
+    cudaMemcpyToSymbol(tc5::g_fprof, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
+int launch_fwd_tc5_d64(const jvpfa_fwd_args& a, cudaStream_t s) {
+  const bool dual = a.tq != nullptr;
+  if (a.dtype == JVPFA_BF16)
+    return dual ? tc5::launch_fwd64<__nv_bfloat16, true>(a, s) : tc5::launch_fwd64<__nv_bfloat16, false>(a, s);
+  return dual ? tc5::launch_fwd64<__half, true>(a, s) : tc5::launch_fwd64<__half, false>(a, s);
+}
+
+}  // namespace jvpfa

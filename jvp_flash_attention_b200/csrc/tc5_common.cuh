@@ -94,13 +94,18 @@ struct AbortState {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortState& ab, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  int polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*ab.cta_flag != 0) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
-      *ab.cta_flag = code;
-      atomicCAS(ab.global_status, 0, code);
-      return false;
+    // Plain polling: a measured mbarrier hand-off between two warps costs ~200 cycles and any
+    // sleep here adds directly to it.  The clock and the abort flag are looked at every 64 polls.
+    if ((++polls & 63) == 0) {
+      if (*ab.cta_flag != 0) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *ab.cta_flag = code;
+        atomicCAS(ab.global_status, 0, code);
+        return false;
+      }
     }
   }
 }
