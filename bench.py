@@ -180,10 +180,14 @@ def run_ours(args, rank, world, local):
     def k_fwd():
         _lib.fwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], o, to, lse, mu, spec, scale)
 
+    diff = torch.empty_like(d["q"])
+
     def k_loss():
-        diff = to.float() - d["target"].float()
-        loss_buf.copy_((diff * diff).mean())
-        gto.copy_(diff * (2.0 / n_el))
+        # loss = mean((tO - target)^2) and its gradient w.r.t. tO; user-side torch ops, kept in
+        # the compute dtype so that they stay a small part of the step
+        torch.sub(to, d["target"], out=diff)
+        loss_buf.copy_(torch.linalg.vector_norm(diff, dtype=torch.float32).square() / n_el)
+        torch.mul(diff, 2.0 / n_el, out=gto)
 
     def k_pre():
         _lib.bwd_preprocess(o, to, None, gto, mu, stats[0], stats[1], stats[2])
@@ -317,10 +321,10 @@ def run_ours(args, rank, world, local):
         n_pairs = w.attended_pairs()
         mma = 2.0 * D * n_pairs  # flops of one L x L x D product over the attended pairs
         kernels = [
-            {"name": "fwd_tc5_kernel (fwd_dual)", "ms": br["fwd_dual"], "mma_executed": 6, "mma_algorithmic": 6},
-            {"name": "bwd_tc5_kernel<own keys> (dK,dV)", "ms": br["bwd_dkdv_only"], "mma_executed": 8,
+            {"name": "fwd_tc5_d64_kernel (fwd_dual)", "ms": br["fwd_dual"], "mma_executed": 6, "mma_algorithmic": 6},
+            {"name": "bwd_tc5_d64_kernel<own keys> (dK,dV)", "ms": br["bwd_dkdv_only"], "mma_executed": 8,
              "mma_algorithmic": None},
-            {"name": "bwd_tc5_kernel<own queries> (dQ)", "ms": br["bwd_dq_only"], "mma_executed": 7,
+            {"name": "bwd_tc5_d64_kernel<own queries> (dQ)", "ms": br["bwd_dq_only"], "mma_executed": 7,
              "mma_algorithmic": None},
             {"name": "pre_kernel (HBM bound)", "ms": br["bwd_preprocess"],
              "gbs": (3 * n_el * 2 + 4 * B * H * L * 4) / (br["bwd_preprocess"] * 1e-3) / 1e9,
@@ -345,8 +349,8 @@ def run_ours(args, rank, world, local):
                     "path": "torch.func.jvp(JVPAttn.fwd_dual) + autograd.grad; pinned host inputs, double-buffered H2D"},
             "gpu_launches": 4 * args.steps,
             "roofline": {"bound": "tensor",
-                         "kernel": "jvpfa_fwd (fwd_tc5_kernel)" if dom == "fwd_dual" else
-                         "jvpfa_bwd (bwd_tc5_kernel own-keys + own-queries launches, timed as one call; "
+                         "kernel": "jvpfa_fwd (fwd_tc5_d64_kernel)" if dom == "fwd_dual" else
+                         "jvpfa_bwd (bwd_tc5_d64_kernel own-keys + own-queries launches, timed as one call; "
                          "10 algorithmic MMAs, 15 executed because both launches recompute the score tiles)",
                          "achieved": ach, "peak": peaks["burst"],
                          "unit": "TFLOP/s", "frac": ach / peaks["burst"], "traffic": None,
