@@ -123,6 +123,7 @@ def run_reference(args, rank, world):
         return
     steps = max(1, min(args.steps, 3))
     warm = 1 if args.warmup > 0 else 0
+    torch.set_num_threads(max(1, os.cpu_count() or 1))  # torchrun pins OMP_NUM_THREADS=1; use every host core
     tf, sec, sample = _cpu_reference(args.workload, steps, warm)
     cores = torch.get_num_threads()
     line = {

@@ -256,12 +256,6 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         break;
       }
       tc_fence_after();
-#ifdef JVPFA_EXP_SKIP_SOFTMAX
-      tc_fence_before();
-      mbar_arrive(p_full);
-      l_run = 1.f;
-      continue;
-#endif
       FPROF_ACC(s_w, ts0);
       FPROF_T0(ts1);
       uint32_t x0[32], x1[32];
@@ -520,6 +514,7 @@ extern "C" int jvpfa_debug_read_fprof(unsigned long long* out, int clear) {
 
 int launch_fwd_tc5_d64(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
+  if (!dual) return launch_fwd_tc5_sub32(a, s);  // primal only: 32-key sub-tile pipeline (fwd_tc5_sub32.cu)
   if (a.dtype == JVPFA_BF16)
     return dual ? tc5::launch_fwd64<__nv_bfloat16, true>(a, s) : tc5::launch_fwd64<__nv_bfloat16, false>(a, s);
   return dual ? tc5::launch_fwd64<__half, true>(a, s) : tc5::launch_fwd64<__half, false>(a, s);
