@@ -67,7 +67,7 @@ struct Bwd64Cfg {
 
 #ifdef JVPFA_TC5_PROFILE
 // Experiment-only cycle counters (summed over CTAs).
-__device__ unsigned long long g_prof[32];
+__device__ unsigned long long g_prof[64];
 #define PROF_T0(v) long long v = clock64()
 #define PROF_ACC(var, v) var += clock64() - (v)
 #else
@@ -84,6 +84,9 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   constexpr int D = 64, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES;
 
   if (*(volatile int*)status != 0) return;
+#ifdef JVPFA_TC5_PROFILE
+  const long long t_cta0 = clock64();
+#endif
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -126,6 +129,39 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   const size_t stat_off = (size_t)bh * L;
   const size_t head_off = (size_t)bh * L * D;
 
+  // Elementwise threads fetch their rows of the own operand tiles right away, so that the global
+  // load latency overlaps the barrier / TMEM set-up below (group g takes the slots of parity g).
+  uint32_t own_r[2][32];
+  if (warp >= 4 && n_sub > 0) {
+    const int wg_ = (warp - 4) >> 2;
+    const int own_idx_ = own0 + (warp & 3) * 32 + lane;
+    const void* own_src[4] = {nullptr, nullptr, nullptr, nullptr};
+    if constexpr (OWN_KEYS) {
+      own_src[C::SLOT_K] = a.k, own_src[C::SLOT_V] = a.v;
+      if constexpr (HAS_GT) own_src[C::SLOT_TK] = a.tk, own_src[C::SLOT_TV] = a.tv;
+    } else {
+      own_src[C::SLOT_Q] = a.q;
+      if constexpr (HAS_GO) own_src[C::SLOT_GO] = a.go;
+      if constexpr (HAS_GT) own_src[C::SLOT_TQ] = a.tq, own_src[C::SLOT_G] = a.gto;
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int slot = 2 * j + wg_;
+      if (slot < C::N_OWN && own_idx_ < L) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(own_src[slot]) + head_off +
+                                                          (size_t)own_idx_ * D);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const uint4 v = __ldg(src + x);
+          own_r[j][4 * x] = v.x, own_r[j][4 * x + 1] = v.y, own_r[j][4 * x + 2] = v.z, own_r[j][4 * x + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) own_r[j][x] = 0u;
+      }
+    }
+  }
+
   if (tid == 0) {
     mbar_init(own_ready, 256);
     for (int s = 0; s < STAGES; ++s) {
@@ -152,6 +188,16 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (+ stats)
+    if (lane == 0) {
+      if constexpr (OWN_KEYS) {
+        prefetch_tmap(&maps.q);
+        if constexpr (HAS_GO) prefetch_tmap(&maps.go);
+        if constexpr (HAS_GT) prefetch_tmap(&maps.tq), prefetch_tmap(&maps.g);
+      } else {
+        prefetch_tmap(&maps.k), prefetch_tmap(&maps.v);
+        if constexpr (HAS_GT) prefetch_tmap(&maps.tk), prefetch_tmap(&maps.tv);
+      }
+    }
     for (int s = 0; s < n_sub; ++s) {
       const int st = s % STAGES;
       const uint32_t ph = (s / STAGES) & 1;
@@ -362,40 +408,25 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     const uint32_t tbase = tmem + lane_off;
     const uint32_t tbuf = tbase + wg * C::COL_BUF;
     bool alive = true;
+#ifdef JVPFA_TC5_PROFILE
+    const long long tl_sync = clock64() - t_cta0;
+    long long tl_own = 0, tl_first = 0, tl_loop = 0, tl_done = 0, tl_end = 0;
+#endif
 
-    // ---- own operand rows: global memory -> TMEM (packed 16-bit, 32 columns per operand) ----
+    // ---- own operand rows (already in registers) -> TMEM: packed 16-bit, 32 columns per operand ----
     if (n_sub > 0) {
-      const void* own_src[4] = {nullptr, nullptr, nullptr, nullptr};
-      if constexpr (OWN_KEYS) {
-        own_src[C::SLOT_K] = a.k, own_src[C::SLOT_V] = a.v;
-        if constexpr (HAS_GT) own_src[C::SLOT_TK] = a.tk, own_src[C::SLOT_TV] = a.tv;
-      } else {
-        own_src[C::SLOT_Q] = a.q;
-        if constexpr (HAS_GO) own_src[C::SLOT_GO] = a.go;
-        if constexpr (HAS_GT) own_src[C::SLOT_TQ] = a.tq, own_src[C::SLOT_G] = a.gto;
-      }
 #pragma unroll
-      for (int slot = 0; slot < C::N_OWN; ++slot) {
-        if ((slot & 1) != wg) continue;
-        uint32_t r[32];
-        if (own_idx < L) {
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(own_src[slot]) + head_off +
-                                                            (size_t)own_idx * D);
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const uint4 v = __ldg(src + x);
-            r[4 * x] = v.x, r[4 * x + 1] = v.y, r[4 * x + 2] = v.z, r[4 * x + 3] = v.w;
-          }
-        } else {
-#pragma unroll
-          for (int x = 0; x < 32; ++x) r[x] = 0u;
-        }
-        tmem_st32(tbase + C::COL_OWN + slot * 32, r);
+      for (int j = 0; j < 2; ++j) {
+        const int slot = 2 * j + wg;
+        if (slot < C::N_OWN) tmem_st32(tbase + C::COL_OWN + slot * 32, own_r[j]);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(own_ready);
     }
+#ifdef JVPFA_TC5_PROFILE
+    tl_own = clock64() - t_cta0;
+#endif
 
     // own-queries variant: row statistics, negated
     float r_nlse = -INFINITY, r_nmu = 0.f, r_neps = 0.f, r_nsub = 0.f;
@@ -434,6 +465,9 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         break;
       }
       tc_fence_after();
+#ifdef JVPFA_TC5_PROFILE
+      if (s == wg) tl_first = clock64() - t_cta0;
+#endif
       PROF_ACC(e_wait, te0);
       PROF_T0(te1);
       // Masking by index comparison; columns outside [col_lo, col_hi) get p = 0.
@@ -523,8 +557,14 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     }
 #endif
 
+#ifdef JVPFA_TC5_PROFILE
+    tl_loop = clock64() - t_cta0;
+#endif
     // ---- epilogue: group 0 stores columns [0,32) of every output, group 1 columns [32,64) ----
     if (alive && n_sub > 0) alive = mbar_wait(done, 0, ab, kAbortBwdDone);
+#ifdef JVPFA_TC5_PROFILE
+    tl_done = clock64() - t_cta0;
+#endif
     if (alive) {
       tc_fence_after();
       const bool in_range = own_idx < L;
@@ -554,8 +594,27 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         store_half(a.dq, C::COL_OUT0, a.sm_scale);
       }
     }
+#ifdef JVPFA_TC5_PROFILE
+    tl_end = clock64() - t_cta0;
+    if (row == 0 && wg == 0 && n_sub > 0) {
+      const int o = OWN_KEYS ? 32 : 48;
+      atomicAdd(&g_prof[o + 0], (unsigned long long)tl_sync);
+      atomicAdd(&g_prof[o + 1], (unsigned long long)tl_own);
+      atomicAdd(&g_prof[o + 2], (unsigned long long)tl_first);
+      atomicAdd(&g_prof[o + 3], (unsigned long long)tl_loop);
+      atomicAdd(&g_prof[o + 4], (unsigned long long)tl_done);
+      atomicAdd(&g_prof[o + 5], (unsigned long long)tl_end);
+      atomicAdd(&g_prof[o + 7], 1ull);
+    }
+#endif
   }
 
+#ifdef JVPFA_TC5_PROFILE
+  if (warp == 4 && lane == 0 && n_sub > 0) {
+    const int o = OWN_KEYS ? 32 : 48;
+    atomicAdd(&g_prof[o + 6], (unsigned long long)(clock64() - t_cta0));
+  }
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
@@ -636,9 +695,9 @@ static int launch_t64(const jvpfa_bwd_args& a, cudaStream_t s) {
 #ifdef JVPFA_TC5_PROFILE
 extern "C" int jvpfa_debug_read_prof(unsigned long long* out, int clear) {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, tc5::g_prof, sizeof(unsigned long long) * 32);
+  cudaMemcpyFromSymbol(out, tc5::g_prof, sizeof(unsigned long long) * 64);
   if (clear) {
-    unsigned long long z[32] = {};
+    unsigned long long z[64] = {};
     cudaMemcpyToSymbol(tc5::g_prof, z, sizeof(z));
   }
   return 0;
