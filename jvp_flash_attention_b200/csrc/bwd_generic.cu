@@ -170,15 +170,45 @@ template <typename T, int D, int KROWS>
 __device__ __forceinline__ void gemm_acc_nn(float (*out)[4], const float (*atile)[4], const T* sB, int ld,
                                             int lane) {
   constexpr int KS = Elem<T>::kKStep;
+  if constexpr (Elem<T>::k16) {
 #pragma unroll
-  for (int kk = 0; kk < KROWS / KS; ++kk) {
-    FragA<T> fa;
-    a_from_acc<T>(fa, atile, kk);
+    for (int kk = 0; kk < KROWS / KS; ++kk) {
+      FragA<T> fa;
+      a_from_acc<T>(fa, atile, kk);
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) {
-      FragB<T> fb;
-      load_b_nn<T>(fb, sB, ld, kk * KS, dt * 8, lane);
-      mma<T>(out[dt], fa, fb);
+      for (int dt = 0; dt < D / 8; ++dt) {
+        FragB<T> fb;
+        load_b_nn<T>(fb, sB, ld, kk * KS, dt * 8, lane);
+        mma<T>(out[dt], fa, fb);
+      }
+    }
+  } else {
+    // fp32: the tensor core adds into its fp32 accumulator with truncation, and hundreds of such
+    // adds into one long-lived accumulator show up as a bias of ~1e-5.  Accumulate this tile's
+    // contribution in a fresh register tile (32 columns at a time) and add it once, rounded.
+#pragma unroll
+    for (int d0 = 0; d0 < D / 8; d0 += 4) {
+      float tmp[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tmp[i][0] = tmp[i][1] = tmp[i][2] = tmp[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KROWS / KS; ++kk) {
+        FragA<T> fa;
+        a_from_acc<T>(fa, atile, kk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          FragB<T> fb;
+          load_b_nn<T>(fb, sB, ld, kk * KS, (d0 + i) * 8, lane);
+          mma<T>(tmp[i], fa, fb);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        out[d0 + i][0] += tmp[i][0];
+        out[d0 + i][1] += tmp[i][1];
+        out[d0 + i][2] += tmp[i][2];
+        out[d0 + i][3] += tmp[i][3];
+      }
     }
   }
 }

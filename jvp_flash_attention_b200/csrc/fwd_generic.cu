@@ -209,21 +209,62 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const jvpfa_fwd_args a
     }
 
     // ---- second MMAs: contraction over the keys of this tile ----
+    if constexpr (Elem<T>::k16) {
 #pragma unroll
-    for (int kk = 0; kk < BN / KS; ++kk) {
-      FragA<T> fp, fw;
-      a_from_acc<T>(fp, s, kk);
-      if constexpr (DUAL) a_from_acc<T>(fw, ts, kk);
+      for (int kk = 0; kk < BN / KS; ++kk) {
+        FragA<T> fp, fw;
+        a_from_acc<T>(fp, s, kk);
+        if constexpr (DUAL) a_from_acc<T>(fw, ts, kk);
 #pragma unroll
-      for (int dt = 0; dt < ND; ++dt) {
-        FragB<T> fv;
-        load_b_nn<T>(fv, sV, LD, kk * KS, dt * 8, lane);
-        mma<T>(acc_o[dt], fp, fv);
-        if constexpr (DUAL) {
-          FragB<T> ftv;
-          load_b_nn<T>(ftv, sTV, LD, kk * KS, dt * 8, lane);
-          mma<T>(acc_t[dt], fw, fv);
-          mma<T>(acc_t[dt], fp, ftv);
+        for (int dt = 0; dt < ND; ++dt) {
+          FragB<T> fv;
+          load_b_nn<T>(fv, sV, LD, kk * KS, dt * 8, lane);
+          mma<T>(acc_o[dt], fp, fv);
+          if constexpr (DUAL) {
+            FragB<T> ftv;
+            load_b_nn<T>(ftv, sTV, LD, kk * KS, dt * 8, lane);
+            mma<T>(acc_t[dt], fw, fv);
+            mma<T>(acc_t[dt], fp, ftv);
+          }
+        }
+      }
+    } else {
+      // fp32: the tensor core adds into its fp32 accumulator with truncation; over a thousand keys
+      // that bias reaches ~1e-5.  This tile's contribution is therefore accumulated in a fresh
+      // register tile (32 output columns at a time) and added to the running sums once, rounded.
+#pragma unroll
+      for (int d0 = 0; d0 < ND; d0 += 4) {
+        float to_[4][4], tt_[DUAL ? 4 : 1][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          to_[i][0] = to_[i][1] = to_[i][2] = to_[i][3] = 0.f;
+          if constexpr (DUAL) tt_[i][0] = tt_[i][1] = tt_[i][2] = tt_[i][3] = 0.f;
+        }
+#pragma unroll
+        for (int kk = 0; kk < BN / KS; ++kk) {
+          FragA<T> fp, fw;
+          a_from_acc<T>(fp, s, kk);
+          if constexpr (DUAL) a_from_acc<T>(fw, ts, kk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            FragB<T> fv;
+            load_b_nn<T>(fv, sV, LD, kk * KS, (d0 + i) * 8, lane);
+            mma<T>(to_[i], fp, fv);
+            if constexpr (DUAL) {
+              FragB<T> ftv;
+              load_b_nn<T>(ftv, sTV, LD, kk * KS, (d0 + i) * 8, lane);
+              mma<T>(tt_[i], fw, fv);
+              mma<T>(tt_[i], fp, ftv);
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc_o[d0 + i][e] += to_[i][e];
+            if constexpr (DUAL) acc_t[d0 + i][e] += tt_[i][e];
+          }
         }
       }
     }

@@ -450,3 +450,48 @@ def test_library_rejects_bad_arguments_without_launching():
     a.mask.kind = _lib.MASK_BOOL
     assert lib.jvpfa_fwd(C.byref(a), None) == -4  # mask without pointer
     assert b"mask" in lib.jvpfa_strerror(-4)
+
+
+def test_config4_full_size_bias_hvp_sampled_heads():
+    """fp32 B2 H8 L1024 D128 with a (B,H,L,L) bias: primal + tangent forward and the Hessian-vector
+    product d/dq <d/dq sum(O*w), v_dir>; two (batch, head) slices against the float64 oracle."""
+    w = workloads.make_workload("c4_fp32_bias_hvp")
+    c = w.tensors
+    dev = "cuda:0"
+    d = {k_: v_.to(dev) for k_, v_ in c.items()}
+    o, to = torch.func.jvp(lambda q_, k_, v_: ja.JVPAttn.fwd_dual(q_, k_, v_, attn_mask=d["mask"]),
+                           (d["q"], d["k"], d["v"]), (d["tq"], d["tk"], d["tv"]))
+    q1 = d["q"].clone().requires_grad_()
+    o1 = ja.attention(q1, d["k"], d["v"], attn_mask=d["mask"])
+    (g1,) = torch.autograd.grad((o1 * d["w"]).sum(), q1, create_graph=True)
+    (h,) = torch.autograd.grad((g1 * d["v_dir"]).sum(), q1)
+    for (b, hh) in ((0, 0), (1, 7)):
+        sl = lambda x: x[b:b + 1, hh:hh + 1]  # noqa: E731
+        cc = {k_: sl(v_) for k_, v_ in c.items()}
+        ro, rto = orc.sdpa_jvp(cc["q"], cc["k"], cc["v"], cc["tq"], cc["tk"], cc["tv"], attn_mask=cc["mask"])
+        _, rg1, rh = orc.hvp_q(cc["q"], cc["k"], cc["v"], cc["w"], cc["v_dir"], attn_mask=cc["mask"])
+        _close(sl(o), ro, torch.float32, "O")
+        _close(sl(to), rto, torch.float32, "tO")
+        _close(sl(g1), rg1, torch.float32, "grad")
+        _close(sl(h), rh, torch.float32, "hvp")
+
+
+def test_config5_shard_long_sequence_sampled_head():
+    """bf16 L8192 D128 non-causal: the shard a rank would own (here 4 of the 512 (batch, head) units,
+    generated per head as on any rank), fwd_dual + backward through both outputs; head 0 against the
+    float64 oracle, and linearity of tO in the tangents on the whole shard."""
+    w = workloads.make_workload("c5_bf16_long", heads=(0, 4))
+    t = {k_: v_.to("cuda:0") for k_, v_ in w.tensors.items()}
+    a = [t[n].requires_grad_() for n in ("q", "k", "v")]
+    o, to = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a), (t["tq"], t["tk"], t["tv"]))
+    g = torch.autograd.grad((o.float() * t["w1"].float()).sum() + (to.float() * t["w2"].float()).sum(), a)
+    assert _lib.device_status() == 0
+    c = {k_: v_[:, :1] for k_, v_ in w.tensors.items()}
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], c["w1"], c["w2"])
+    _close(o[:, :1], ro, torch.bfloat16, "O")
+    _close(to[:, :1], rto, torch.bfloat16, "tO")
+    for x, r_, nme in zip(g, (rdq, rdk, rdv), ("dq", "dk", "dv")):
+        _close(x[:, :1], r_, torch.bfloat16, nme)
+    o2, to2 = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(x.detach() for x in a), (2 * t["tq"], 2 * t["tk"], 2 * t["tv"]))
+    assert torch.equal(o2, o.detach())
+    assert (to2.float() - 2 * to.detach().float()).abs().max().item() <= 2e-2
