@@ -3,37 +3,41 @@
 //
 // Same mathematics and the same two launches as bwd_tc5.cu (own 128 keys -> dK, dV; own 128
 // queries -> dQ), organised around what was measured on B200:
-//   (1) one thread issues a tcgen05.mma about every 58-70 cycles whatever N <= 64 is, several
+//   (1) one thread issues a tcgen05.mma about every 60-100 cycles whatever N <= 128 is, several
 //       issuing warps scale almost linearly;
-//   (2) with A operands read from shared memory, N <= 64 instructions are bound by the shared
-//       memory port, with A in TMEM they are not;
-//   (3) a hand-off through an mbarrier costs ~200 cycles (MMA -> commit -> waiter ~300);
-//   (4) a CTA that owns all of TMEM cannot overlap its start-up (~7000 cycles) and wind-down (~5000)
-//       with another CTA.
+//   (2) a hand-off through an mbarrier costs ~200 cycles (MMA -> commit -> waiter ~300), so the life
+//       of one 32-row sub-tile (scores -> elementwise -> second-stage MMAs -> accumulators free again)
+//       is ~2200-3300 cycles against ~500 cycles of tensor work: throughput = that latency divided
+//       by the number of sub-tiles in flight;
+//   (3) a CTA that owns all of TMEM cannot overlap its start-up and wind-down with another CTA.
 // Hence:
 //  * one CTA per SM stays resident and walks a static, weight-balanced list of work items
 //    (own tile, batch*head): barriers and TMEM are set up once, the TMA producer runs ahead across
-//    item boundaries, the next item's own tiles are staged in shared memory while the current item
-//    is still computing, and the previous item's outputs are converted and stored while the next
-//    item's first scores are already being formed;
-//  * the item's own operand tiles (K, V, tK, tV or Q, gO, tQ, G) are copied from the staging area into
-//    TMEM as packed 16-bit rows (32 columns each) and are the A operand of every score MMA;
-//  * the streamed side advances in sub-tiles of 32 rows; the four score accumulators of a sub-tile
-//    take 128 TMEM columns and exist twice (buffers 0 / 1);
+//    item boundaries, the next item's own tiles are fetched into the other half of a double-buffered
+//    staging area while the current item computes, and the previous item's outputs are converted
+//    and stored while the next item's first scores are already being formed;
+//  * three sub-tiles are in flight: the four score accumulators of a sub-tile take 128 TMEM columns
+//    and exist three times.  That leaves 128 columns: dK and dV (own keys), or dQ and the packed
+//    rows of Q and tQ as TMEM-resident A operands (own queries).  All other own-side operands are
+//    read from the staging area by shared-memory-descriptor MMAs;
+//  * the streamed side advances in sub-tiles of 32 rows through a TMA ring;
 //  * three warps issue MMAs, each owning fixed accumulator chains (listed at the issuer code); where
 //    two accumulators share the A operand and their B tiles are neighbours in shared memory
-//    ([Q;tQ], [K;tK], [V;tV]) one N=64 instruction fills both;
-//  * two elementwise warpgroups alternate over the sub-tiles (group g owns buffer g): they turn the
-//    accumulators into the 16-bit operands (P, A, gtS, gS, written back in place) with packed fp32x2
-//    arithmetic and selects instead of branches.
+//    ([Q;tQ], [K;tK], [V;tV]) one N=64 instruction fills both.  An issuer forms the scores of
+//    sub-tile g+2 before the second stage of sub-tile g, so it never waits for its own MMAs;
+//  * two elementwise warpgroups alternate over the sub-tiles: they turn the accumulators into the
+//    16-bit operands (P, A, gtS, gS, written back in place) with packed fp32x2 arithmetic and
+//    selects instead of branches.
 //
-// TMEM map (512 columns):  buffer g at 128*g: S | TS | E | FP (32 each) ; OUT0 at 256 (64) ;
-// OUT1 at 320 (64) ; own operand slots at 384 + 32*slot.
-// Sub-tiles are numbered globally over the CTA's items (index g): stage g % STAGES, buffer g & 1.
+// TMEM map (512 columns):  buffer b at 128*b: S | TS | E | FP (32 each), b = 0..2 ; OUT0 at 384
+// (64) ; own keys: OUT1 at 448 (64) ; own queries: packed Q at 448, tQ at 480.
+// Sub-tiles are numbered globally over the CTA's items (index g): stage g % STAGES, buffer g % 3,
+// elementwise group g & 1.
 // Barriers: loop_full/loop_empty[stage]; s_full[b] (one arrival per score issuer) -> elementwise;
 // p_full[b] (128 threads) -> second-stage issuers; loop_empty[stage] (one arrival per second-stage
-// issuer) also releases buffer b to the score issuers.  Per item: own_staged (TMA) -> elementwise;
-// own_ready (256 threads) -> issuers and producer; done (second-stage issuers) -> elementwise;
+// issuer) also releases buffer b to the score issuers.  Per item: own_staged[h] (TMA, staging half
+// h) -> issuers / elementwise; own_free[h] (256 threads) -> producer; own_ready (256 threads, own
+// queries only: packed rows are in TMEM) -> issuers; done (second-stage issuers) -> elementwise;
 // out_free (256 threads) -> second-stage issuers of the next item.
 #include "tc5_common.cuh"
 
@@ -51,29 +55,38 @@ struct Bwd64Cfg {
   static constexpr int D = 64;
   static constexpr int OWN = 128;
   static constexpr int BL = 32;
-  static constexpr int STAGES = 6;
-  static constexpr int NTHREADS = 384;  // producer warp, 3 issuer warps, 2 x 4 elementwise warps
-  static constexpr int N_SCORE_ISSUERS = (OWN_KEYS && HAS_GT) ? 3 : 2;
+  static constexpr int NBUF = 3;                                // sub-tiles in flight
+  static constexpr int STAGES = (HAS_GO && HAS_GT) ? 5 : 6;     // TMA ring depth (limited by shared memory)
+  // warp 0: TMA producer; warps 1, 2: score issuers (even / odd sub-tiles); warp 3: second-stage
+  // issuer (dK or dQ); warps 4..11: two elementwise warpgroups; warp 12 (own keys): second-stage
+  // issuer for dV
+  static constexpr int NTHREADS = OWN_KEYS ? 416 : 384;
   static constexpr int N_OUT_ISSUERS = OWN_KEYS ? 2 : 1;
+  // s_full barriers are indexed by g % 6: sub-tiles that share one have the same accumulator buffer
+  // (g % 3) and the same elementwise group (g & 1), so its waiter sees every phase.
+  static constexpr int N_SFULL = 6;
   static constexpr int N_KEY_TILES = HAS_GT ? 4 : 2;
   static constexpr int N_QRY_TILES = 1 + (HAS_GO ? 1 : 0) + (HAS_GT ? 2 : 0);
   static constexpr int N_OWN = OWN_KEYS ? N_KEY_TILES : N_QRY_TILES;
   static constexpr int N_LOOP = OWN_KEYS ? N_QRY_TILES : N_KEY_TILES;
+  static constexpr int N_OWN_TMEM = OWN_KEYS ? 0 : (HAS_GT ? 2 : 1);  // own queries: Q (, tQ) as TMEM operands
   static constexpr int LOOP_BYTES = BL * D * 2;  // 4 KiB
   static constexpr int OWN_BYTES = OWN * D * 2;  // 16 KiB
   static constexpr int STAGE_BYTES = N_LOOP * LOOP_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int STAGING_BYTES = N_OWN * OWN_BYTES;
+  static constexpr int STAGING_HALF = N_OWN * OWN_BYTES;
+  static constexpr int STAGING_BYTES = 2 * STAGING_HALF;
   static constexpr int STAT_BYTES = OWN_KEYS ? STAGES * (BL / 2) * 32 : 0;  // two float4 per column pair
   static constexpr int TILE_BYTES = RING_BYTES + STAGING_BYTES;
   // At least 120 KiB so that a second CTA can never share the SM (the CTA allocates all of TMEM).
   static constexpr int SMEM_NEEDED = TILE_BYTES + STAT_BYTES + 512 + 1024;
   static constexpr int SMEM_BYTES = SMEM_NEEDED > 120 * 1024 ? SMEM_NEEDED : 120 * 1024;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
   static constexpr int COL_BUF = 128;  // columns per accumulator buffer
   static constexpr int OFF_S = 0, OFF_TS = 32, OFF_E = 64, OFF_FP = HAS_GT ? 96 : 32;
-  static constexpr int COL_OUT0 = 256, COL_OUT1 = 320, COL_OWN = 384;
+  static constexpr int COL_OUT0 = NBUF * COL_BUF, COL_OUT1 = COL_OUT0 + 64, COL_OWN = COL_OUT0 + 64;
   static constexpr int COLS_ALLOC = 512;
-  // Tile slots (TMEM operand slots / staging tiles of the own side, ring tiles of the streamed side).
+  // Tile slots (staging tiles of the own side, ring tiles of the streamed side, TMEM operand slots).
   // K|tK, V|tV and Q|tQ are neighbours so that one N=64 instruction can take both as its B operand.
   static constexpr int SLOT_K = 0, SLOT_TK = 1, SLOT_V = HAS_GT ? 2 : 1, SLOT_TV = 3;
   static constexpr int SLOT_Q = 0, SLOT_TQ = 1, SLOT_G = 2, SLOT_GO = HAS_GT ? 3 : 1;
@@ -81,16 +94,29 @@ struct Bwd64Cfg {
 
 __device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
 
+#ifdef JVPFA_TC5_PROFILE
+// Event trace of CTA 0 (experiment flag): clock64 at fixed points of sub-tiles [G0, G0 + W).
+constexpr int kTraceG0 = 16, kTraceW = 24, kTraceEv = 20;
+__device__ long long g_bwd_trace[2][kTraceW * kTraceEv];
+#define TRACE(g, ev)                                                                 \
+  do {                                                                               \
+    if (blockIdx.x == 0 && (g) >= kTraceG0 && (g) < kTraceG0 + kTraceW)              \
+      g_bwd_trace[OWN_KEYS ? 0 : 1][((g) - kTraceG0) * kTraceEv + (ev)] = clock64(); \
+  } while (0)
+#else
+#define TRACE(g, ev)
+#endif
+
 // One work item of the persistent loop.
 struct BwdItem {
   int bh, b, own0, loop_begin, n_sub;
 };
 
 template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(416, 1)
 bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps maps, int* status) {
   using C = Bwd64Cfg<OWN_KEYS, HAS_GO, HAS_GT>;
-  constexpr int D = 64, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES;
+  constexpr int D = 64, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES, NBUF = C::NBUF;
 
   if (*(volatile int*)status != 0) return;
 
@@ -98,18 +124,19 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   unsigned char* sLoop = smem;
-  unsigned char* sOwn = smem + C::RING_BYTES;                        // staging of the next item's own tiles
+  unsigned char* sOwn = smem + C::RING_BYTES;                        // two halves of N_OWN tiles
   float4* sStat = reinterpret_cast<float4*>(smem + C::TILE_BYTES);  // [STAGES][BL/2][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::TILE_BYTES + C::STAT_BYTES);
   uint64_t* loop_full = bars;                // [STAGES]
   uint64_t* loop_empty = bars + STAGES;      // [STAGES]
-  uint64_t* s_full = bars + 2 * STAGES;      // [2]
-  uint64_t* p_full = s_full + 2;             // [2]
-  uint64_t* own_staged = s_full + 4;
-  uint64_t* own_ready = s_full + 5;
-  uint64_t* done = s_full + 6;
-  uint64_t* out_free = s_full + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
+  uint64_t* s_full = bars + 2 * STAGES;      // [N_SFULL]
+  uint64_t* p_full = s_full + C::N_SFULL;    // [NBUF]
+  uint64_t* own_staged = p_full + NBUF;      // [2]
+  uint64_t* own_free = own_staged + 2;       // [2]
+  uint64_t* own_ready = own_free + 2;
+  uint64_t* done = own_ready + 1;
+  uint64_t* out_free = done + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -147,6 +174,13 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     }
     return true;
   };
+  const int k_max = (n_items + G - 1) / G;
+  // Advances k to the next item that has work; false when the list is exhausted.
+  auto next_active = [&](int& k, BwdItem& it) -> bool {
+    for (; k < k_max; ++k)
+      if (get_item(k, it) && it.n_sub > 0) return true;
+    return false;
+  };
   auto valid_keys = [&](int b) {
     int n_valid = L;
     if (a.mask.kind == JVPFA_MASK_KVLEN) {
@@ -155,20 +189,21 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     }
     return n_valid;
   };
-  const int k_max = (n_items + G - 1) / G;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(loop_full + s, 1);
       mbar_init(loop_empty + s, C::N_OUT_ISSUERS);
     }
-    for (int g = 0; g < 2; ++g) {
-      mbar_init(s_full + g, C::N_SCORE_ISSUERS);
-      mbar_init(p_full + g, 128);
+    for (int b = 0; b < C::N_SFULL; ++b) mbar_init(s_full + b, 1);
+    for (int b = 0; b < NBUF; ++b) mbar_init(p_full + b, 128);
+    // The two score threads take part in one per-item barrier each (own_free or done, see below).
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(own_staged + h, 1);
+      mbar_init(own_free + h, 256 + (OWN_KEYS ? 2 : 0));
     }
-    mbar_init(own_staged, 1);
     mbar_init(own_ready, 256);
-    mbar_init(done, C::N_OUT_ISSUERS);
+    mbar_init(done, C::N_OUT_ISSUERS + (OWN_KEYS ? 0 : 2));
     mbar_init(out_free, 256);
     *abort_flag = 0;
     fence_mbar_init();
@@ -190,35 +225,47 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       if constexpr (HAS_GO) prefetch_tmap(&maps.go);
       if constexpr (HAS_GT) prefetch_tmap(&maps.tk), prefetch_tmap(&maps.tv), prefetch_tmap(&maps.tq), prefetch_tmap(&maps.g);
     }
-    int gbase = 0, kact = 0;
-    bool ok = true;
-    BwdItem it;
-    for (int k = 0; ok && k < k_max; ++k) {
-      if (!get_item(k, it)) continue;
-      if (it.n_sub == 0) continue;
-      // Own tiles of this item -> staging area (free once the previous item's rows sit in TMEM).
-      if (kact > 0) ok = mbar_wait(own_ready, (kact - 1) & 1, ab, kAbortBwdOwn);
-      if (!ok) break;
+    // Own tiles of active item number j -> staging half j & 1 (free once item j - 2 is complete).
+    auto load_own = [&](const BwdItem& it, int j) -> bool {
+      const int h = j & 1, use = j >> 1;
+      if (use > 0 && !mbar_wait(own_free + h, (use - 1) & 1, ab, kAbortBwdOwn)) return false;
       if (lane == 0) {
-        mbar_expect_tx(own_staged, C::STAGING_BYTES);
+        unsigned char* dst = sOwn + h * C::STAGING_HALF;
+        mbar_expect_tx(own_staged + h, C::STAGING_HALF);
         if constexpr (OWN_KEYS) {
-          tma_load_3d(sOwn + C::SLOT_K * C::OWN_BYTES, &maps.k, own_staged, 0, it.own0, it.bh);
-          tma_load_3d(sOwn + C::SLOT_V * C::OWN_BYTES, &maps.v, own_staged, 0, it.own0, it.bh);
+          tma_load_3d(dst + C::SLOT_K * C::OWN_BYTES, &maps.k, own_staged + h, 0, it.own0, it.bh);
+          tma_load_3d(dst + C::SLOT_V * C::OWN_BYTES, &maps.v, own_staged + h, 0, it.own0, it.bh);
           if constexpr (HAS_GT) {
-            tma_load_3d(sOwn + C::SLOT_TK * C::OWN_BYTES, &maps.tk, own_staged, 0, it.own0, it.bh);
-            tma_load_3d(sOwn + C::SLOT_TV * C::OWN_BYTES, &maps.tv, own_staged, 0, it.own0, it.bh);
+            tma_load_3d(dst + C::SLOT_TK * C::OWN_BYTES, &maps.tk, own_staged + h, 0, it.own0, it.bh);
+            tma_load_3d(dst + C::SLOT_TV * C::OWN_BYTES, &maps.tv, own_staged + h, 0, it.own0, it.bh);
           }
         } else {
-          tma_load_3d(sOwn + C::SLOT_Q * C::OWN_BYTES, &maps.q, own_staged, 0, it.own0, it.bh);
-          if constexpr (HAS_GO) tma_load_3d(sOwn + C::SLOT_GO * C::OWN_BYTES, &maps.go, own_staged, 0, it.own0, it.bh);
+          tma_load_3d(dst + C::SLOT_Q * C::OWN_BYTES, &maps.q, own_staged + h, 0, it.own0, it.bh);
+          if constexpr (HAS_GO) tma_load_3d(dst + C::SLOT_GO * C::OWN_BYTES, &maps.go, own_staged + h, 0, it.own0, it.bh);
           if constexpr (HAS_GT) {
-            tma_load_3d(sOwn + C::SLOT_TQ * C::OWN_BYTES, &maps.tq, own_staged, 0, it.own0, it.bh);
-            tma_load_3d(sOwn + C::SLOT_G * C::OWN_BYTES, &maps.g, own_staged, 0, it.own0, it.bh);
+            tma_load_3d(dst + C::SLOT_TQ * C::OWN_BYTES, &maps.tq, own_staged + h, 0, it.own0, it.bh);
+            tma_load_3d(dst + C::SLOT_G * C::OWN_BYTES, &maps.g, own_staged + h, 0, it.own0, it.bh);
           }
         }
       }
+      return true;
+    };
+    int gbase = 0, kact = 0, k = 0;
+    BwdItem it, nxt;
+    bool have = next_active(k, it);
+    bool ok = have ? load_own(it, 0) : true;
+    while (ok && have) {
+      int k2 = k + 1;
+      const bool have_next = next_active(k2, nxt);
+      bool next_loaded = !have_next;
       const size_t stat_off = (size_t)it.bh * L;
       for (int s = 0; s < it.n_sub; ++s) {
+        // The next item's own tiles go out once the ring is full: by then its staging half is free.
+        if (s == STAGES && !next_loaded) {
+          ok = load_own(nxt, kact + 1);
+          next_loaded = true;
+          if (!ok) break;
+        }
         const int g = gbase + s;
         const int st = g % STAGES;
         const uint32_t ph = (g / STAGES) & 1;
@@ -269,155 +316,213 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           }
         }
       }
+      if (ok && !next_loaded) ok = load_own(nxt, kact + 1);
       gbase += it.n_sub;
       ++kact;
+      it = nxt;
+      k = k2;
+      have = have_next;
     }
-  } else if (warp <= 3) {
-    // ------------------------------------------------------------------ MMA issuers 0..2
-    const int iss = warp - 1;
-    // Accumulator chains (every chain belongs to exactly one issuing thread):
-    //   own keys    iss0: [S|TS] = K [Q;tQ]^T, TS += tK Q^T      (GO only: S ; second stage dV += P^T gO)
-    //               iss1: E = V G^T          ; second stage dV += A^T G (+ P^T gO)
-    //               iss2: FP = tV G^T (+ V gO^T) ; second stage dK += gS^T Q + gtS^T tQ
-    //   own queries iss0: [S|TS] = Q [K;tK]^T, TS += tQ K^T
-    //               iss1: [E|FP] = G [V;tV]^T (+ FP += gO V^T)   (GO only: FP = gO V^T)
-    //               iss2: second stage dQ += gS K + gtS tK
-    bool has_scores, has_out;
-    if constexpr (OWN_KEYS) {
-      has_scores = HAS_GT ? true : (iss != 1);
-      has_out = HAS_GT ? (iss != 0) : (iss != 1);
-    } else {
-      has_scores = iss != 2;
-      has_out = iss == 2;
-    }
-    if (lane == 0 && (has_scores || has_out)) {
-      constexpr uint32_t idesc_sc = make_idesc(Fmt<T>::kIdesc, OWN, BL, 0, 0);       // 128 x 32 scores
-      constexpr uint32_t idesc_sc2 = make_idesc(Fmt<T>::kIdesc, OWN, 2 * BL, 0, 0);  // 128 x 64: two neighbours
-      constexpr uint32_t idesc_out = make_idesc(Fmt<T>::kIdesc, OWN, D, 0, 1);       // 128 x 64 outputs
-      const uint32_t own_col = tmem + C::COL_OWN;
-      // accumulator columns [off, off + 32*(wide ? 2 : 1)) of buffer buf (+)= own slot (A, TMEM) x
-      // streamed tile(s)^T (B, K-major; wide: the tile in b_tile and its neighbour, 64 rows)
-      auto score = [&](int buf, int off, int slot, uint32_t b_tile, bool first, bool wide) {
+  } else if (warp <= 3 || warp == 12) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Each of these warps works with one thread.  Such a thread pays ~75 cycles per MMA and ~450
+    // cycles of waits and bookkeeping per sub-tile, so the work is split by sub-tile, not by
+    // accumulator: warp 1 forms all scores of the even sub-tiles, warp 2 those of the odd ones
+    //   own keys   : [S|TS] = K [Q;tQ]^T, TS += tK Q^T, E = V G^T, FP = tV G^T (+ V gO^T)
+    //   own queries: [S|TS] = Q [K;tK]^T, TS += tQ K^T, [E|FP] = G [V;tV]^T (+ FP += gO V^T)
+    // and the output accumulators, which run through all sub-tiles of an item, have a thread each:
+    //   warp 3 : dK += gS^T Q + gtS^T tQ   or   dQ += gS K + gtS tK
+    //   warp 12: dV += A^T G (+ P^T gO)    (own keys only)
+    // Stage / buffer indices, parities, barrier addresses and descriptor words live in registers
+    // and advance by additions.
+    constexpr uint32_t idesc_sc = make_idesc(Fmt<T>::kIdesc, OWN, BL, 0, 0);       // 128 x 32 scores
+    constexpr uint32_t idesc_sc2 = make_idesc(Fmt<T>::kIdesc, OWN, 2 * BL, 0, 0);  // 128 x 64: two neighbours
+    constexpr uint32_t idesc_out = make_idesc(Fmt<T>::kIdesc, OWN, D, 0, 1);       // 128 x 64 outputs
+    constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, LOOP16 = C::LOOP_BYTES >> 4, OWN16 = C::OWN_BYTES >> 4;
+    // A position in the sequence of sub-tiles: ring stage and accumulator buffer with their parities.
+    struct Cursor {
+      uint32_t st_bar, st_tile, st_par, buf_bar, buf_col, buf_par, sf_bar;
+      __device__ __forceinline__ explicit Cursor(uint32_t g)  // g < min(STAGES, NBUF)
+          : st_bar(8 * g), st_tile(g * STAGE16), st_par(0), buf_bar(8 * g), buf_col(g * C::COL_BUF), buf_par(0),
+            sf_bar(8 * g) {}
+      __device__ __forceinline__ void advance(uint32_t n) {  // n = 1 or 2
+        st_bar += 8 * n, st_tile += n * STAGE16;
+        if (st_bar >= 8 * STAGES) st_bar -= 8 * STAGES, st_tile -= STAGES * STAGE16, st_par ^= 1;
+        buf_bar += 8 * n, buf_col += n * C::COL_BUF;
+        if (buf_bar >= 8 * NBUF) buf_bar -= 8 * NBUF, buf_col -= NBUF * C::COL_BUF, buf_par ^= 1;
+        sf_bar += 8 * n;
+        if (sf_bar >= 8 * C::N_SFULL) sf_bar -= 8 * C::N_SFULL;
+      }
+    };
+    const uint32_t bar_loop_full = smem_u32(loop_full), bar_loop_empty = smem_u32(loop_empty);
+    const uint32_t bar_s_full = smem_u32(s_full), bar_p_full = smem_u32(p_full);
+    const uint32_t ring_lo = kDescLo | (smem_u32(sLoop) >> 4);
+    const uint32_t own_col = tmem + C::COL_OWN;
+
+    if (lane == 0 && (warp == 1 || warp == 2)) {
+      // ---------------- scores of the sub-tiles g = r, r + 2, r + 4, ...
+      const uint32_t r = warp - 1;
+      Cursor cs(r);      // the next sub-tile of this thread
+      Cursor cf(1 - r);  // the sub-tile NBUF before the first one (>= NBUF) of this thread: 4 - 3 or 3 - 3
+      int g = (int)r;
+      uint32_t own_lo = 0;  // descriptor word of the current item's staging half
+      // acc (+)= own tile `slot` (A: packed rows in TMEM where they exist, else the staging tile) x
+      // streamed tile(s)^T (B, K-major; wide: the tile and its neighbour, 64 rows)
+      auto score = [&](uint32_t d, auto slot_c, uint32_t b_lo, auto first_c, auto wide_c) {
+        constexpr int slot = decltype(slot_c)::value;
+        constexpr bool first = decltype(first_c)::value != 0, wide = decltype(wide_c)::value != 0;
+        constexpr uint32_t id = wide ? idesc_sc2 : idesc_sc;
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          umma_ts(tmem + buf * C::COL_BUF + off, own_col + slot * 32 + ks * 8,
-                  make_smem_desc(b_tile + ks * 32, 16, 1024), wide ? idesc_sc2 : idesc_sc, (!first || ks > 0));
-      };
-      // out (+)= packed operand (A, TMEM, 16 columns) x streamed tile (B, MN-major, 32 rows)
-      auto outer = [&](int out_col, int buf, int off, uint32_t b_tile, bool accumulate) {
-#pragma unroll
-        for (int kk = 0; kk < BL / 16; ++kk)
-          umma_ts(tmem + out_col, tmem + buf * C::COL_BUF + off + kk * 8,
-                  make_smem_desc(b_tile + kk * 2048, 16, 1024), idesc_out, (accumulate || kk > 0));
-      };
-      // Scores of global sub-tile g for the accumulators this issuer owns.
-      auto issue_scores = [&](int g) -> bool {
-        const int st = g % STAGES, buf = g & 1;
-        // Buffer `buf` may be overwritten once every second-stage chain of sub-tile g-2 has read it:
-        // that is what loop_empty[stage of g-2] records (one arrival per second-stage issuer).
-        if (g >= 2 && !mbar_wait(loop_empty + ((g - 2) % STAGES), ((g - 2) / STAGES) & 1, ab, kAbortAux)) return false;
-        if (!mbar_wait(loop_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull)) return false;
-        tc_fence_after();
-        const uint32_t lp = smem_u32(sLoop + st * C::STAGE_BYTES);
-        auto lt = [&](int slot) { return lp + slot * C::LOOP_BYTES; };
-        if constexpr (OWN_KEYS) {
-          if (iss == 0) {
-            if constexpr (HAS_GT) {
-              score(buf, C::OFF_S, C::SLOT_K, lt(C::SLOT_Q), true, true);      // [S|TS] = K [Q;tQ]^T
-              score(buf, C::OFF_TS, C::SLOT_TK, lt(C::SLOT_Q), false, false);  // TS += tK Q^T
-            } else {
-              score(buf, C::OFF_S, C::SLOT_K, lt(C::SLOT_Q), true, false);
-            }
-          } else if (iss == 1) {
-            if constexpr (HAS_GT) score(buf, C::OFF_E, C::SLOT_V, lt(C::SLOT_G), true, false);
+        for (int ks = 0; ks < D / 16; ++ks) {
+          if constexpr (slot < C::N_OWN_TMEM) {
+            if (first && ks == 0)
+              umma_ts_lo<false>(d, own_col + slot * 32 + ks * 8, b_lo + ks * 2, id);
+            else
+              umma_ts_lo<true>(d, own_col + slot * 32 + ks * 8, b_lo + ks * 2, id);
           } else {
-            if constexpr (HAS_GT) {
-              score(buf, C::OFF_FP, C::SLOT_TV, lt(C::SLOT_G), true, false);
-              if constexpr (HAS_GO) score(buf, C::OFF_FP, C::SLOT_V, lt(C::SLOT_GO), false, false);
-            } else {
-              score(buf, C::OFF_FP, C::SLOT_V, lt(C::SLOT_GO), true, false);
-            }
-          }
-        } else {
-          if (iss == 0) {
-            if constexpr (HAS_GT) {
-              score(buf, C::OFF_S, C::SLOT_Q, lt(C::SLOT_K), true, true);      // [S|TS] = Q [K;tK]^T
-              score(buf, C::OFF_TS, C::SLOT_TQ, lt(C::SLOT_K), false, false);  // TS += tQ K^T
-            } else {
-              score(buf, C::OFF_S, C::SLOT_Q, lt(C::SLOT_K), true, false);
-            }
-          } else {
-            if constexpr (HAS_GT) {
-              score(buf, C::OFF_E, C::SLOT_G, lt(C::SLOT_V), true, true);      // [E|FP] = G [V;tV]^T
-              if constexpr (HAS_GO) score(buf, C::OFF_FP, C::SLOT_GO, lt(C::SLOT_V), false, false);
-            } else {
-              score(buf, C::OFF_FP, C::SLOT_GO, lt(C::SLOT_V), true, false);
-            }
+            if (first && ks == 0)
+              umma_ss_lo<false>(d, own_lo + slot * OWN16 + ks * 2, b_lo + ks * 2, id);
+            else
+              umma_ss_lo<true>(d, own_lo + slot * OWN16 + ks * 2, b_lo + ks * 2, id);
           }
         }
-        tc_commit(s_full + buf);
-        return true;
       };
+      using I0 = IntC<0>;
+      using I1 = IntC<1>;
       int gbase = 0, kact = 0;
       bool ok = true;
       BwdItem it;
       for (int k = 0; ok && k < k_max; ++k) {
         if (!get_item(k, it)) continue;
         if (it.n_sub == 0) continue;
-        ok = mbar_wait(own_ready, kact & 1, ab, kAbortBwdOwn);  // this item's own rows are in TMEM
+        const int g_end = gbase + it.n_sub;
+        // This item's own operands: the staging half (own keys), the packed rows in TMEM (own queries).
+        // Waited for even when none of the item's sub-tiles is this thread's: a parity wait is only
+        // safe for a thread that sees every phase of the barrier.
+        if constexpr (OWN_KEYS)
+          ok = mbar_wait(own_staged + (kact & 1), (kact >> 1) & 1, ab, kAbortBwdOwn);
+        else
+          ok = mbar_wait(own_ready, kact & 1, ab, kAbortBwdOwn);
         if (!ok) break;
         tc_fence_after();
-        if (has_scores)
-          for (int s = 0; ok && s < 2 && s < it.n_sub; ++s) ok = issue_scores(gbase + s);
-        for (int s = 0; ok && s < it.n_sub; ++s) {
-          const int g = gbase + s;
-          const int st = g % STAGES, buf = g & 1;
-          if (has_out) {
-            if (!mbar_wait(p_full + buf, (g >> 1) & 1, ab, kAbortBwdPFull)) {
+        own_lo = kDescLo | (smem_u32(sOwn + (kact & 1) * C::STAGING_HALF) >> 4);
+#pragma unroll 1
+        for (; g < g_end; g += 2) {
+          // The buffer may be overwritten once every second-stage chain of sub-tile g - NBUF has read
+          // it: that is what loop_empty[its stage] records (one arrival per second-stage issuer).
+          if (g >= NBUF) {
+            if (!mbar_wait_u32(bar_loop_empty + cf.st_bar, cf.st_par, ab, kAbortAux)) {
               ok = false;
               break;
             }
-            // The first sub-tile overwrites the output accumulators: the previous item's epilogue
-            // must have read them.
-            if (s == 0 && kact > 0 && !mbar_wait(out_free, (kact - 1) & 1, ab, kAbortBwdDone)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t lp = smem_u32(sLoop + st * C::STAGE_BYTES);
-            auto lt = [&](int slot) { return lp + slot * C::LOOP_BYTES; };
-            const bool acc = s > 0;
-            if constexpr (OWN_KEYS) {
-              if (iss == 2) {
-                outer(C::COL_OUT0, buf, C::OFF_FP, lt(C::SLOT_Q), acc);                            // dK += gS^T Q
-                if constexpr (HAS_GT) outer(C::COL_OUT0, buf, C::OFF_E, lt(C::SLOT_TQ), true);    // dK += gtS^T tQ
-              } else if constexpr (HAS_GT) {
-                outer(C::COL_OUT1, buf, C::OFF_TS, lt(C::SLOT_G), acc);                            // dV += A^T G
-                if constexpr (HAS_GO) outer(C::COL_OUT1, buf, C::OFF_S, lt(C::SLOT_GO), true);    // dV += P^T gO
-              } else {
-                outer(C::COL_OUT1, buf, C::OFF_S, lt(C::SLOT_GO), acc);                            // dV += P^T gO
-              }
-            } else {
-              outer(C::COL_OUT0, buf, C::OFF_FP, lt(C::SLOT_K), acc);                              // dQ += gS K
-              if constexpr (HAS_GT) outer(C::COL_OUT0, buf, C::OFF_E, lt(C::SLOT_TK), true);      // dQ += gtS tK
-            }
-            tc_commit(loop_empty + st);
+            cf.advance(2);
           }
-          if (has_scores && s + 2 < it.n_sub) ok = issue_scores(g + 2);
+          if (!mbar_wait_u32(bar_loop_full + cs.st_bar, cs.st_par, ab, kAbortBwdLoopFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          TRACE(g, r * 4 + 0);
+          const uint32_t lp = ring_lo + cs.st_tile;  // tile slot 0 of the stage
+          const uint32_t acc = tmem + cs.buf_col;
+          if constexpr (OWN_KEYS) {
+            if constexpr (HAS_GT) {
+              score(acc + C::OFF_S, IntC<C::SLOT_K>{}, lp + C::SLOT_Q * LOOP16, I1{}, I1{});    // [S|TS] = K [Q;tQ]^T
+              score(acc + C::OFF_TS, IntC<C::SLOT_TK>{}, lp + C::SLOT_Q * LOOP16, I0{}, I0{});  // TS += tK Q^T
+              score(acc + C::OFF_E, IntC<C::SLOT_V>{}, lp + C::SLOT_G * LOOP16, I1{}, I0{});    // E = V G^T
+              score(acc + C::OFF_FP, IntC<C::SLOT_TV>{}, lp + C::SLOT_G * LOOP16, I1{}, I0{});  // FP = tV G^T
+              if constexpr (HAS_GO) score(acc + C::OFF_FP, IntC<C::SLOT_V>{}, lp + C::SLOT_GO * LOOP16, I0{}, I0{});
+            } else {
+              score(acc + C::OFF_S, IntC<C::SLOT_K>{}, lp + C::SLOT_Q * LOOP16, I1{}, I0{});    // S = K Q^T
+              score(acc + C::OFF_FP, IntC<C::SLOT_V>{}, lp + C::SLOT_GO * LOOP16, I1{}, I0{});  // FP = V gO^T
+            }
+          } else {
+            if constexpr (HAS_GT) {
+              score(acc + C::OFF_S, IntC<C::SLOT_Q>{}, lp + C::SLOT_K * LOOP16, I1{}, I1{});    // [S|TS] = Q [K;tK]^T
+              score(acc + C::OFF_TS, IntC<C::SLOT_TQ>{}, lp + C::SLOT_K * LOOP16, I0{}, I0{});  // TS += tQ K^T
+              score(acc + C::OFF_E, IntC<C::SLOT_G>{}, lp + C::SLOT_V * LOOP16, I1{}, I1{});    // [E|FP] = G [V;tV]^T
+              if constexpr (HAS_GO) score(acc + C::OFF_FP, IntC<C::SLOT_GO>{}, lp + C::SLOT_V * LOOP16, I0{}, I0{});
+            } else {
+              score(acc + C::OFF_S, IntC<C::SLOT_Q>{}, lp + C::SLOT_K * LOOP16, I1{}, I0{});    // S = Q K^T
+              score(acc + C::OFF_FP, IntC<C::SLOT_GO>{}, lp + C::SLOT_V * LOOP16, I1{}, I0{});  // FP = gO V^T
+            }
+          }
+          tc_commit_u32(bar_s_full + cs.sf_bar);
+          TRACE(g, r * 4 + 1);
+          cs.advance(2);
         }
-        if (ok && has_out) tc_commit(done);
-        gbase += it.n_sub;
+        if (!ok) break;
+        // "This thread is through with the item": keeps the per-item barrier it waits on from running
+        // more than one phase ahead of it.  Own keys: the staging half is not refilled before (own_free);
+        // own queries: the next item's rows are not written to TMEM before (done).
+        if constexpr (OWN_KEYS)
+          mbar_arrive(own_free + (kact & 1));
+        else
+          mbar_arrive(done);
+        gbase = g_end;
+        ++kact;
+      }
+    } else if (lane == 0 && (warp == 3 || OWN_KEYS)) {
+      // ---------------- second stage: one output accumulator through all sub-tiles
+      const bool second = warp == 12;  // dV
+      Cursor co(0);
+      int kact = 0, g = 0;
+      bool ok = true;
+      BwdItem it;
+      // out (+)= packed operand (A, TMEM, 16 columns per 16 streamed rows) x streamed tile (B, MN-major)
+      auto outer = [&](uint32_t out_col, uint32_t a_col, uint32_t b_lo, uint32_t accumulate) {
+        umma_ts_lo_dyn(tmem + out_col, a_col, b_lo, idesc_out, accumulate);
+        umma_ts_lo<true>(tmem + out_col, a_col + 8, b_lo + (2048 >> 4), idesc_out);
+      };
+      for (int k = 0; ok && k < k_max; ++k) {
+        if (!get_item(k, it)) continue;
+        if (it.n_sub == 0) continue;
+#pragma unroll 1
+        for (int s = 0; s < it.n_sub; ++s, ++g) {
+          if (!mbar_wait_u32(bar_p_full + co.buf_bar, co.buf_par, ab, kAbortBwdPFull)) {
+            ok = false;
+            break;
+          }
+          // The first sub-tile overwrites the output accumulators: the previous item's epilogue must
+          // have read them.
+          if (s == 0 && kact > 0 && !mbar_wait(out_free, (kact - 1) & 1, ab, kAbortBwdDone)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          TRACE(g, second ? 10 : 6);
+          const uint32_t lp = ring_lo + co.st_tile;
+          const uint32_t opnd = tmem + co.buf_col;
+          const uint32_t acc = s > 0;
+          if constexpr (OWN_KEYS) {
+            if (!second) {
+              outer(C::COL_OUT0, opnd + C::OFF_FP, lp + C::SLOT_Q * LOOP16, acc);                        // dK += gS^T Q
+              if constexpr (HAS_GT) outer(C::COL_OUT0, opnd + C::OFF_E, lp + C::SLOT_TQ * LOOP16, 1);   // dK += gtS^T tQ
+            } else if constexpr (HAS_GT) {
+              outer(C::COL_OUT1, opnd + C::OFF_TS, lp + C::SLOT_G * LOOP16, acc);                        // dV += A^T G
+              if constexpr (HAS_GO) outer(C::COL_OUT1, opnd + C::OFF_S, lp + C::SLOT_GO * LOOP16, 1);   // dV += P^T gO
+            } else {
+              outer(C::COL_OUT1, opnd + C::OFF_S, lp + C::SLOT_GO * LOOP16, acc);                        // dV += P^T gO
+            }
+          } else {
+            outer(C::COL_OUT0, opnd + C::OFF_FP, lp + C::SLOT_K * LOOP16, acc);                          // dQ += gS K
+            if constexpr (HAS_GT) outer(C::COL_OUT0, opnd + C::OFF_E, lp + C::SLOT_TK * LOOP16, 1);     // dQ += gtS tK
+          }
+          tc_commit_u32(bar_loop_empty + co.st_bar);
+          TRACE(g, second ? 11 : 7);
+          co.advance(1);
+        }
+        if (ok) tc_commit(done);
         ++kact;
       }
     }
   } else {
     // ------------------------------------------------------------------ elementwise warpgroups
-    const int wg = (warp - 4) >> 2;  // 0 / 1: accumulator buffer this group works on
+    const int wg = (warp - 4) >> 2;  // 0 / 1: parity of the sub-tiles this group works on
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t tbase = tmem + lane_off;
-    const uint32_t tbuf = tbase + wg * C::COL_BUF;
     const float2 c2 = make_float2(a.sm_scale * kLog2e, a.sm_scale * kLog2e);
     const float2 sc2 = make_float2(a.sm_scale, a.sm_scale);
     bool alive = true;
@@ -456,32 +561,27 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       const int n_valid = valid_keys(it.b);
       const size_t stat_off = (size_t)it.bh * L;
 
-      // ---- own operand rows: staging area (128-byte-swizzled TMA tiles) -> TMEM, packed 16-bit ----
-      if (!mbar_wait(own_staged, kact & 1, ab, kAbortBwdOwn)) {
-        alive = false;
-        break;
-      }
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int slot = 2 * j + wg;
-        if (slot < C::N_OWN) {
+      float r_nlse = -INFINITY, r_nmu = 0.f, r_neps = 0.f, r_nsub = 0.f;
+      if constexpr (!OWN_KEYS) {
+        // ---- own query rows Q (, tQ): staging half (128-byte-swizzled TMA tiles) -> TMEM, packed ----
+        if (!mbar_wait(own_staged + (kact & 1), (kact >> 1) & 1, ab, kAbortBwdOwn)) {
+          alive = false;
+          break;
+        }
+        if (wg < C::N_OWN_TMEM) {
           uint32_t r[32];
-          const unsigned char* src = sOwn + slot * C::OWN_BYTES + row * 128;
+          const unsigned char* src = sOwn + (kact & 1) * C::STAGING_HALF + wg * C::OWN_BYTES + row * 128;
 #pragma unroll
           for (int x = 0; x < 8; ++x) {
             const uint4 v = *reinterpret_cast<const uint4*>(src + ((x ^ (row & 7)) << 4));
             r[4 * x] = v.x, r[4 * x + 1] = v.y, r[4 * x + 2] = v.z, r[4 * x + 3] = v.w;
           }
-          tmem_st32(tbase + C::COL_OWN + slot * 32, r);
+          tmem_st32(tbase + C::COL_OWN + wg * 32, r);
+          tmem_wait_st();
         }
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(own_ready);
-
-      // own-queries variant: row statistics, negated
-      float r_nlse = -INFINITY, r_nmu = 0.f, r_neps = 0.f, r_nsub = 0.f;
-      if constexpr (!OWN_KEYS) {
+        tc_fence_before();
+        mbar_arrive(own_ready);
+        // row statistics, negated
         if (own_idx < L) {
           r_nlse = -a.lse[stat_off + own_idx];
           float sub = a.delta[stat_off + own_idx];
@@ -498,7 +598,8 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       // sub-tiles whose global index has this group's parity
       for (int s = ((wg - gbase) & 1); s < it.n_sub; s += 2) {
         const int g = gbase + s;
-        const int st = g % STAGES;
+        const int st = g % STAGES, buf = g % NBUF;
+        const uint32_t tbuf = tbase + buf * C::COL_BUF;
         const int l0 = it.loop_begin + s * BL;
         if constexpr (OWN_KEYS) {
           if (!mbar_wait(loop_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull)) {
@@ -506,11 +607,12 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             break;
           }
         }
-        if (!mbar_wait(s_full + wg, (g >> 1) & 1, ab, kAbortBwdSFull)) {
+        if (!mbar_wait(s_full + g % C::N_SFULL, (g / C::N_SFULL) & 1, ab, kAbortBwdSFull)) {
           alive = false;
           break;
         }
         tc_fence_after();
+        if (row == 0) TRACE(g, 12);
         // Masking by index comparison; columns outside [col_lo, col_hi) get p = 0.
         //   own keys   : (key j = own_idx, query i = l0 + col) is dead if j >= n_valid, or causal and j > i
         //   own queries: (query i = own_idx, key j = l0 + col) is dead if j >= n_valid, or causal and j > i
@@ -522,50 +624,50 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           col_hi = min(BL, n_valid - l0);
           if (causal) col_hi = min(col_hi, own_idx - l0 + 1);  // j <= i
         }
-        uint32_t sv[2][16], fp[2][16];
-        uint32_t ts[HAS_GT ? 2 : 1][16], ev[HAS_GT ? 2 : 1][16];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld16(tbuf + C::OFF_S + 16 * c, sv[c]);
-          tmem_ld16(tbuf + C::OFF_FP + 16 * c, fp[c]);
-          if constexpr (HAS_GT) {
-            tmem_ld16(tbuf + C::OFF_TS + 16 * c, ts[c]);
-            tmem_ld16(tbuf + C::OFF_E + 16 * c, ev[c]);
-          }
-        }
-        tmem_wait_ld();
         const float4* stat = sStat + st * (BL / 2) * 2;
-#pragma unroll
+        // Two halves of 16 columns, as a real loop: the body exists once, which keeps the instruction
+        // footprint of the eight elementwise warps small next to the single-thread MMA issuers.
+#pragma unroll 1
         for (int c = 0; c < 2; ++c) {
+          uint32_t sv[16], fp[16], ts[16], ev[16];
+          tmem_ld16(tbuf + C::OFF_S + 16 * c, sv);
+          tmem_ld16(tbuf + C::OFF_FP + 16 * c, fp);
+          if constexpr (HAS_GT) {
+            tmem_ld16(tbuf + C::OFF_TS + 16 * c, ts);
+            tmem_ld16(tbuf + C::OFF_E + 16 * c, ev);
+          }
+          tmem_wait_ld();
+          if (row == 0 && c == 0) TRACE(g, 13);
+          const int lo_c = col_lo - 16 * c, hi_c = col_hi - 16 * c;  // live columns of this half: [lo_c, hi_c)
           uint32_t pk_gs[8], pk_gt[8], pk_av[8], pk_p[8];
 #pragma unroll
           for (int x = 0; x < 8; ++x) {
-            const int col = 16 * c + 2 * x;  // even column of the pair
+            const int col = 2 * x;  // even column of the pair, within the half
             float2 nl, nmu, neps, nsub;
             if constexpr (OWN_KEYS) {
-              const float4 sa = stat[(col >> 1) * 2], sb = stat[(col >> 1) * 2 + 1];
+              const float4 sa = stat[(8 * c + x) * 2], sb = stat[(8 * c + x) * 2 + 1];
               nl = make_float2(sa.x, sa.y), nmu = make_float2(sa.z, sa.w);
               neps = make_float2(sb.x, sb.y), nsub = make_float2(sb.z, sb.w);
             } else {
               nl = make_float2(r_nlse, r_nlse), nmu = make_float2(r_nmu, r_nmu);
               neps = make_float2(r_neps, r_neps), nsub = make_float2(r_nsub, r_nsub);
             }
-            const float2 xs = __ffma2_rn(f2(sv[c][2 * x], sv[c][2 * x + 1]), c2, nl);
+            const float2 xs = __ffma2_rn(f2(sv[2 * x], sv[2 * x + 1]), c2, nl);
             float2 p;
-            p.x = (col >= col_lo && col < col_hi) ? fast_exp2(xs.x) : 0.f;
-            p.y = (col + 1 >= col_lo && col + 1 < col_hi) ? fast_exp2(xs.y) : 0.f;
+            p.x = (col >= lo_c && col < hi_c) ? fast_exp2(xs.x) : 0.f;
+            p.y = (col + 1 >= lo_c && col + 1 < hi_c) ? fast_exp2(xs.y) : 0.f;
             if constexpr (HAS_GT) {
-              const float2 tm = __ffma2_rn(f2(ts[c][2 * x], ts[c][2 * x + 1]), sc2, nmu);
-              const float2 eb = __fadd2_rn(f2(ev[c][2 * x], ev[c][2 * x + 1]), neps);
+              const float2 tm = __ffma2_rn(f2(ts[2 * x], ts[2 * x + 1]), sc2, nmu);
+              const float2 eb = __fadd2_rn(f2(ev[2 * x], ev[2 * x + 1]), neps);
               const float2 av = __fmul2_rn(p, tm);
               const float2 gt = __fmul2_rn(p, eb);
-              const float2 u = __fadd2_rn(f2(fp[c][2 * x], fp[c][2 * x + 1]), nsub);
+              const float2 u = __fadd2_rn(f2(fp[2 * x], fp[2 * x + 1]), nsub);
               const float2 gs = __fmul2_rn(p, __ffma2_rn(eb, tm, u));
               pk_gs[x] = Elem<T>::pack(gs.x, gs.y);
               pk_gt[x] = Elem<T>::pack(gt.x, gt.y);
               pk_av[x] = Elem<T>::pack(av.x, av.y);
             } else {
-              const float2 u = __fadd2_rn(f2(fp[c][2 * x], fp[c][2 * x + 1]), nsub);
+              const float2 u = __fadd2_rn(f2(fp[2 * x], fp[2 * x + 1]), nsub);
               const float2 gs = __fmul2_rn(p, u);
               pk_gs[x] = Elem<T>::pack(gs.x, gs.y);
             }
@@ -578,9 +680,11 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           }
           if constexpr (OWN_KEYS && HAS_GO) tmem_st8(tbuf + C::OFF_S + 8 * c, pk_p);
         }
+        if (row == 0) TRACE(g, 14);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(p_full + wg);
+        mbar_arrive(p_full + buf);
+        if (row == 0) TRACE(g, 15);
       }
       if (!alive) break;
 
@@ -598,6 +702,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(out_free);
+        mbar_arrive(own_free + (kact & 1));  // every MMA of the item is complete: its staging half is free
         if constexpr (OWN_KEYS) {
           store_half(a.dk, it.bh, own_idx, r0, a.sm_scale);
           store_half(a.dv, it.bh, own_idx, r1, 1.f);
@@ -703,6 +808,13 @@ static int launch_t64(const jvpfa_bwd_args& a, cudaStream_t s) {
 }
 
 }  // namespace tc5
+
+#ifdef JVPFA_TC5_PROFILE
+extern "C" int jvpfa_debug_read_trace(long long* out, int which) {
+  return (int)cudaMemcpyFromSymbol(out, tc5::g_bwd_trace, sizeof(long long) * tc5::kTraceW * tc5::kTraceEv,
+                                   sizeof(long long) * tc5::kTraceW * tc5::kTraceEv * which);
+}
+#endif
 
 int launch_bwd_tc5_d64(const jvpfa_bwd_args& a, cudaStream_t s) {
   return a.dtype == JVPFA_BF16 ? tc5::launch_t64<__nv_bfloat16>(a, s) : tc5::launch_t64<__half>(a, s);

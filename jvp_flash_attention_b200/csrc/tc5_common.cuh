@@ -110,6 +110,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// Variants that take the barrier's shared-memory address (the issuing threads keep barrier
+// addresses and parities in registers; every instruction between two MMAs of a thread that runs
+// alone in its warp costs its full latency).
+__device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_slow_u32(uint32_t bar, uint32_t parity, volatile int* cta_flag,
+                                                int* global_status, int code) {
+  const long long t0 = clock64();
+  int polls = 0;
+  while (true) {
+    if (mbar_try_wait_u32(bar, parity)) return true;
+    if ((++polls & 63) == 0) {
+      if (*cta_flag != 0) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *cta_flag = code;
+        atomicCAS(global_status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t bar, uint32_t parity, const AbortState& ab, int code) {
+  if (mbar_try_wait_u32(bar, parity)) return true;
+  if (mbar_try_wait_u32(bar, parity)) return true;
+  return mbar_wait_slow_u32(bar, parity, ab.cta_flag, ab.global_status, code);
+}
+
 // ---- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y,
                                             int z) {
@@ -141,6 +177,10 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_u32(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // 32 lanes x 32 columns: thread i of the warp receives columns [col, col+32) of TMEM lane
@@ -230,6 +270,47 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+
+
+// The same two instructions with the shared-memory descriptors given as (low, high) words.  For the
+// 128-byte-swizzled tiles used here (leading offset 16 B, 8-row groups 1024 B apart) the high word
+// is the constant kDescHi and the low word is kDescLo | (byte address >> 4): stepping through a
+// tile is an integer add on the low word.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescLo = (16u >> 4) << 16;
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+// accumulate flag known only at run time
+__device__ __forceinline__ void umma_ts_lo_dyn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int I>
+struct IntC {
+  static constexpr int value = I;
+};
 
 }  // namespace tc5
 }  // namespace jvpfa
