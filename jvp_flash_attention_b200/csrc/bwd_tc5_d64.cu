@@ -57,10 +57,11 @@ struct Bwd64Cfg {
   static constexpr int BL = 32;
   static constexpr int NBUF = 3;                                // sub-tiles in flight
   static constexpr int STAGES = (HAS_GO && HAS_GT) ? 5 : 6;     // TMA ring depth (limited by shared memory)
-  // warp 0: TMA producer; warps 1, 2: score issuers (even / odd sub-tiles); warp 3: second-stage
-  // issuer (dK or dQ); warps 4..11: two elementwise warpgroups; warp 12 (own keys): second-stage
-  // issuer for dV
-  static constexpr int NTHREADS = OWN_KEYS ? 416 : 384;
+  // warp 0: TMA producer; warps 1, 2 and 13, 14: score issuers (two per sub-tile, even / odd
+  // sub-tiles); warp 3: second-stage issuer (dK or dQ); warps 4..11: two elementwise warpgroups;
+  // warp 12: second-stage issuer for dV (own keys; idle otherwise)
+  static constexpr int NTHREADS = 480;
+  static constexpr int N_SCORE_THREADS = 4;
   static constexpr int N_OUT_ISSUERS = OWN_KEYS ? 2 : 1;
   // s_full barriers are indexed by g % 6: sub-tiles that share one have the same accumulator buffer
   // (g % 3) and the same elementwise group (g & 1), so its waiter sees every phase.
@@ -113,7 +114,7 @@ struct BwdItem {
 };
 
 template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
-__global__ void __launch_bounds__(416, 1)
+__global__ void __launch_bounds__(480, 1)
 bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps maps, int* status) {
   using C = Bwd64Cfg<OWN_KEYS, HAS_GO, HAS_GT>;
   constexpr int D = 64, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES, NBUF = C::NBUF;
@@ -195,15 +196,15 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       mbar_init(loop_full + s, 1);
       mbar_init(loop_empty + s, C::N_OUT_ISSUERS);
     }
-    for (int b = 0; b < C::N_SFULL; ++b) mbar_init(s_full + b, 1);
+    for (int b = 0; b < C::N_SFULL; ++b) mbar_init(s_full + b, 2);  // the two score threads of a sub-tile
     for (int b = 0; b < NBUF; ++b) mbar_init(p_full + b, 128);
-    // The two score threads take part in one per-item barrier each (own_free or done, see below).
+    // The score threads take part in one per-item barrier each (own_free or done, see below).
     for (int h = 0; h < 2; ++h) {
       mbar_init(own_staged + h, 1);
-      mbar_init(own_free + h, 256 + (OWN_KEYS ? 2 : 0));
+      mbar_init(own_free + h, 256 + (OWN_KEYS ? C::N_SCORE_THREADS : 0));
     }
     mbar_init(own_ready, 256);
-    mbar_init(done, C::N_OUT_ISSUERS + (OWN_KEYS ? 0 : 2));
+    mbar_init(done, C::N_OUT_ISSUERS + (OWN_KEYS ? 0 : C::N_SCORE_THREADS));
     mbar_init(out_free, 256);
     *abort_flag = 0;
     fence_mbar_init();
@@ -323,13 +324,14 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       k = k2;
       have = have_next;
     }
-  } else if (warp <= 3 || warp == 12) {
+  } else if (warp <= 3 || warp >= 12) {
     // ------------------------------------------------------------------ MMA issuers
-    // Each of these warps works with one thread.  Such a thread pays ~75 cycles per MMA and ~450
-    // cycles of waits and bookkeeping per sub-tile, so the work is split by sub-tile, not by
-    // accumulator: warp 1 forms all scores of the even sub-tiles, warp 2 those of the odd ones
-    //   own keys   : [S|TS] = K [Q;tQ]^T, TS += tK Q^T, E = V G^T, FP = tV G^T (+ V gO^T)
-    //   own queries: [S|TS] = Q [K;tK]^T, TS += tQ K^T, [E|FP] = G [V;tV]^T (+ FP += gO V^T)
+    // Each of these warps works with one thread.  Such a thread pays ~75 cycles per MMA and a few
+    // hundred cycles of waits and bookkeeping per sub-tile, and the time a sub-tile's scores take to
+    // issue is part of the latency that the three buffers in flight have to cover.  So the scores of
+    // the even sub-tiles belong to warps 1 and 13, those of the odd sub-tiles to warps 2 and 14:
+    //   own keys   : warps 1, 2: [S|TS] = K [Q;tQ]^T, TS += tK Q^T ; warps 13, 14: E = V G^T, FP = tV G^T (+ V gO^T)
+    //   own queries: warps 1, 2: [S|TS] = Q [K;tK]^T, TS += tQ K^T ; warps 13, 14: [E|FP] = G [V;tV]^T (+ FP += gO V^T)
     // and the output accumulators, which run through all sub-tiles of an item, have a thread each:
     //   warp 3 : dK += gS^T Q + gtS^T tQ   or   dQ += gS K + gtS tK
     //   warp 12: dV += A^T G (+ P^T gO)    (own keys only)
@@ -359,9 +361,10 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     const uint32_t ring_lo = kDescLo | (smem_u32(sLoop) >> 4);
     const uint32_t own_col = tmem + C::COL_OWN;
 
-    if (lane == 0 && (warp == 1 || warp == 2)) {
+    if (lane == 0 && (warp == 1 || warp == 2 || warp >= 13)) {
       // ---------------- scores of the sub-tiles g = r, r + 2, r + 4, ...
-      const uint32_t r = warp - 1;
+      const bool part_b = warp >= 13;  // which accumulators
+      const uint32_t r = part_b ? warp - 13 : warp - 1;
       Cursor cs(r);      // the next sub-tile of this thread
       Cursor cf(1 - r);  // the sub-tile NBUF before the first one (>= NBUF) of this thread: 4 - 3 or 3 - 3
       int g = (int)r;
@@ -422,33 +425,45 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             break;
           }
           tc_fence_after();
-          TRACE(g, r * 4 + 0);
+          TRACE(g, r * 4 + (part_b ? 2 : 0));
           const uint32_t lp = ring_lo + cs.st_tile;  // tile slot 0 of the stage
           const uint32_t acc = tmem + cs.buf_col;
-          if constexpr (OWN_KEYS) {
-            if constexpr (HAS_GT) {
-              score(acc + C::OFF_S, IntC<C::SLOT_K>{}, lp + C::SLOT_Q * LOOP16, I1{}, I1{});    // [S|TS] = K [Q;tQ]^T
-              score(acc + C::OFF_TS, IntC<C::SLOT_TK>{}, lp + C::SLOT_Q * LOOP16, I0{}, I0{});  // TS += tK Q^T
-              score(acc + C::OFF_E, IntC<C::SLOT_V>{}, lp + C::SLOT_G * LOOP16, I1{}, I0{});    // E = V G^T
-              score(acc + C::OFF_FP, IntC<C::SLOT_TV>{}, lp + C::SLOT_G * LOOP16, I1{}, I0{});  // FP = tV G^T
-              if constexpr (HAS_GO) score(acc + C::OFF_FP, IntC<C::SLOT_V>{}, lp + C::SLOT_GO * LOOP16, I0{}, I0{});
+          if (!part_b) {
+            if constexpr (OWN_KEYS) {
+              if constexpr (HAS_GT) {
+                score(acc + C::OFF_S, IntC<C::SLOT_K>{}, lp + C::SLOT_Q * LOOP16, I1{}, I1{});    // [S|TS] = K [Q;tQ]^T
+                score(acc + C::OFF_TS, IntC<C::SLOT_TK>{}, lp + C::SLOT_Q * LOOP16, I0{}, I0{});  // TS += tK Q^T
+              } else {
+                score(acc + C::OFF_S, IntC<C::SLOT_K>{}, lp + C::SLOT_Q * LOOP16, I1{}, I0{});    // S = K Q^T
+              }
             } else {
-              score(acc + C::OFF_S, IntC<C::SLOT_K>{}, lp + C::SLOT_Q * LOOP16, I1{}, I0{});    // S = K Q^T
-              score(acc + C::OFF_FP, IntC<C::SLOT_V>{}, lp + C::SLOT_GO * LOOP16, I1{}, I0{});  // FP = V gO^T
+              if constexpr (HAS_GT) {
+                score(acc + C::OFF_S, IntC<C::SLOT_Q>{}, lp + C::SLOT_K * LOOP16, I1{}, I1{});    // [S|TS] = Q [K;tK]^T
+                score(acc + C::OFF_TS, IntC<C::SLOT_TQ>{}, lp + C::SLOT_K * LOOP16, I0{}, I0{});  // TS += tQ K^T
+              } else {
+                score(acc + C::OFF_S, IntC<C::SLOT_Q>{}, lp + C::SLOT_K * LOOP16, I1{}, I0{});    // S = Q K^T
+              }
             }
           } else {
-            if constexpr (HAS_GT) {
-              score(acc + C::OFF_S, IntC<C::SLOT_Q>{}, lp + C::SLOT_K * LOOP16, I1{}, I1{});    // [S|TS] = Q [K;tK]^T
-              score(acc + C::OFF_TS, IntC<C::SLOT_TQ>{}, lp + C::SLOT_K * LOOP16, I0{}, I0{});  // TS += tQ K^T
-              score(acc + C::OFF_E, IntC<C::SLOT_G>{}, lp + C::SLOT_V * LOOP16, I1{}, I1{});    // [E|FP] = G [V;tV]^T
-              if constexpr (HAS_GO) score(acc + C::OFF_FP, IntC<C::SLOT_GO>{}, lp + C::SLOT_V * LOOP16, I0{}, I0{});
+            if constexpr (OWN_KEYS) {
+              if constexpr (HAS_GT) {
+                score(acc + C::OFF_E, IntC<C::SLOT_V>{}, lp + C::SLOT_G * LOOP16, I1{}, I0{});    // E = V G^T
+                score(acc + C::OFF_FP, IntC<C::SLOT_TV>{}, lp + C::SLOT_G * LOOP16, I1{}, I0{});  // FP = tV G^T
+                if constexpr (HAS_GO) score(acc + C::OFF_FP, IntC<C::SLOT_V>{}, lp + C::SLOT_GO * LOOP16, I0{}, I0{});
+              } else {
+                score(acc + C::OFF_FP, IntC<C::SLOT_V>{}, lp + C::SLOT_GO * LOOP16, I1{}, I0{});  // FP = V gO^T
+              }
             } else {
-              score(acc + C::OFF_S, IntC<C::SLOT_Q>{}, lp + C::SLOT_K * LOOP16, I1{}, I0{});    // S = Q K^T
-              score(acc + C::OFF_FP, IntC<C::SLOT_GO>{}, lp + C::SLOT_V * LOOP16, I1{}, I0{});  // FP = gO V^T
+              if constexpr (HAS_GT) {
+                score(acc + C::OFF_E, IntC<C::SLOT_G>{}, lp + C::SLOT_V * LOOP16, I1{}, I1{});    // [E|FP] = G [V;tV]^T
+                if constexpr (HAS_GO) score(acc + C::OFF_FP, IntC<C::SLOT_GO>{}, lp + C::SLOT_V * LOOP16, I0{}, I0{});
+              } else {
+                score(acc + C::OFF_FP, IntC<C::SLOT_GO>{}, lp + C::SLOT_V * LOOP16, I1{}, I0{});  // FP = gO V^T
+              }
             }
           }
           tc_commit_u32(bar_s_full + cs.sf_bar);
-          TRACE(g, r * 4 + 1);
+          TRACE(g, r * 4 + (part_b ? 3 : 1));
           cs.advance(2);
         }
         if (!ok) break;
@@ -462,7 +477,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         gbase = g_end;
         ++kact;
       }
-    } else if (lane == 0 && (warp == 3 || OWN_KEYS)) {
+    } else if (lane == 0 && (warp == 3 || (OWN_KEYS && warp == 12))) {
       // ---------------- second stage: one output accumulator through all sub-tiles
       const bool second = warp == 12;  // dV
       Cursor co(0);
@@ -490,7 +505,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             break;
           }
           tc_fence_after();
-          TRACE(g, second ? 10 : 6);
+          TRACE(g, second ? 10 : 8);
           const uint32_t lp = ring_lo + co.st_tile;
           const uint32_t opnd = tmem + co.buf_col;
           const uint32_t acc = s > 0;
@@ -509,7 +524,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             if constexpr (HAS_GT) outer(C::COL_OUT0, opnd + C::OFF_E, lp + C::SLOT_TK * LOOP16, 1);     // dQ += gtS tK
           }
           tc_commit_u32(bar_loop_empty + co.st_bar);
-          TRACE(g, second ? 11 : 7);
+          TRACE(g, second ? 11 : 9);
           co.advance(1);
         }
         if (ok) tc_commit(done);
