@@ -97,15 +97,26 @@ __device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float
 
 #ifdef JVPFA_TC5_PROFILE
 // Event trace of CTA 0 (experiment flag): clock64 at fixed points of sub-tiles [G0, G0 + W).
-constexpr int kTraceG0 = 16, kTraceW = 24, kTraceEv = 20;
+#ifndef JVPFA_TRACE_G0
+#define JVPFA_TRACE_G0 16
+#endif
+constexpr int kTraceG0 = JVPFA_TRACE_G0, kTraceW = 24, kTraceEv = 20;
 __device__ long long g_bwd_trace[2][kTraceW * kTraceEv];
 #define TRACE(g, ev)                                                                 \
   do {                                                                               \
     if (blockIdx.x == 0 && (g) >= kTraceG0 && (g) < kTraceG0 + kTraceW)              \
       g_bwd_trace[OWN_KEYS ? 0 : 1][((g) - kTraceG0) * kTraceEv + (ev)] = clock64(); \
   } while (0)
+// Per-item time line of three CTAs: [0] kernel start, [1 + 2k] item k's first s_full seen, [2 + 2k] item k stored.
+__device__ long long g_bwd_items[2][3][24];
+#define ITEM_TRACE(idx)                                                                           \
+  do {                                                                                            \
+    const int slot_ = blockIdx.x == 0 ? 0 : (blockIdx.x == 73 ? 1 : (blockIdx.x == 147 ? 2 : -1)); \
+    if (slot_ >= 0 && (idx) < 24) g_bwd_items[OWN_KEYS ? 0 : 1][slot_][(idx)] = clock64();        \
+  } while (0)
 #else
 #define TRACE(g, ev)
+#define ITEM_TRACE(idx)
 #endif
 
 // One work item of the persistent loop.
@@ -137,7 +148,8 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   uint64_t* own_ready = own_free + 2;
   uint64_t* done = own_ready + 1;
   uint64_t* out_free = done + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_free + 1);
+  uint64_t* stat_full = out_free + 1;        // [STAGES] (own keys: row statistics of the stage are in place)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_full + STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -192,8 +204,10 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   };
 
   if (tid == 0) {
+    ITEM_TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(loop_full + s, 1);
+      mbar_init(stat_full + s, 1);
       mbar_init(loop_empty + s, C::N_OUT_ISSUERS);
     }
     for (int b = 0; b < C::N_SFULL; ++b) mbar_init(s_full + b, 2);  // the two score threads of a sub-tile
@@ -260,61 +274,86 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       const bool have_next = next_active(k2, nxt);
       bool next_loaded = !have_next;
       const size_t stat_off = (size_t)it.bh * L;
-      for (int s = 0; s < it.n_sub; ++s) {
-        // The next item's own tiles go out once the ring is full: by then its staging half is free.
-        if (s == STAGES && !next_loaded) {
-          ok = load_own(nxt, kact + 1);
-          next_loaded = true;
-          if (!ok) break;
+      // Own keys: the row statistics of the streamed queries, one query per lane, negated and stored
+      // pairwise for the packed arithmetic.  A global load takes longer than a sub-tile, and this loop
+      // has nothing else to wait for, so the loads are issued for CH sub-tiles at a time, one chunk
+      // ahead of their use.
+      constexpr int CH = 4;
+      struct Stat {  // raw values: the arithmetic waits until they are used, not until they are loaded
+        float lse, delta, mu, eps, cterm;
+      };
+      auto load_stats = [&](int s_first, Stat(&r)[CH]) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int i = it.loop_begin + (s_first + j) * BL + lane;
+          r[j] = Stat{INFINITY, 0.f, 0.f, 0.f, 0.f};
+          if (s_first + j < it.n_sub && i < L) {
+            r[j].lse = a.lse[stat_off + i];
+            r[j].delta = a.delta[stat_off + i];
+            if constexpr (HAS_GT) {
+              r[j].mu = a.mu[stat_off + i];
+              r[j].eps = a.eps[stat_off + i];
+              r[j].cterm = a.cterm[stat_off + i];
+            }
+          }
         }
-        const int g = gbase + s;
-        const int st = g % STAGES;
-        const uint32_t ph = (g / STAGES) & 1;
-        if (!mbar_wait(loop_empty + st, ph ^ 1, ab, kAbortBwdLoopEmpty)) {
-          ok = false;
-          break;
+      };
+      auto put_stats = [&](int st, const Stat& v) {
+        float* base = reinterpret_cast<float*>(sStat + (st * (BL / 2) + (lane >> 1)) * 2);
+        base[(lane & 1)] = -v.lse;      // float4 A = (-lse0, -lse1, -mu0, -mu1)
+        base[2 + (lane & 1)] = -v.mu;
+        base[4 + (lane & 1)] = -v.eps;  // float4 B = (-eps0, -eps1, -sub0, -sub1)
+        base[6 + (lane & 1)] = -(v.delta + v.cterm + v.eps * v.mu);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stat_full + st);
+      };
+      Stat cur[CH], ahead[CH];
+      if constexpr (OWN_KEYS) load_stats(0, cur);
+      for (int s0 = 0; ok && s0 < it.n_sub; s0 += CH) {
+        if constexpr (OWN_KEYS) load_stats(s0 + CH, ahead);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int s = s0 + j;
+          if (!ok || s >= it.n_sub) continue;
+          // The next item's own tiles go out once the ring is full: by then its staging half is free.
+          if (s == STAGES && !next_loaded) {
+            ok = load_own(nxt, kact + 1);
+            next_loaded = true;
+            if (!ok) continue;
+          }
+          const int g = gbase + s;
+          const int st = g % STAGES;
+          const uint32_t ph = (g / STAGES) & 1;
+          if (!mbar_wait(loop_empty + st, ph ^ 1, ab, kAbortBwdLoopEmpty)) {
+            ok = false;
+            continue;
+          }
+          const int l0 = it.loop_begin + s * BL;
+          if (lane == 0) TRACE(g, 18);
+          if (lane == 0) {
+            unsigned char* base = sLoop + st * C::STAGE_BYTES;
+            mbar_expect_tx(loop_full + st, C::STAGE_BYTES);
+            if constexpr (OWN_KEYS) {
+              tma_load_3d(base + C::SLOT_Q * C::LOOP_BYTES, &maps.q, loop_full + st, 0, l0, it.bh);
+              if constexpr (HAS_GO) tma_load_3d(base + C::SLOT_GO * C::LOOP_BYTES, &maps.go, loop_full + st, 0, l0, it.bh);
+              if constexpr (HAS_GT) {
+                tma_load_3d(base + C::SLOT_TQ * C::LOOP_BYTES, &maps.tq, loop_full + st, 0, l0, it.bh);
+                tma_load_3d(base + C::SLOT_G * C::LOOP_BYTES, &maps.g, loop_full + st, 0, l0, it.bh);
+              }
+            } else {
+              tma_load_3d(base + C::SLOT_K * C::LOOP_BYTES, &maps.k, loop_full + st, 0, l0, it.bh);
+              tma_load_3d(base + C::SLOT_V * C::LOOP_BYTES, &maps.v, loop_full + st, 0, l0, it.bh);
+              if constexpr (HAS_GT) {
+                tma_load_3d(base + C::SLOT_TK * C::LOOP_BYTES, &maps.tk, loop_full + st, 0, l0, it.bh);
+                tma_load_3d(base + C::SLOT_TV * C::LOOP_BYTES, &maps.tv, loop_full + st, 0, l0, it.bh);
+              }
+            }
+          }
+          if constexpr (OWN_KEYS) put_stats(st, cur[j]);
         }
-        const int l0 = it.loop_begin + s * BL;
         if constexpr (OWN_KEYS) {
-          // One query per lane: negated statistics, stored pairwise for the packed arithmetic.
-          const int i = l0 + lane;
-          float nlse = -INFINITY, nmu = 0.f, neps = 0.f, nsub = 0.f;
-          if (i < L) {
-            nlse = -a.lse[stat_off + i];
-            float sub = a.delta[stat_off + i];
-            if constexpr (HAS_GT) {
-              const float mu = a.mu[stat_off + i], eps = a.eps[stat_off + i];
-              nmu = -mu;
-              neps = -eps;
-              sub += a.cterm[stat_off + i] + eps * mu;
-            }
-            nsub = -sub;
-          }
-          float* base = reinterpret_cast<float*>(sStat + (st * (BL / 2) + (lane >> 1)) * 2);
-          base[(lane & 1)] = nlse;      // float4 A = (-lse0, -lse1, -mu0, -mu1)
-          base[2 + (lane & 1)] = nmu;
-          base[4 + (lane & 1)] = neps;  // float4 B = (-eps0, -eps1, -sub0, -sub1)
-          base[6 + (lane & 1)] = nsub;
-          __syncwarp();
-        }
-        if (lane == 0) {
-          unsigned char* base = sLoop + st * C::STAGE_BYTES;
-          mbar_expect_tx(loop_full + st, C::STAGE_BYTES);
-          if constexpr (OWN_KEYS) {
-            tma_load_3d(base + C::SLOT_Q * C::LOOP_BYTES, &maps.q, loop_full + st, 0, l0, it.bh);
-            if constexpr (HAS_GO) tma_load_3d(base + C::SLOT_GO * C::LOOP_BYTES, &maps.go, loop_full + st, 0, l0, it.bh);
-            if constexpr (HAS_GT) {
-              tma_load_3d(base + C::SLOT_TQ * C::LOOP_BYTES, &maps.tq, loop_full + st, 0, l0, it.bh);
-              tma_load_3d(base + C::SLOT_G * C::LOOP_BYTES, &maps.g, loop_full + st, 0, l0, it.bh);
-            }
-          } else {
-            tma_load_3d(base + C::SLOT_K * C::LOOP_BYTES, &maps.k, loop_full + st, 0, l0, it.bh);
-            tma_load_3d(base + C::SLOT_V * C::LOOP_BYTES, &maps.v, loop_full + st, 0, l0, it.bh);
-            if constexpr (HAS_GT) {
-              tma_load_3d(base + C::SLOT_TK * C::LOOP_BYTES, &maps.tk, loop_full + st, 0, l0, it.bh);
-              tma_load_3d(base + C::SLOT_TV * C::LOOP_BYTES, &maps.tv, loop_full + st, 0, l0, it.bh);
-            }
-          }
+#pragma unroll
+          for (int j = 0; j < CH; ++j) cur[j] = ahead[j];
         }
       }
       if (ok && !next_loaded) ok = load_own(nxt, kact + 1);
@@ -420,6 +459,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             }
             cf.advance(2);
           }
+          if (!part_b) TRACE(g, 17);
           if (!mbar_wait_u32(bar_loop_full + cs.st_bar, cs.st_par, ab, kAbortBwdLoopFull)) {
             ok = false;
             break;
@@ -617,7 +657,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         const uint32_t tbuf = tbase + buf * C::COL_BUF;
         const int l0 = it.loop_begin + s * BL;
         if constexpr (OWN_KEYS) {
-          if (!mbar_wait(loop_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull)) {
+          if (!mbar_wait(stat_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull)) {
             alive = false;
             break;
           }
@@ -628,6 +668,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         }
         tc_fence_after();
         if (row == 0) TRACE(g, 12);
+        if (tid == 128 && (g & 7) == 0) ITEM_TRACE(1 + g / 8);
         // Masking by index comparison; columns outside [col_lo, col_hi) get p = 0.
         //   own keys   : (key j = own_idx, query i = l0 + col) is dead if j >= n_valid, or causal and j > i
         //   own queries: (query i = own_idx, key j = l0 + col) is dead if j >= n_valid, or causal and j > i
@@ -825,6 +866,9 @@ static int launch_t64(const jvpfa_bwd_args& a, cudaStream_t s) {
 }  // namespace tc5
 
 #ifdef JVPFA_TC5_PROFILE
+extern "C" int jvpfa_debug_read_items(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, tc5::g_bwd_items, sizeof(long long) * 2 * 3 * 24);
+}
 extern "C" int jvpfa_debug_read_trace(long long* out, int which) {
   return (int)cudaMemcpyFromSymbol(out, tc5::g_bwd_trace, sizeof(long long) * tc5::kTraceW * tc5::kTraceEv,
                                    sizeof(long long) * tc5::kTraceW * tc5::kTraceEv * which);
