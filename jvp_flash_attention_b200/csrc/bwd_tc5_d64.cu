@@ -70,7 +70,7 @@ struct Bwd64Cfg {
   static constexpr int N_QRY_TILES = 1 + (HAS_GO ? 1 : 0) + (HAS_GT ? 2 : 0);
   static constexpr int N_OWN = OWN_KEYS ? N_KEY_TILES : N_QRY_TILES;
   static constexpr int N_LOOP = OWN_KEYS ? N_QRY_TILES : N_KEY_TILES;
-  static constexpr int N_OWN_TMEM = OWN_KEYS ? 0 : (HAS_GT ? 2 : 1);  // own queries: Q (, tQ) as TMEM operands
+  static constexpr int N_OUT_BUF = OWN_KEYS ? 1 : 2;  // own queries: dQ accumulator exists twice
   static constexpr int LOOP_BYTES = BL * D * 2;  // 4 KiB
   static constexpr int OWN_BYTES = OWN * D * 2;  // 16 KiB
   static constexpr int STAGE_BYTES = N_LOOP * LOOP_BYTES;
@@ -85,7 +85,7 @@ struct Bwd64Cfg {
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
   static constexpr int COL_BUF = 128;  // columns per accumulator buffer
   static constexpr int OFF_S = 0, OFF_TS = 32, OFF_E = 64, OFF_FP = HAS_GT ? 96 : 32;
-  static constexpr int COL_OUT0 = NBUF * COL_BUF, COL_OUT1 = COL_OUT0 + 64, COL_OWN = COL_OUT0 + 64;
+  static constexpr int COL_OUT0 = NBUF * COL_BUF, COL_OUT1 = COL_OUT0 + 64;  // own queries: second dQ at COL_OUT1
   static constexpr int COLS_ALLOC = 512;
   // Tile slots (staging tiles of the own side, ring tiles of the streamed side, TMEM operand slots).
   // K|tK, V|tV and Q|tQ are neighbours so that one N=64 instruction can take both as its B operand.
@@ -145,10 +145,9 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   uint64_t* p_full = s_full + C::N_SFULL;    // [NBUF]
   uint64_t* own_staged = p_full + NBUF;      // [2]
   uint64_t* own_free = own_staged + 2;       // [2]
-  uint64_t* own_ready = own_free + 2;
-  uint64_t* done = own_ready + 1;
-  uint64_t* out_free = done + 1;
-  uint64_t* stat_full = out_free + 1;        // [STAGES] (own keys: row statistics of the stage are in place)
+  uint64_t* done = own_free + 2;             // [2] (per output buffer)
+  uint64_t* out_free = done + 2;             // [2] (per output buffer)
+  uint64_t* stat_full = out_free + 2;        // [STAGES] (own keys: row statistics of the stage are in place)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_full + STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -212,14 +211,13 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     }
     for (int b = 0; b < C::N_SFULL; ++b) mbar_init(s_full + b, 2);  // the two score threads of a sub-tile
     for (int b = 0; b < NBUF; ++b) mbar_init(p_full + b, 128);
-    // The score threads take part in one per-item barrier each (own_free or done, see below).
+    // The score threads take part in own_free (see below).
     for (int h = 0; h < 2; ++h) {
       mbar_init(own_staged + h, 1);
-      mbar_init(own_free + h, 256 + (OWN_KEYS ? C::N_SCORE_THREADS : 0));
+      mbar_init(own_free + h, 256 + C::N_SCORE_THREADS);
+      mbar_init(out_free + h, 256);
+      mbar_init(done + h, C::N_OUT_ISSUERS);
     }
-    mbar_init(own_ready, 256);
-    mbar_init(done, C::N_OUT_ISSUERS + (OWN_KEYS ? 0 : C::N_SCORE_THREADS));
-    mbar_init(out_free, 256);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -398,7 +396,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     const uint32_t bar_loop_full = smem_u32(loop_full), bar_loop_empty = smem_u32(loop_empty);
     const uint32_t bar_s_full = smem_u32(s_full), bar_p_full = smem_u32(p_full);
     const uint32_t ring_lo = kDescLo | (smem_u32(sLoop) >> 4);
-    const uint32_t own_col = tmem + C::COL_OWN;
 
     if (lane == 0 && (warp == 1 || warp == 2 || warp >= 13)) {
       // ---------------- scores of the sub-tiles g = r, r + 2, r + 4, ...
@@ -416,17 +413,10 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         constexpr uint32_t id = wide ? idesc_sc2 : idesc_sc;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          if constexpr (slot < C::N_OWN_TMEM) {
-            if (first && ks == 0)
-              umma_ts_lo<false>(d, own_col + slot * 32 + ks * 8, b_lo + ks * 2, id);
-            else
-              umma_ts_lo<true>(d, own_col + slot * 32 + ks * 8, b_lo + ks * 2, id);
-          } else {
-            if (first && ks == 0)
-              umma_ss_lo<false>(d, own_lo + slot * OWN16 + ks * 2, b_lo + ks * 2, id);
-            else
-              umma_ss_lo<true>(d, own_lo + slot * OWN16 + ks * 2, b_lo + ks * 2, id);
-          }
+          if (first && ks == 0)
+            umma_ss_lo<false>(d, own_lo + slot * OWN16 + ks * 2, b_lo + ks * 2, id);
+          else
+            umma_ss_lo<true>(d, own_lo + slot * OWN16 + ks * 2, b_lo + ks * 2, id);
         }
       };
       using I0 = IntC<0>;
@@ -438,13 +428,9 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         if (!get_item(k, it)) continue;
         if (it.n_sub == 0) continue;
         const int g_end = gbase + it.n_sub;
-        // This item's own operands: the staging half (own keys), the packed rows in TMEM (own queries).
-        // Waited for even when none of the item's sub-tiles is this thread's: a parity wait is only
-        // safe for a thread that sees every phase of the barrier.
-        if constexpr (OWN_KEYS)
-          ok = mbar_wait(own_staged + (kact & 1), (kact >> 1) & 1, ab, kAbortBwdOwn);
-        else
-          ok = mbar_wait(own_ready, kact & 1, ab, kAbortBwdOwn);
+        // This item's own operands: its staging half.  Waited for even when none of the item's sub-tiles
+        // is this thread's: a parity wait is only safe for a thread that sees every phase of the barrier.
+        ok = mbar_wait(own_staged + (kact & 1), (kact >> 1) & 1, ab, kAbortBwdOwn);
         if (!ok) break;
         tc_fence_after();
         own_lo = kDescLo | (smem_u32(sOwn + (kact & 1) * C::STAGING_HALF) >> 4);
@@ -507,13 +493,9 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           cs.advance(2);
         }
         if (!ok) break;
-        // "This thread is through with the item": keeps the per-item barrier it waits on from running
-        // more than one phase ahead of it.  Own keys: the staging half is not refilled before (own_free);
-        // own queries: the next item's rows are not written to TMEM before (done).
-        if constexpr (OWN_KEYS)
-          mbar_arrive(own_free + (kact & 1));
-        else
-          mbar_arrive(done);
+        // "This thread is through with the item": the staging half is not refilled before, so its
+        // barrier cannot run more than one phase ahead of this thread.
+        mbar_arrive(own_free + (kact & 1));
         gbase = g_end;
         ++kact;
       }
@@ -538,9 +520,10 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             ok = false;
             break;
           }
-          // The first sub-tile overwrites the output accumulators: the previous item's epilogue must
-          // have read them.
-          if (s == 0 && kact > 0 && !mbar_wait(out_free, (kact - 1) & 1, ab, kAbortBwdDone)) {
+          // The first sub-tile overwrites the output accumulators: the epilogue of the item that used
+          // them last must have read them.
+          if (s == 0 && kact >= C::N_OUT_BUF &&
+              !mbar_wait(out_free + kact % C::N_OUT_BUF, (kact / C::N_OUT_BUF - 1) & 1, ab, kAbortBwdDone)) {
             ok = false;
             break;
           }
@@ -560,14 +543,15 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
               outer(C::COL_OUT1, opnd + C::OFF_S, lp + C::SLOT_GO * LOOP16, acc);                        // dV += P^T gO
             }
           } else {
-            outer(C::COL_OUT0, opnd + C::OFF_FP, lp + C::SLOT_K * LOOP16, acc);                          // dQ += gS K
-            if constexpr (HAS_GT) outer(C::COL_OUT0, opnd + C::OFF_E, lp + C::SLOT_TK * LOOP16, 1);     // dQ += gtS tK
+            const uint32_t oc = C::COL_OUT0 + 64 * (kact & 1);
+            outer(oc, opnd + C::OFF_FP, lp + C::SLOT_K * LOOP16, acc);                                   // dQ += gS K
+            if constexpr (HAS_GT) outer(oc, opnd + C::OFF_E, lp + C::SLOT_TK * LOOP16, 1);              // dQ += gtS tK
           }
           tc_commit_u32(bar_loop_empty + co.st_bar);
           TRACE(g, second ? 11 : 9);
           co.advance(1);
         }
-        if (ok) tc_commit(done);
+        if (ok) tc_commit(done + kact % C::N_OUT_BUF);
         ++kact;
       }
     }
@@ -597,6 +581,34 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         reinterpret_cast<uint4*>(gp)[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
     };
 
+    // Item epilogue: read this group's half of the output accumulators, release them, store.
+    int pend_kact = -1, pend_bh = 0, pend_own_idx = 0;
+    auto epilogue = [&]() -> bool {
+      const int pk = pend_kact;
+      pend_kact = -1;
+      // (done and out_free exist per output buffer: with two buffers an item can complete without one
+      // of the elementwise groups, and a parity wait must not fall two phases behind)
+      if (!mbar_wait(done + pk % C::N_OUT_BUF, (pk / C::N_OUT_BUF) & 1, ab, kAbortBwdDone)) {
+        alive = false;
+        return false;
+      }
+      tc_fence_after();
+      uint32_t r0[32];
+      uint32_t r1[OWN_KEYS ? 32 : 1];
+      tmem_ld32(tbase + C::COL_OUT0 + (OWN_KEYS ? 0 : 64 * (pk & 1)) + 32 * wg, r0);
+      if constexpr (OWN_KEYS) tmem_ld32(tbase + C::COL_OUT1 + 32 * wg, r1);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(out_free + pk % C::N_OUT_BUF);
+      mbar_arrive(own_free + (pk & 1));  // every MMA of the item is complete: its staging half is free
+      if constexpr (OWN_KEYS) {
+        store_half(a.dk, pend_bh, pend_own_idx, r0, a.sm_scale);
+        store_half(a.dv, pend_bh, pend_own_idx, r1, 1.f);
+      } else {
+        store_half(a.dq, pend_bh, pend_own_idx, r0, a.sm_scale);
+      }
+      return true;
+    };
     for (int k = 0; alive && k < k_max; ++k) {
       if (!get_item(k, it)) continue;
       const int own_idx = it.own0 + row;
@@ -618,24 +630,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
 
       float r_nlse = -INFINITY, r_nmu = 0.f, r_neps = 0.f, r_nsub = 0.f;
       if constexpr (!OWN_KEYS) {
-        // ---- own query rows Q (, tQ): staging half (128-byte-swizzled TMA tiles) -> TMEM, packed ----
-        if (!mbar_wait(own_staged + (kact & 1), (kact >> 1) & 1, ab, kAbortBwdOwn)) {
-          alive = false;
-          break;
-        }
-        if (wg < C::N_OWN_TMEM) {
-          uint32_t r[32];
-          const unsigned char* src = sOwn + (kact & 1) * C::STAGING_HALF + wg * C::OWN_BYTES + row * 128;
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const uint4 v = *reinterpret_cast<const uint4*>(src + ((x ^ (row & 7)) << 4));
-            r[4 * x] = v.x, r[4 * x + 1] = v.y, r[4 * x + 2] = v.z, r[4 * x + 3] = v.w;
-          }
-          tmem_st32(tbase + C::COL_OWN + wg * 32, r);
-          tmem_wait_st();
-        }
-        tc_fence_before();
-        mbar_arrive(own_ready);
         // row statistics, negated
         if (own_idx < L) {
           r_nlse = -a.lse[stat_off + own_idx];
@@ -741,34 +735,17 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         tc_fence_before();
         mbar_arrive(p_full + buf);
         if (row == 0) TRACE(g, 15);
+        if (pend_kact >= 0 && !epilogue()) break;
       }
       if (!alive) break;
-
-      // ---- item epilogue: read this group's half of the output accumulators, release them, store ----
-      if (!mbar_wait(done, kact & 1, ab, kAbortBwdDone)) {
-        alive = false;
-        break;
-      }
-      tc_fence_after();
-      {
-        uint32_t r0[32];
-        uint32_t r1[OWN_KEYS ? 32 : 1];
-        tmem_ld32(tbase + C::COL_OUT0 + 32 * wg, r0);
-        if constexpr (OWN_KEYS) tmem_ld32(tbase + C::COL_OUT1 + 32 * wg, r1);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(out_free);
-        mbar_arrive(own_free + (kact & 1));  // every MMA of the item is complete: its staging half is free
-        if constexpr (OWN_KEYS) {
-          store_half(a.dk, it.bh, own_idx, r0, a.sm_scale);
-          store_half(a.dv, it.bh, own_idx, r1, 1.f);
-        } else {
-          store_half(a.dq, it.bh, own_idx, r0, a.sm_scale);
-        }
-      }
+      // The item's epilogue is deferred until this group has worked on its first sub-tile of the next
+      // item: the wait for the item's last MMAs is then covered by useful work.
+      if (pend_kact >= 0 && !epilogue()) break;
+      pend_kact = kact, pend_bh = it.bh, pend_own_idx = own_idx;
       gbase += it.n_sub;
       ++kact;
     }
+    if (alive && pend_kact >= 0) epilogue();
   }
 
   tc_fence_before();
