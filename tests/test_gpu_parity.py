@@ -164,6 +164,41 @@ def test_tcgen05_forward_against_oracle_and_generic_family(dt, B, H, L, D, kind,
     assert orc.max_abs_err(lse, lse2) < 1e-4
 
 
+PERSISTENT_CASES = [
+    # cotangents, mask kind, dtype, B, H, L: more work items than a B200 has SMs, so that every CTA of
+    # the persistent backward walks several items; short items (1 to 5 sub-tiles of 32 rows), odd
+    # sub-tile counts, items without any live key, all three cotangent modes
+    ("gt", "kvlen", "bf16", 40, 12, 96), ("both", "kvlen", "fp16", 40, 12, 128), ("go", "causal", "bf16", 40, 12, 160),
+    ("gt", "none", "bf16", 64, 12, 32), ("both", "none", "bf16", 8, 12, 1024), ("gt", "causal", "fp16", 24, 8, 224),
+]
+
+
+@pytest.mark.parametrize("cot,kind,dt,B,H,L", PERSISTENT_CASES)
+def test_tcgen05_backward_many_items_per_cta(cot, kind, dt, B, H, L):
+    """The persistent tcgen05 backward (D = 64) against the register-tiled family on the same inputs,
+    in shapes where each CTA processes a list of work items and the barrier phases carry over from
+    one item to the next.  The bounded waits inside the kernel must not have given up."""
+    dtype = DT[dt]
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, 64, dtype, seed=B + L)
+    go = go if cot in ("go", "both") else None
+    gto = gto if cot in ("gt", "both") else None
+    mask, causal = _mask(kind, B, H, L, dtype, seed=L)
+    *_, dq, dk, dv = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_TCGEN05)
+    assert _lib.device_status() == 0, "a bounded wait inside the tcgen05 kernel gave up"
+    *_, dq2, dk2, dv2 = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC)
+    for name, a, b in (("dq", dq, dq2), ("dk", dk, dk2), ("dv", dv, dv2)):
+        assert torch.isfinite(a.float()).all(), name
+        _close(a, b.float(), dtype, name)
+    # one (batch, head) slice against the float64 oracle
+    sl = lambda x: None if x is None else x[B - 1:, H - 1:]  # noqa: E731
+    msl = None if mask is None else mask[B - 1:]
+    _, _, rdq, rdk, rdv = orc.grads_through_both(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), sl(go), sl(gto),
+                                                 attn_mask=msl, causal=causal)
+    _close(dq[B - 1:, H - 1:], rdq, dtype, "dq")
+    _close(dk[B - 1:, H - 1:], rdk, dtype, "dk")
+    _close(dv[B - 1:, H - 1:], rdv, dtype, "dv")
+
+
 def test_tcgen05_dispatch_rules():
     """AUTO takes the tcgen05 kernels exactly for 16-bit, D in {64,128}, none/causal/key-padding."""
     import ctypes as C
