@@ -34,6 +34,11 @@ if str(ROOT) not in sys.path:
 
 METRIC = "fwd_dual+bwd TFLOP/s (bf16 causal B4 H16 L2048 D64; algorithmic MMA flops)"
 CPU_SAMPLE_HEADS = 8
+DEFAULT_WORKLOAD = "c2_bf16_causal"
+# DRAM bytes (read + write) per C-ABI call on the default workload, from one ncu --set full capture of each kernel
+# (profiles/tc5_kernels_c2_bf16_causal.md): forward 100.7 + 17.7 MB; backward = own-keys launch 123.6 + 14.3 MB
+# plus own-queries launch 171.0 + 9.2 MB.
+NCU_DRAM_BYTES = {"fwd_dual": 118.4e6, "bwd": 318.1e6}
 
 
 def _peaks():
@@ -358,7 +363,10 @@ def run_ours(args, rank, world, local):
                          "jvpfa_bwd (bwd_tc5_d64_kernel own-keys + own-queries launches, timed as one call; "
                          "10 algorithmic MMAs, 15 executed because both launches recompute the score tiles)",
                          "achieved": ach, "peak": peaks["burst"],
-                         "unit": "TFLOP/s", "frac": ach / peaks["burst"], "traffic": None,
+                         "unit": "TFLOP/s", "frac": ach / peaks["burst"],
+                         # dram__bytes_read.sum + dram__bytes_write.sum per call from the committed ncu capture of
+                         # this same workload (profiles/tc5_kernels_c2_bf16_causal.md); algorithmic minimum 138 MB
+                         "traffic": (NCU_DRAM_BYTES[dom] if args.workload == DEFAULT_WORKLOAD else None),
                          "peak_source": f"{peaks['src']} bf16 burst (kernel timed alone)",
                          "ms_per_launch": br[dom], "algorithmic_flops_per_launch": stage_flops[dom]},
             "breakdown_ms": br,
@@ -381,7 +389,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--skip-e2e", action="store_true", help="stop after the device-resident part (profiling runs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2_bf16_causal")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank, world, local = _dist_init(args.gpus)
