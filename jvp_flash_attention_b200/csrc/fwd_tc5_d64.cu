@@ -8,7 +8,10 @@
 //   issuer A:  [S | tS] = Q [K ; tK]^T  (N=128) ;  tS += tQ K^T  (N=64)         -> s_full
 //   issuer B:  [O | tO'] += P [V | tV]  (N=128) ;  tO' += W V    (N=64)         -> kv_empty[stage]
 //
-// CTA = one 128-row query tile of one (batch, head); 7 warps: TMA producer, issuer A, issuer B,
+// Work item = one 128-row query tile of one (batch, head).  The CTAs are persistent (two per SM):
+// each walks a static list of items, so barriers and TMEM are set up once, the next item's Q and
+// first key tiles are on their way while the current item finishes, and an item's epilogue runs
+// behind the softmax of the next item's first tile.  7 warps: TMA producer, issuer A, issuer B,
 // four softmax / epilogue warps (thread <-> query row <-> TMEM lane).  TMEM columns:
 //   S [64] | tS [64] | O [64] | tO' [64]   (256 columns -> two CTAs per SM)
 // P and W = P*tS*scale are written as packed 16-bit values over the head of S and tS and feed
@@ -33,7 +36,8 @@ struct Fwd64Cfg {
   // stage layout: K, tK, V, tV (DUAL) or K, V
   static constexpr int SLOT_K = 0, SLOT_TK = 1, SLOT_V = DUAL ? 2 : 1, SLOT_TV = 3;
   static constexpr int TILE_BYTES = N_Q * Q_BYTES + STAGES * N_KV * KV_BYTES;
-  static constexpr int SMEM_BYTES = TILE_BYTES + 256 + 1024;
+  static constexpr int PEND_BYTES = 128 * 3 * 4;  // running statistics of the item whose epilogue is pending
+  static constexpr int SMEM_BYTES = TILE_BYTES + 256 + PEND_BYTES + 1024;
   static constexpr int COL_S = 0;
   static constexpr int COL_TS = 64;
   static constexpr int COL_O = DUAL ? 128 : 64;
@@ -45,16 +49,12 @@ struct Fwd64Maps {
   CUtensorMap q, tq, k, tk, v, tv;
 };
 
-#ifdef JVPFA_TC5_PROFILE
-__device__ unsigned long long g_fprof[32];
-#define FPROF_T0(v) long long v = clock64()
-#define FPROF_ACC(var, v) var += clock64() - (v)
-#else
-#define FPROF_T0(v)
-#define FPROF_ACC(var, v)
-#endif
-
 __device__ __forceinline__ float2 ff2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+
+// One work item of the persistent loop: a 128-row query tile of one (batch, head).
+struct FwdItem {
+  int bh, m0, n_valid, n_tiles;
+};
 
 template <typename T, bool DUAL>
 __global__ void __launch_bounds__(224, 2)
@@ -77,24 +77,44 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
   uint64_t* s_full = bars + 1 + 2 * STAGES;
   uint64_t* p_full = s_full + 1;
   uint64_t* o_full = s_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 3);
+  uint64_t* q_empty = s_full + 3;  // issuer A has read the item's Q tiles
+  uint64_t* o_free = s_full + 4;   // the epilogue has read the item's accumulators
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
+  float* sPend = reinterpret_cast<float*>(smem + C::TILE_BYTES + 256);  // [3][128]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
-  const int bh = blockIdx.y;
-  const int b = bh / a.H;
-  const int mt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
-  const int m0 = mt * BM;
+  const int BH = a.B * a.H;
   const bool causal = a.mask.kind == JVPFA_MASK_CAUSAL;
-  int n_valid = L;
-  if (a.mask.kind == JVPFA_MASK_KVLEN) {
-    const int n = a.mask.kv_len[b];
-    n_valid = n < 0 ? 0 : (n > L ? L : n);
-  }
-  int n_end = n_valid;
-  if (causal) n_end = min(n_end, m0 + BM);
-  const int n_tiles = (n_end + BN - 1) / BN;
+  const int n_q_tiles = (L + BM - 1) / BM;
+  const int n_items = n_q_tiles * BH;
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int k_max = (n_items + G - 1) / G;
+
+  // Item k of this CTA.  The CTAs stay resident (two per SM) and walk a static list: items are ranked
+  // heaviest first (for causal masks the last query tile is the longest) and dealt in serpentine order.
+  auto get_item = [&](int k, FwdItem& it) -> bool {
+    const int w = k * G + ((k & 1) ? (G - 1 - cta) : cta);
+    if (w >= n_items) return false;
+    if (causal) {  // heaviest query tiles first, over all heads
+      const int rank = w / BH;
+      it.bh = w - rank * BH;
+      it.m0 = (n_q_tiles - 1 - rank) * BM;
+    } else {  // equal weights: the query tiles of a head run side by side and share its K / V in L2
+      it.bh = w / n_q_tiles;
+      it.m0 = (w - it.bh * n_q_tiles) * BM;
+    }
+    it.n_valid = L;
+    if (a.mask.kind == JVPFA_MASK_KVLEN) {
+      const int n = a.mask.kv_len[it.bh / a.H];
+      it.n_valid = n < 0 ? 0 : (n > L ? L : n);
+    }
+    int n_end = it.n_valid;
+    if (causal) n_end = min(n_end, it.m0 + BM);
+    it.n_tiles = (n_end + BN - 1) / BN;
+    return true;
+  };
 
   if (tid == 0) {
     mbar_init(q_full, 1);
@@ -105,6 +125,8 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
     mbar_init(s_full, 1);
     mbar_init(p_full, 128);
     mbar_init(o_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(o_free, 128);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -118,279 +140,154 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
   const uint32_t tmem = *tmem_slot;
   const AbortState ab{abort_flag, status};
 
+  // Barrier phases run on across the items: g counts the key tiles of all items of this CTA (ring
+  // stage g % STAGES; s_full / p_full complete once per tile), kact the items that have tiles
+  // (q_full, q_empty, o_full, o_free complete once per such item).  Every role walks the same list.
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
-      tma_load_3d(sQ, &maps.q, q_full, 0, m0, bh);
-      if constexpr (DUAL) tma_load_3d(sTQ, &maps.tq, q_full, 0, m0, bh);
-      for (int it = 0; it < n_tiles; ++it) {
-        const int st = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(kv_empty + st, ph ^ 1, ab, kAbortKvEmpty)) break;
-        unsigned char* base = sKV + st * (C::N_KV * C::KV_BYTES);
-        mbar_expect_tx(kv_full + st, C::N_KV * C::KV_BYTES);
-        const int n0 = it * BN;
-        tma_load_3d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, bh);
-        tma_load_3d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, bh);
-        if constexpr (DUAL) {
-          tma_load_3d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, bh);
-          tma_load_3d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, bh);
+    if (lane == 0) {
+      prefetch_tmap(&maps.q), prefetch_tmap(&maps.k), prefetch_tmap(&maps.v);
+      if constexpr (DUAL) prefetch_tmap(&maps.tq), prefetch_tmap(&maps.tk), prefetch_tmap(&maps.tv);
+      int g = 0, kact = 0;
+      bool ok = true;
+      FwdItem it;
+      for (int k = 0; ok && k < k_max; ++k) {
+        if (!get_item(k, it) || it.n_tiles == 0) continue;
+        // The Q tiles are single-buffered: issuer A must be through with the previous item's.
+        if (kact > 0 && !mbar_wait(q_empty, (kact - 1) & 1, ab, kAbortQFull)) break;
+        mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
+        tma_load_3d(sQ, &maps.q, q_full, 0, it.m0, it.bh);
+        if constexpr (DUAL) tma_load_3d(sTQ, &maps.tq, q_full, 0, it.m0, it.bh);
+        for (int t = 0; t < it.n_tiles; ++t, ++g) {
+          const int st = g % STAGES;
+          const uint32_t ph = (g / STAGES) & 1;
+          if (!mbar_wait(kv_empty + st, ph ^ 1, ab, kAbortKvEmpty)) {
+            ok = false;
+            break;
+          }
+          unsigned char* base = sKV + st * (C::N_KV * C::KV_BYTES);
+          mbar_expect_tx(kv_full + st, C::N_KV * C::KV_BYTES);
+          const int n0 = t * BN;
+          tma_load_3d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, it.bh);
+          tma_load_3d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, it.bh);
+          if constexpr (DUAL) {
+            tma_load_3d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, it.bh);
+            tma_load_3d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, it.bh);
+          }
         }
+        ++kact;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ issuer A: scores
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kIdesc, BM, BN, 0, 0);       // 128 x 64
       constexpr uint32_t idesc_s2 = make_idesc(Fmt<T>::kIdesc, BM, 2 * BN, 0, 0);  // 128 x 128: [S | tS]
       const uint32_t aQ = smem_u32(sQ), aTQ = smem_u32(sTQ);
-      bool ok = mbar_wait(q_full, 0, ab, kAbortQFull);
-#ifdef JVPFA_TC5_PROFILE
-      long long a_w1 = 0, a_w2 = 0, a_is = 0;
-      const long long a_t0 = clock64();
-#endif
-      for (int it = 0; ok && it < n_tiles; ++it) {
-        const int st = it % STAGES;
-        FPROF_T0(ta1);
-        // S / tS still hold P / W of the previous tile until issuer B's chain for it has completed.
-        if (it > 0 && !mbar_wait(kv_empty + ((it - 1) % STAGES), ((it - 1) / STAGES) & 1, ab, kAbortKvEmpty)) break;
-        FPROF_ACC(a_w1, ta1);
-        FPROF_T0(ta2);
-        if (!mbar_wait(kv_full + st, (it / STAGES) & 1, ab, kAbortKvFull)) break;
-        FPROF_ACC(a_w2, ta2);
-        tc_fence_after();
-        FPROF_T0(ta3);
-        const uint32_t aK = smem_u32(sKV + st * (C::N_KV * C::KV_BYTES)) + C::SLOT_K * C::KV_BYTES;
-        if constexpr (DUAL) {
+      int g = 0, kact = 0;
+      bool ok = true;
+      FwdItem it;
+      for (int k = 0; ok && k < k_max; ++k) {
+        if (!get_item(k, it) || it.n_tiles == 0) continue;
+        if (!mbar_wait(q_full, kact & 1, ab, kAbortQFull)) break;
+        for (int t = 0; t < it.n_tiles; ++t, ++g) {
+          const int st = g % STAGES;
+          // S / tS still hold P / W of the previous tile (of this item or of the one before) until
+          // issuer B's chain for it has completed.
+          if (g > 0 && !mbar_wait(kv_empty + ((g - 1) % STAGES), ((g - 1) / STAGES) & 1, ab, kAbortKvEmpty)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(kv_full + st, (g / STAGES) & 1, ab, kAbortKvFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t aK = smem_u32(sKV + st * (C::N_KV * C::KV_BYTES)) + C::SLOT_K * C::KV_BYTES;
+          if constexpr (DUAL) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)  // [S | tS] = Q [K ; tK]^T
-            umma_ss(tmem + C::COL_S, make_smem_desc(aQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
-                    idesc_s2, ks > 0);
+            for (int ks = 0; ks < D / 16; ++ks)  // [S | tS] = Q [K ; tK]^T
+              umma_ss(tmem + C::COL_S, make_smem_desc(aQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
+                      idesc_s2, ks > 0);
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)  // tS += tQ K^T
-            umma_ss(tmem + C::COL_TS, make_smem_desc(aTQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
-                    idesc_s, 1);
-        } else {
+            for (int ks = 0; ks < D / 16; ++ks)  // tS += tQ K^T
+              umma_ss(tmem + C::COL_TS, make_smem_desc(aTQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
+                      idesc_s, 1);
+          } else {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)
-            umma_ss(tmem + C::COL_S, make_smem_desc(aQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
-                    idesc_s, ks > 0);
+            for (int ks = 0; ks < D / 16; ++ks)
+              umma_ss(tmem + C::COL_S, make_smem_desc(aQ + ks * 32, 16, 1024), make_smem_desc(aK + ks * 32, 16, 1024),
+                      idesc_s, ks > 0);
+          }
+          tc_commit(s_full);
         }
-        tc_commit(s_full);
-        FPROF_ACC(a_is, ta3);
+        if (ok) tc_commit(q_empty);  // arrives when the item's last scores are complete
+        ++kact;
       }
-#ifdef JVPFA_TC5_PROFILE
-      atomicAdd(&g_fprof[0], (unsigned long long)(clock64() - a_t0));
-      atomicAdd(&g_fprof[1], (unsigned long long)a_w1);
-      atomicAdd(&g_fprof[2], (unsigned long long)a_w2);
-      atomicAdd(&g_fprof[3], (unsigned long long)a_is);
-      atomicAdd(&g_fprof[4], (unsigned long long)n_tiles);
-#endif
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------ issuer B: outputs
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_o = make_idesc(Fmt<T>::kIdesc, BM, D, 0, 1);       // 128 x 64, B MN-major
       constexpr uint32_t idesc_o2 = make_idesc(Fmt<T>::kIdesc, BM, 2 * D, 0, 1);  // 128 x 128: [O | tO']
-#ifdef JVPFA_TC5_PROFILE
-      long long b_w = 0, b_is = 0;
-      const long long b_t0 = clock64();
-#endif
-      for (int it = 0; it < n_tiles; ++it) {
-        const int st = it % STAGES;
-        FPROF_T0(tb1);
-        if (!mbar_wait(p_full, it & 1, ab, kAbortPFull)) break;
-        FPROF_ACC(b_w, tb1);
-        tc_fence_after();
-        FPROF_T0(tb2);
-        const uint32_t aV = smem_u32(sKV + st * (C::N_KV * C::KV_BYTES)) + C::SLOT_V * C::KV_BYTES;
-        if constexpr (DUAL) {
+      int g = 0, kact = 0;
+      bool ok = true;
+      FwdItem it;
+      for (int k = 0; ok && k < k_max; ++k) {
+        if (!get_item(k, it) || it.n_tiles == 0) continue;
+        for (int t = 0; t < it.n_tiles; ++t, ++g) {
+          const int st = g % STAGES;
+          if (!mbar_wait(p_full, g & 1, ab, kAbortPFull)) {
+            ok = false;
+            break;
+          }
+          // The item's first tile overwrites O / tO': the previous item's epilogue must have read them.
+          if (t == 0 && kact > 0 && !mbar_wait(o_free, (kact - 1) & 1, ab, kAbortOFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t aV = smem_u32(sKV + st * (C::N_KV * C::KV_BYTES)) + C::SLOT_V * C::KV_BYTES;
+          if constexpr (DUAL) {
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk)  // [O | tO'] += P [V | tV]   (64-column chunks KV_BYTES apart)
-            umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
-                    idesc_o2, (it > 0 || kk > 0));
+            for (int kk = 0; kk < BN / 16; ++kk)  // [O | tO'] += P [V | tV]   (64-column chunks KV_BYTES apart)
+              umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
+                      idesc_o2, (t > 0 || kk > 0));
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk)  // tO' += W V
-            umma_ts(tmem + C::COL_TO, tmem + C::COL_TS + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
-                    idesc_o, 1);
-        } else {
+            for (int kk = 0; kk < BN / 16; ++kk)  // tO' += W V
+              umma_ts(tmem + C::COL_TO, tmem + C::COL_TS + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
+                      idesc_o, 1);
+          } else {
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk)
-            umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
-                    idesc_o, (it > 0 || kk > 0));
+            for (int kk = 0; kk < BN / 16; ++kk)
+              umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
+                      idesc_o, (t > 0 || kk > 0));
+          }
+          tc_commit(kv_empty + st);
         }
-        tc_commit(kv_empty + st);
-        FPROF_ACC(b_is, tb2);
+        if (ok) tc_commit(o_full);
+        ++kact;
       }
-      tc_commit(o_full);
-#ifdef JVPFA_TC5_PROFILE
-      atomicAdd(&g_fprof[8], (unsigned long long)(clock64() - b_t0));
-      atomicAdd(&g_fprof[9], (unsigned long long)b_w);
-      atomicAdd(&g_fprof[10], (unsigned long long)b_is);
-#endif
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const int i = m0 + row;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_off + C::COL_S, tTS = tmem + lane_off + C::COL_TS;
     const uint32_t tO = tmem + lane_off + C::COL_O, tTO = tmem + lane_off + C::COL_TO;
     const float scale_log2 = a.sm_scale * kLog2e;
     const float2 c2 = make_float2(scale_log2, scale_log2);
     const float2 sc2 = make_float2(a.sm_scale, a.sm_scale);
-    float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
     bool alive = true;
 
-#ifdef JVPFA_TC5_PROFILE
-    long long s_w = 0, s_ld = 0, s_mx = 0, s_ex = 0, s_ts = 0, s_st = 0;
-    const long long s_t0 = clock64();
-#endif
-    for (int it = 0; it < n_tiles; ++it) {
-      const int n0 = it * BN;
-      FPROF_T0(ts0);
-      if (!mbar_wait(s_full, it & 1, ab, kAbortSFull)) {
-        alive = false;
-        break;
+    // Normalise and store one item's rows.  has_acc: the accumulators hold something (the item had
+    // key tiles); then the item's last MMAs are waited for and O / tO' are released afterwards.
+    auto epilogue = [&](int bh, int i, float m_used, float l_run, float mu_run, bool has_acc, int kact_of_item) -> bool {
+      if (has_acc) {
+        if (!mbar_wait(o_full, kact_of_item & 1, ab, kAbortOFull)) return false;
+        tc_fence_after();
       }
-      tc_fence_after();
-      FPROF_ACC(s_w, ts0);
-      FPROF_T0(ts1);
-      uint32_t x0[32], x1[32];
-      tmem_ld32(tS, x0);
-      tmem_ld32(tS + 32, x1);
-      tmem_wait_ld();
-      FPROF_ACC(s_ld, ts1);
-      FPROF_T0(ts2);
-      // live key columns of this row inside the tile: col < col_hi
-      int col_hi = min(BN, n_valid - n0);
-      if (causal) col_hi = min(col_hi, i - n0 + 1);
-      const bool partial = (n0 + BN > n_valid) || (causal && n0 + BN - 1 > m0);
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        float2 v0 = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), c2);
-        float2 v1 = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), c2);
-        if (partial) {
-          if (2 * c >= col_hi) v0.x = -INFINITY;
-          if (2 * c + 1 >= col_hi) v0.y = -INFINITY;
-          if (32 + 2 * c >= col_hi) v1.x = -INFINITY;
-          if (33 + 2 * c >= col_hi) v1.y = -INFINITY;
-        }
-        x0[2 * c] = __float_as_uint(v0.x), x0[2 * c + 1] = __float_as_uint(v0.y);
-        x1[2 * c] = __float_as_uint(v1.x), x1[2 * c + 1] = __float_as_uint(v1.y);
-        mx0 = fmaxf(mx0, v0.x), mx1 = fmaxf(mx1, v0.y), mx2 = fmaxf(mx2, v1.x), mx3 = fmaxf(mx3, v1.y);
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // Lazy running max: keep the old reference while the new maximum is at most 2^8 above it.
-      const bool grow = mx > m_used + 8.f;
-      float alpha = 1.f;
-      if (grow) {
-        alpha = fast_exp2(m_used - mx);
-        m_used = mx;
-      }
-      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-      if (it > 0 && __any_sync(0xffffffffu, grow)) {
-        const float2 al2 = make_float2(alpha, alpha);
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + 32 * c, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float2 v = __fmul2_rn(ff2(r[2 * e], r[2 * e + 1]), al2);
-            r[2 * e] = __float_as_uint(v.x), r[2 * e + 1] = __float_as_uint(v.y);
-          }
-          tmem_st32(tO + 32 * c, r);
-          if constexpr (DUAL) {
-            tmem_ld32(tTO + 32 * c, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const float2 v = __fmul2_rn(ff2(r[2 * e], r[2 * e + 1]), al2);
-              r[2 * e] = __float_as_uint(v.x), r[2 * e + 1] = __float_as_uint(v.y);
-            }
-            tmem_st32(tTO + 32 * c, r);
-          }
-        }
-      }
-      FPROF_ACC(s_mx, ts2);
-      FPROF_T0(ts3);
-      const float2 nm2 = make_float2(-m_eff, -m_eff);
-      float2 ls2a = make_float2(0.f, 0.f), ls2b = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const float2 e0 = __fadd2_rn(ff2(x0[2 * c], x0[2 * c + 1]), nm2);
-        const float2 e1 = __fadd2_rn(ff2(x1[2 * c], x1[2 * c + 1]), nm2);
-        const float2 p0 = make_float2(fast_exp2(e0.x), fast_exp2(e0.y));
-        const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
-        x0[2 * c] = __float_as_uint(p0.x), x0[2 * c + 1] = __float_as_uint(p0.y);
-        x1[2 * c] = __float_as_uint(p1.x), x1[2 * c + 1] = __float_as_uint(p1.y);
-        ls2a = __fadd2_rn(ls2a, p0);
-        ls2b = __fadd2_rn(ls2b, p1);
-      }
-      l_run = l_run * alpha + ((ls2a.x + ls2a.y) + (ls2b.x + ls2b.y));
-      FPROF_ACC(s_ex, ts3);
-      FPROF_T0(ts4);
-      if constexpr (DUAL) {
-        float2 ms2a = make_float2(0.f, 0.f), ms2b = make_float2(0.f, 0.f);
-        uint32_t t[32];
-        uint32_t wp[16];
-        tmem_ld32(tTS, t);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float2 w = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), __fmul2_rn(ff2(t[2 * c], t[2 * c + 1]), sc2));
-          ms2a = __fadd2_rn(ms2a, w);
-          wp[c] = Elem<T>::pack(w.x, w.y);
-        }
-        tmem_ld32(tTS + 32, t);  // second half is read before the first packed half is written below
-        tmem_wait_ld();
-        tmem_st16(tTS, wp);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float2 w = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), __fmul2_rn(ff2(t[2 * c], t[2 * c + 1]), sc2));
-          ms2b = __fadd2_rn(ms2b, w);
-          wp[c] = Elem<T>::pack(w.x, w.y);
-        }
-        tmem_st16(tTS + 16, wp);
-        mu_run = mu_run * alpha + ((ms2a.x + ms2a.y) + (ms2b.x + ms2b.y));
-      }
-      FPROF_ACC(s_ts, ts4);
-      FPROF_T0(ts5);
-      {
-        uint32_t pp[32];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          pp[c] = Elem<T>::pack(__uint_as_float(x0[2 * c]), __uint_as_float(x0[2 * c + 1]));
-          pp[16 + c] = Elem<T>::pack(__uint_as_float(x1[2 * c]), __uint_as_float(x1[2 * c + 1]));
-        }
-        tmem_st32(tS, pp);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_full);
-      FPROF_ACC(s_st, ts5);
-    }
-#ifdef JVPFA_TC5_PROFILE
-    if (row == 0) {
-      atomicAdd(&g_fprof[16], (unsigned long long)(clock64() - s_t0));
-      atomicAdd(&g_fprof[17], (unsigned long long)s_w);
-      atomicAdd(&g_fprof[18], (unsigned long long)s_ld);
-      atomicAdd(&g_fprof[19], (unsigned long long)s_mx);
-      atomicAdd(&g_fprof[20], (unsigned long long)s_ex);
-      atomicAdd(&g_fprof[21], (unsigned long long)s_ts);
-      atomicAdd(&g_fprof[22], (unsigned long long)s_st);
-    }
-#endif
-
-    // ---- epilogue ----
-    if (alive && n_tiles > 0) alive = mbar_wait(o_full, 0, ab, kAbortOFull);
-    if (alive) {
-      tc_fence_after();
       const bool empty = !(l_run > 0.f);
       const float inv_l = empty ? 0.f : 1.f / l_run;
       const float mu_n = mu_run * inv_l;
@@ -403,14 +300,22 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
       T* gTO = DUAL ? reinterpret_cast<T*>(a.to) + ((size_t)bh * L + i) * D : nullptr;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
-        uint32_t ro[32];
+        uint32_t ro[32], rt[DUAL ? 32 : 1];
         uint32_t po[16];
-        if (n_tiles > 0) {
+        if (has_acc) {
           tmem_ld32(tO + 32 * c, ro);
+          if constexpr (DUAL) tmem_ld32(tTO + 32 * c, rt);
           tmem_wait_ld();
+          if (c == D / 32 - 1) {  // everything is in registers: the accumulators may be overwritten
+            tc_fence_before();
+            mbar_arrive(o_free);
+          }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) ro[e] = 0u;
+          for (int e = 0; e < 32; ++e) {
+            ro[e] = 0u;
+            if constexpr (DUAL) rt[e] = 0u;
+          }
         }
 #pragma unroll
         for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * inv_l);
@@ -422,14 +327,6 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
             reinterpret_cast<uint4*>(gO + 32 * c)[e] = make_uint4(po[4 * e], po[4 * e + 1], po[4 * e + 2], po[4 * e + 3]);
         }
         if constexpr (DUAL) {
-          uint32_t rt[32];
-          if (n_tiles > 0) {
-            tmem_ld32(tTO + 32 * c, rt);
-            tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) rt[e] = 0u;
-          }
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const float t0 = __uint_as_float(rt[2 * e]) * inv_l - mu_n * __uint_as_float(ro[2 * e]);
@@ -444,7 +341,155 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
           }
         }
       }
+      return true;
+    };
+
+    // The previous item's epilogue is deferred behind the softmax of this item's first tile: the wait
+    // for the previous item's last MMAs is then covered by work.
+    // (its running statistics wait in shared memory, the item itself is looked up again: registers
+    // are what limits this role)
+    int p_k = -1, p_kact = 0;
+    auto pending_epilogue = [&]() -> bool {
+      FwdItem pit;
+      get_item(p_k, pit);
+      p_k = -1;
+      return epilogue(pit.bh, pit.m0 + row, sPend[row], sPend[128 + row], sPend[256 + row], true, p_kact);
+    };
+    int g = 0, kact = 0;
+    FwdItem it;
+    for (int k = 0; alive && k < k_max; ++k) {
+      if (!get_item(k, it)) continue;
+      const int i = it.m0 + row;
+      if (it.n_tiles == 0) {  // no live key: zeros, lse = +inf
+        alive = epilogue(it.bh, i, -INFINITY, 0.f, 0.f, false, 0);
+        continue;
+      }
+      float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
+      for (int t = 0; t < it.n_tiles; ++t, ++g) {
+        const int n0 = t * BN;
+        if (!mbar_wait(s_full, g & 1, ab, kAbortSFull)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t x0[32], x1[32];
+        tmem_ld32(tS, x0);
+        tmem_ld32(tS + 32, x1);
+        tmem_wait_ld();
+        // live key columns of this row inside the tile: col < col_hi
+        int col_hi = min(BN, it.n_valid - n0);
+        if (causal) col_hi = min(col_hi, i - n0 + 1);
+        const bool partial = (n0 + BN > it.n_valid) || (causal && n0 + BN - 1 > it.m0);
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float2 v0 = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), c2);
+          float2 v1 = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), c2);
+          if (partial) {
+            if (2 * c >= col_hi) v0.x = -INFINITY;
+            if (2 * c + 1 >= col_hi) v0.y = -INFINITY;
+            if (32 + 2 * c >= col_hi) v1.x = -INFINITY;
+            if (33 + 2 * c >= col_hi) v1.y = -INFINITY;
+          }
+          x0[2 * c] = __float_as_uint(v0.x), x0[2 * c + 1] = __float_as_uint(v0.y);
+          x1[2 * c] = __float_as_uint(v1.x), x1[2 * c + 1] = __float_as_uint(v1.y);
+          mx0 = fmaxf(mx0, v0.x), mx1 = fmaxf(mx1, v0.y), mx2 = fmaxf(mx2, v1.x), mx3 = fmaxf(mx3, v1.y);
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // Lazy running max: keep the old reference while the new maximum is at most 2^8 above it.
+        const bool grow = mx > m_used + 8.f;
+        float alpha = 1.f;
+        if (grow) {
+          alpha = fast_exp2(m_used - mx);
+          m_used = mx;
+        }
+        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+        if (t > 0 && __any_sync(0xffffffffu, grow)) {
+          const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tO + 32 * c, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float2 v = __fmul2_rn(ff2(r[2 * e], r[2 * e + 1]), al2);
+              r[2 * e] = __float_as_uint(v.x), r[2 * e + 1] = __float_as_uint(v.y);
+            }
+            tmem_st32(tO + 32 * c, r);
+            if constexpr (DUAL) {
+              tmem_ld32(tTO + 32 * c, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const float2 v = __fmul2_rn(ff2(r[2 * e], r[2 * e + 1]), al2);
+                r[2 * e] = __float_as_uint(v.x), r[2 * e + 1] = __float_as_uint(v.y);
+              }
+              tmem_st32(tTO + 32 * c, r);
+            }
+          }
+        }
+        const float2 nm2 = make_float2(-m_eff, -m_eff);
+        float2 ls2a = make_float2(0.f, 0.f), ls2b = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float2 e0 = __fadd2_rn(ff2(x0[2 * c], x0[2 * c + 1]), nm2);
+          const float2 e1 = __fadd2_rn(ff2(x1[2 * c], x1[2 * c + 1]), nm2);
+          const float2 p0 = make_float2(fast_exp2(e0.x), fast_exp2(e0.y));
+          const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
+          x0[2 * c] = __float_as_uint(p0.x), x0[2 * c + 1] = __float_as_uint(p0.y);
+          x1[2 * c] = __float_as_uint(p1.x), x1[2 * c + 1] = __float_as_uint(p1.y);
+          ls2a = __fadd2_rn(ls2a, p0);
+          ls2b = __fadd2_rn(ls2b, p1);
+        }
+        l_run = l_run * alpha + ((ls2a.x + ls2a.y) + (ls2b.x + ls2b.y));
+        if constexpr (DUAL) {
+          float2 ms2a = make_float2(0.f, 0.f), ms2b = make_float2(0.f, 0.f);
+          uint32_t tt[32];
+          uint32_t wp[16];
+          tmem_ld32(tTS, tt);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float2 w = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), __fmul2_rn(ff2(tt[2 * c], tt[2 * c + 1]), sc2));
+            ms2a = __fadd2_rn(ms2a, w);
+            wp[c] = Elem<T>::pack(w.x, w.y);
+          }
+          tmem_ld32(tTS + 32, tt);  // second half is read before the first packed half is written below
+          tmem_wait_ld();
+          tmem_st16(tTS, wp);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float2 w = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), __fmul2_rn(ff2(tt[2 * c], tt[2 * c + 1]), sc2));
+            ms2b = __fadd2_rn(ms2b, w);
+            wp[c] = Elem<T>::pack(w.x, w.y);
+          }
+          tmem_st16(tTS + 16, wp);
+          mu_run = mu_run * alpha + ((ms2a.x + ms2a.y) + (ms2b.x + ms2b.y));
+        }
+        {
+          uint32_t pp[32];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            pp[c] = Elem<T>::pack(__uint_as_float(x0[2 * c]), __uint_as_float(x0[2 * c + 1]));
+            pp[16 + c] = Elem<T>::pack(__uint_as_float(x1[2 * c]), __uint_as_float(x1[2 * c + 1]));
+          }
+          tmem_st32(tS, pp);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full);
+        if (p_k >= 0 && !pending_epilogue()) {
+          alive = false;
+          break;
+        }
+      }
+      if (!alive) break;
+      p_k = k, p_kact = kact;
+      sPend[row] = m_used, sPend[128 + row] = l_run, sPend[256 + row] = mu_run;
+      ++kact;
     }
+    if (alive && p_k >= 0) pending_epilogue();
   }
 
   tc_fence_before();
@@ -458,6 +503,18 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
     tc_fence_after();
     tmem_dealloc(tmem, C::COLS_ALLOC);
   }
+}
+
+static int fwd_sm_count() {
+  static int cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!cache[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cache[dev] = n;
+  }
+  return cache[dev];
 }
 
 template <typename T, bool DUAL>
@@ -488,7 +545,22 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(fwd_tc5_d64)");
     return JVPFA_ERR_CUDA;
   }
-  dim3 grid((a.L + C::BM - 1) / C::BM, a.B * a.H);
+  const int sms = fwd_sm_count();
+  if (sms <= 0) {
+    set_last_cuda_error(cudaErrorUnknown, "multiprocessor count");
+    return JVPFA_ERR_CUDA;
+  }
+  const long long n_items = (long long)((a.L + C::BM - 1) / C::BM) * BH;
+  // Persistent CTAs (two per SM) pay off when the static list balances: causal shapes, where heavy and
+  // light items alternate in every list, and uniform shapes whose item count fills the last round.
+  // Otherwise (key padding: item lengths vary by batch; a thin last round) one CTA per item leaves the
+  // balancing to the hardware scheduler; the kernel is the same, its list then has one entry.
+  const long long slots = 2ll * sms;
+  const long long rounds = (n_items + slots - 1) / slots;
+  bool persistent = n_items > slots;
+  if (persistent && a.mask.kind != JVPFA_MASK_CAUSAL)
+    persistent = a.mask.kind == JVPFA_MASK_NONE ? (n_items * 100 >= rounds * slots * 95) : rounds >= 8;
+  const int grid = (int)(persistent ? slots : n_items);
   kern<<<grid, C::NTHREADS, C::SMEM_BYTES, stream>>>(a, maps, status);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -499,18 +571,6 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
 }
 
 }  // namespace tc5
-
-#ifdef JVPFA_TC5_PROFILE
-extern "C" int jvpfa_debug_read_fprof(unsigned long long* out, int clear) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, tc5::g_fprof, sizeof(unsigned long long) * 32);
-  if (clear) {
-    unsigned long long z[32] = {};
-    cudaMemcpyToSymbol(tc5::g_fprof, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 int launch_fwd_tc5_d64(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
