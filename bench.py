@@ -36,9 +36,9 @@ METRIC = "fwd_dual+bwd TFLOP/s (bf16 causal B4 H16 L2048 D64; algorithmic MMA fl
 CPU_SAMPLE_HEADS = 8
 DEFAULT_WORKLOAD = "c2_bf16_causal"
 # DRAM bytes (read + write) per C-ABI call on the default workload, from one ncu --set full capture of each kernel
-# (profiles/tc5_kernels_c2_bf16_causal.md): forward 100.7 + 17.7 MB; backward = own-keys launch 123.6 + 14.3 MB
-# plus own-queries launch 171.0 + 9.2 MB.
-NCU_DRAM_BYTES = {"fwd_dual": 118.4e6, "bwd": 318.1e6}
+# (profiles/tc5_kernels_c2_bf16_causal.md): forward 147.8 + 15.7 MB; backward = own-keys launch 123.1 + 12.7 MB
+# plus own-queries launch 148.4 + 10.1 MB.
+NCU_DRAM_BYTES = {"fwd_dual": 163.5e6, "bwd": 294.3e6}
 
 
 def _peaks():
