@@ -164,6 +164,32 @@ def test_tcgen05_forward_against_oracle_and_generic_family(dt, B, H, L, D, kind,
     assert orc.max_abs_err(lse, lse2) < 1e-4
 
 
+PERSISTENT_FWD_CASES = [
+    # dtype, B, H, L, mask kind: more query tiles than two CTAs per SM can hold at once, so that the forward's CTAs
+    # walk a list of items (causal, unmasked) or, with key padding, run one item each through the same code
+    ("bf16", 40, 12, 256, "causal"), ("bf16", 40, 12, 160, "none"), ("fp16", 64, 12, 192, "kvlen"), ("bf16", 6, 16, 1100, "causal"),
+]
+
+
+@pytest.mark.parametrize("dt,B,H,L,kind", PERSISTENT_FWD_CASES)
+def test_tcgen05_forward_many_items_per_cta(dt, B, H, L, kind):
+    """The persistent tcgen05 forward (D = 64, with tangents) against the register-tiled family on the same inputs
+    and, for the last (batch, head) slice, against the float64 oracle."""
+    dtype = DT[dt]
+    q, k, v, tq, tk, tv, *_ = _make(B, H, L, 64, dtype, seed=B + L)
+    mask, causal = _mask(kind, B, H, L, dtype, seed=L)
+    o, to, lse, mu, *_ = _run_kernels(q, k, v, tq, tk, tv, None, None, mask, causal, impl=_lib.IMPL_TCGEN05)
+    assert _lib.device_status() == 0, "a bounded wait inside the tcgen05 kernel gave up"
+    o2, to2, lse2, mu2, *_ = _run_kernels(q, k, v, tq, tk, tv, None, None, mask, causal, impl=_lib.IMPL_GENERIC)
+    assert orc.max_abs_err(o, o2) <= HALF_ABS and orc.max_abs_err(to, to2) <= HALF_ABS
+    assert orc.max_abs_err(lse, lse2) < 1e-4 and orc.max_abs_err(mu, mu2) < 1e-3
+    sl = lambda x: x[B - 1:, H - 1:]  # noqa: E731
+    msl = None if mask is None else mask[B - 1:]
+    ro, rto = orc.sdpa_jvp(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), attn_mask=msl, causal=causal)
+    _close(sl(o), ro, dtype, "O")
+    _close(sl(to), rto, dtype, "tO")
+
+
 PERSISTENT_CASES = [
     # cotangents, mask kind, dtype, B, H, L: more work items than a B200 has SMs, so that every CTA of
     # the persistent backward walks several items; short items (1 to 5 sub-tiles of 32 rows), odd
