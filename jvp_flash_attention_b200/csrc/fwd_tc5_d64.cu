@@ -10,8 +10,7 @@
 //
 // Work item = one 128-row query tile of one (batch, head).  The CTAs are persistent (two per SM):
 // each walks a static list of items, so barriers and TMEM are set up once, the next item's Q and
-// first key tiles are on their way while the current item finishes, and an item's epilogue runs
-// behind the softmax of the next item's first tile.  7 warps: TMA producer, issuer A, issuer B,
+// first key tiles are on their way while the current item finishes.  7 warps: TMA producer, issuer A, issuer B,
 // four softmax / epilogue warps (thread <-> query row <-> TMEM lane).  TMEM columns:
 //   S [64] | tS [64] | O [64] | tO' [64]   (256 columns -> two CTAs per SM)
 // P and W = P*tS*scale are written as packed 16-bit values over the head of S and tS and feed
@@ -36,8 +35,7 @@ struct Fwd64Cfg {
   // stage layout: K, tK, V, tV (DUAL) or K, V
   static constexpr int SLOT_K = 0, SLOT_TK = 1, SLOT_V = DUAL ? 2 : 1, SLOT_TV = 3;
   static constexpr int TILE_BYTES = N_Q * Q_BYTES + STAGES * N_KV * KV_BYTES;
-  static constexpr int PEND_BYTES = 128 * 3 * 4;  // running statistics of the item whose epilogue is pending
-  static constexpr int SMEM_BYTES = TILE_BYTES + 256 + PEND_BYTES + 1024;
+  static constexpr int SMEM_BYTES = TILE_BYTES + 256 + 1024;
   static constexpr int COL_S = 0;
   static constexpr int COL_TS = 64;
   static constexpr int COL_O = DUAL ? 128 : 64;
@@ -80,7 +78,6 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
   uint64_t* q_empty = s_full + 3;  // issuer A has read the item's Q tiles
   uint64_t* o_free = s_full + 4;   // the epilogue has read the item's accumulators
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
-  float* sPend = reinterpret_cast<float*>(smem + C::TILE_BYTES + 256);  // [3][128]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -344,17 +341,6 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
       return true;
     };
 
-    // The previous item's epilogue is deferred behind the softmax of this item's first tile: the wait
-    // for the previous item's last MMAs is then covered by work.
-    // (its running statistics wait in shared memory, the item itself is looked up again: registers
-    // are what limits this role)
-    int p_k = -1, p_kact = 0;
-    auto pending_epilogue = [&]() -> bool {
-      FwdItem pit;
-      get_item(p_k, pit);
-      p_k = -1;
-      return epilogue(pit.bh, pit.m0 + row, sPend[row], sPend[128 + row], sPend[256 + row], true, p_kact);
-    };
     int g = 0, kact = 0;
     FwdItem it;
     for (int k = 0; alive && k < k_max; ++k) {
@@ -479,17 +465,13 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full);
-        if (p_k >= 0 && !pending_epilogue()) {
-          alive = false;
-          break;
-        }
       }
       if (!alive) break;
-      p_k = k, p_kact = kact;
-      sPend[row] = m_used, sPend[128 + row] = l_run, sPend[256 + row] = mu_run;
+      // (Deferring this behind the softmax of the next item's first tile, as the backward does, was
+      // measured slower here: the softmax warps are the critical path of this kernel.)
+      if (!epilogue(it.bh, i, m_used, l_run, mu_run, true, kact)) break;
       ++kact;
     }
-    if (alive && p_k >= 0) pending_epilogue();
   }
 
   tc_fence_before();
