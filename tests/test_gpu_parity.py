@@ -556,3 +556,15 @@ def test_config5_shard_long_sequence_sampled_head():
     o2, to2 = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(x.detach() for x in a), (2 * t["tq"], 2 * t["tk"], 2 * t["tv"]))
     assert torch.equal(o2, o.detach())
     assert (to2.float() - 2 * to.detach().float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16", "fp32"])
+def test_reference_harness_grid_short_lengths(dt):
+    """The reference script's own check (tests/harness.py: same grid, seeds, comparator SDPA-MATH in the working dtype,
+    tolerances 3.2e-2 / 4e-3 / 2.35e-2) for L <= 128, without its timing part."""
+    from tests import harness
+
+    rows = harness.run(DT[dt], 128, bench=False)
+    assert len(rows) == 12
+    bad = [(r["seq_len"], r["mask"], r["causal"], r["max_error"]) for r in rows if not r["pass"]]
+    assert not bad, bad
