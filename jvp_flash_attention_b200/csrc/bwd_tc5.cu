@@ -112,7 +112,7 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
   if (tid == 0) {
     mbar_init(own_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(loop_full + s, 1);
+      mbar_init(loop_full + s, OWN_KEYS ? 2 : 1);  // TMA bytes (+ the row statistics, own keys)
       mbar_init(loop_empty + s, 1);
     }
     mbar_init(s_full, 1);
@@ -160,24 +160,6 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait(loop_empty + st, ph ^ 1, ab, kAbortBwdLoopEmpty)) break;
         const int l0 = loop_begin + it * BL;
-        if constexpr (OWN_KEYS) {
-          // per-query statistics of this tile, combined once for all 128 key rows
-          for (int c = lane; c < BL; c += 32) {
-            const int i = l0 + c;
-            float4 s4 = make_float4(INFINITY, 0.f, 0.f, 0.f);
-            if (i < L) {
-              s4.x = a.lse[stat_off + i];
-              s4.w = a.delta[stat_off + i];
-              if constexpr (HAS_GT) {
-                s4.y = a.mu[stat_off + i];
-                s4.z = a.eps[stat_off + i];
-                s4.w += a.cterm[stat_off + i] + s4.z * s4.y;
-              }
-            }
-            sStat[st * BL + c] = s4;
-          }
-          __syncwarp();
-        }
         if (lane == 0) {
           unsigned char* base = sLoop + st * (C::N_LOOP * C::LOOP_BYTES);
           mbar_expect_tx(loop_full + st, C::N_LOOP * C::LOOP_BYTES);
@@ -199,6 +181,26 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
               }
             }
           }
+        }
+        if constexpr (OWN_KEYS) {
+          // per-query statistics of this tile, combined once for all 128 key rows; fetched after the tile
+          // loads have been issued, so that the two latencies overlap
+          for (int c = lane; c < BL; c += 32) {
+            const int i = l0 + c;
+            float4 s4 = make_float4(INFINITY, 0.f, 0.f, 0.f);
+            if (i < L) {
+              s4.x = a.lse[stat_off + i];
+              s4.w = a.delta[stat_off + i];
+              if constexpr (HAS_GT) {
+                s4.y = a.mu[stat_off + i];
+                s4.z = a.eps[stat_off + i];
+                s4.w += a.cterm[stat_off + i] + s4.z * s4.y;
+              }
+            }
+            sStat[st * BL + c] = s4;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(loop_full + st);  // second arrival: the statistics are in place
         }
       }
     }
