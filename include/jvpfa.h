@@ -104,6 +104,13 @@ typedef struct {
   float* lse; /* (B,H,L) */
   float* mu;  /* (B,H,L) or NULL */
   jvpfa_mask mask;
+  /* Element strides of the batch, head and row dimensions of q, k, v, tq, tk, tv (all six alike; the
+   * head dimension D is always contiguous).  {0,0,0} means (B,H,L,D) row-major.  Anything else, e.g. the
+   * (B,H,L,D) view of a (B,L,H,D) tensor, {L*H*D, D, H*D}, is read in place by the tcgen05 kernels for
+   * D = 64 with tangents (strides must be multiples of 8 elements); other requests with strides return
+   * JVPFA_ERR_UNSUPPORTED and the caller passes contiguous copies instead (upstream always copies:
+   * jvp_attention.py:2733-2734, 2787-2788).  Outputs are always (B,H,L,D) row-major. */
+  int64_t in_stride[3];
 } jvpfa_fwd_args;
 
 int jvpfa_fwd(const jvpfa_fwd_args* args, void* stream);
@@ -158,6 +165,7 @@ typedef struct {
   const float *delta, *eps, *cterm;
   void *dq, *dk, *dv;
   jvpfa_mask mask;
+  int64_t in_stride[3]; /* of q, k, v, tq, tk, tv, as in jvpfa_fwd_args; go, gto, dq, dk, dv are row-major */
 } jvpfa_bwd_args;
 
 int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);

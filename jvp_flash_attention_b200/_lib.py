@@ -68,6 +68,7 @@ class FwdArgs(C.Structure):
         ("lse", C.c_void_p),
         ("mu", C.c_void_p),
         ("mask", Mask),
+        ("in_stride", C.c_int64 * 3),
     ]
 
 
@@ -117,6 +118,7 @@ class BwdArgs(C.Structure):
         ("dk", C.c_void_p),
         ("dv", C.c_void_p),
         ("mask", Mask),
+        ("in_stride", C.c_int64 * 3),
     ]
 
 
@@ -242,8 +244,31 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, impl: int = IMPL_AUTO) -> None:
-    """Launches jvpfa_fwd on the current stream of ``q``'s device (all tensors contiguous BHLD)."""
+ERR_UNSUPPORTED = -9
+
+
+class Unsupported(RuntimeError):
+    """The library understood the request but this build cannot serve it (JVPFA_ERR_UNSUPPORTED)."""
+
+
+def common_strides(*ts) -> tuple[int, int, int] | None:
+    """(batch, head, row) element strides shared by the given (B,H,L,D) tensors, or None when they are all
+    row-major.  Raises ValueError when the tensors disagree or the layout cannot be described that way
+    (last dimension not contiguous, strides not multiples of 8 elements, base not 16-byte aligned)."""
+    ts = [t for t in ts if t is not None]
+    if all(t.is_contiguous() for t in ts):
+        return None
+    st = ts[0].stride()
+    for t in ts:
+        if t.stride() != st or t.stride(-1) != 1 or any(x <= 0 or x % 8 for x in t.stride()[:3]) or t.data_ptr() % 16:
+            raise ValueError("layouts differ or are not expressible as (batch, head, row) strides")
+    return st[0], st[1], st[2]
+
+
+def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, impl: int = IMPL_AUTO,
+        in_stride: tuple[int, int, int] | None = None) -> None:
+    """Launches jvpfa_fwd on the current stream of ``q``'s device.  Outputs are contiguous BHLD; the inputs too,
+    unless ``in_stride`` gives their common (batch, head, row) element strides."""
     lib = load()
     B, H, L, D = q.shape
     a = FwdArgs()
@@ -256,8 +281,13 @@ def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, im
     a.tq, a.tk, a.tv = ptr(tq), ptr(tk), ptr(tv)
     a.o, a.to, a.lse, a.mu = ptr(o), ptr(to), ptr(lse), ptr(mu)
     a.mask = mask.to_c()
+    if in_stride is not None:
+        a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
     with torch.cuda.device(q.device):
-        check(lib.jvpfa_fwd(C.byref(a), _stream(q)), "jvpfa_fwd")
+        rc = lib.jvpfa_fwd(C.byref(a), _stream(q))
+    if rc == ERR_UNSUPPORTED and in_stride is not None:
+        raise Unsupported("jvpfa_fwd cannot read this layout in place")
+    check(rc, "jvpfa_fwd")
 
 
 def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
@@ -275,7 +305,7 @@ def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
 
 
 def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, mask: MaskSpec,
-        sm_scale: float, impl: int = IMPL_AUTO) -> None:
+        sm_scale: float, impl: int = IMPL_AUTO, in_stride: tuple[int, int, int] | None = None) -> None:
     """Launches jvpfa_bwd (gradients of <go,O> + <gto,tO> w.r.t. q, k, v)."""
     lib = load()
     B, H, L, D = q.shape
@@ -292,8 +322,13 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
     a.delta, a.eps, a.cterm = ptr(delta), ptr(eps), ptr(cterm)
     a.dq, a.dk, a.dv = ptr(dq), ptr(dk), ptr(dv)
     a.mask = mask.to_c()
+    if in_stride is not None:
+        a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
     with torch.cuda.device(q.device):
-        check(lib.jvpfa_bwd(C.byref(a), _stream(q)), "jvpfa_bwd")
+        rc = lib.jvpfa_bwd(C.byref(a), _stream(q))
+    if rc == ERR_UNSUPPORTED and in_stride is not None:
+        raise Unsupported("jvpfa_bwd cannot read this layout in place")
+    check(rc, "jvpfa_bwd")
 
 
 def bwd_noalloc(q, k, v, tq, tk, tv, o, to, go, gto, lse, mu, dq, dk, dv, mask: MaskSpec, sm_scale: float,

@@ -66,6 +66,15 @@ static int check_mask(const jvpfa_mask& m) {
   }
 }
 
+// in_stride: all zero (row-major) or three positive multiples of 8 elements (16 bytes, a TMA requirement)
+static bool has_strides(const int64_t* st) { return (st[0] | st[1] | st[2]) != 0; }
+static int check_strides(const int64_t* st) {
+  if (!has_strides(st)) return JVPFA_OK;
+  for (int i = 0; i < 3; ++i)
+    if (st[i] <= 0 || (st[i] & 7) != 0) return JVPFA_ERR_SHAPE;
+  return JVPFA_OK;
+}
+
 static int validate_fwd(const jvpfa_fwd_args* a) {
   if (!a) return JVPFA_ERR_NULL;
   if (a->struct_size != (int32_t)sizeof(jvpfa_fwd_args)) return JVPFA_ERR_STRUCT;
@@ -79,6 +88,8 @@ static int validate_fwd(const jvpfa_fwd_args* a) {
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
   if (a->impl < JVPFA_IMPL_AUTO || a->impl > JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
+  rc = check_strides(a->in_stride);
+  if (rc) return rc;
   return check_mask(a->mask);
 }
 
@@ -96,6 +107,8 @@ static int validate_bwd(const jvpfa_bwd_args* a) {
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
   if (impl_family(a->impl) > JVPFA_IMPL_TCGEN05 || (a->impl & ~0x3ff) != 0) return JVPFA_ERR_UNSUPPORTED;
+  rc = check_strides(a->in_stride);
+  if (rc) return rc;
   return check_mask(a->mask);
 }
 
@@ -139,6 +152,10 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc5 = fwd_tc5_eligible(*a);
   if (a->impl == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
+  // strided inputs are read in place only by the D = 64 kernel with tangents
+  if (has_strides(a->in_stride) &&
+      !(tc5 && a->impl != JVPFA_IMPL_GENERIC && a->D == 64 && a->tq != nullptr && a->sm_scale > 0.f))
+    return JVPFA_ERR_UNSUPPORTED;
   if (tc5 && a->impl != JVPFA_IMPL_GENERIC) return launch_fwd_tc5(*a, s);
   return launch_fwd_generic(*a, s);
 }
@@ -160,6 +177,7 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   const bool tc5 = bwd_tc5_eligible(*a);
   const int fam = impl_family(a->impl);
   if (fam == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
+  if (has_strides(a->in_stride) && !(tc5 && fam != JVPFA_IMPL_GENERIC && a->D == 64)) return JVPFA_ERR_UNSUPPORTED;
   if (tc5 && fam != JVPFA_IMPL_GENERIC) return launch_bwd_tc5(*a, s);
   return launch_bwd_generic(*a, s);
 }

@@ -121,7 +121,7 @@ __device__ long long g_bwd_items[2][3][24];
 
 // One work item of the persistent loop.
 struct BwdItem {
-  int bh, b, own0, loop_begin, n_sub;
+  int bh, b, h, own0, loop_begin, n_sub;
 };
 
 template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
@@ -167,6 +167,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     const int rank = w / BH;
     it.bh = w - rank * BH;
     it.b = it.bh / a.H;
+    it.h = it.bh - it.b * a.H;
     int n_valid = L;
     if (a.mask.kind == JVPFA_MASK_KVLEN) {
       const int n = a.mask.kv_len[it.b];
@@ -246,18 +247,18 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         unsigned char* dst = sOwn + h * C::STAGING_HALF;
         mbar_expect_tx(own_staged + h, C::STAGING_HALF);
         if constexpr (OWN_KEYS) {
-          tma_load_3d(dst + C::SLOT_K * C::OWN_BYTES, &maps.k, own_staged + h, 0, it.own0, it.bh);
-          tma_load_3d(dst + C::SLOT_V * C::OWN_BYTES, &maps.v, own_staged + h, 0, it.own0, it.bh);
+          tma_load_4d(dst + C::SLOT_K * C::OWN_BYTES, &maps.k, own_staged + h, 0, it.own0, it.h, it.b);
+          tma_load_4d(dst + C::SLOT_V * C::OWN_BYTES, &maps.v, own_staged + h, 0, it.own0, it.h, it.b);
           if constexpr (HAS_GT) {
-            tma_load_3d(dst + C::SLOT_TK * C::OWN_BYTES, &maps.tk, own_staged + h, 0, it.own0, it.bh);
-            tma_load_3d(dst + C::SLOT_TV * C::OWN_BYTES, &maps.tv, own_staged + h, 0, it.own0, it.bh);
+            tma_load_4d(dst + C::SLOT_TK * C::OWN_BYTES, &maps.tk, own_staged + h, 0, it.own0, it.h, it.b);
+            tma_load_4d(dst + C::SLOT_TV * C::OWN_BYTES, &maps.tv, own_staged + h, 0, it.own0, it.h, it.b);
           }
         } else {
-          tma_load_3d(dst + C::SLOT_Q * C::OWN_BYTES, &maps.q, own_staged + h, 0, it.own0, it.bh);
-          if constexpr (HAS_GO) tma_load_3d(dst + C::SLOT_GO * C::OWN_BYTES, &maps.go, own_staged + h, 0, it.own0, it.bh);
+          tma_load_4d(dst + C::SLOT_Q * C::OWN_BYTES, &maps.q, own_staged + h, 0, it.own0, it.h, it.b);
+          if constexpr (HAS_GO) tma_load_4d(dst + C::SLOT_GO * C::OWN_BYTES, &maps.go, own_staged + h, 0, it.own0, it.h, it.b);
           if constexpr (HAS_GT) {
-            tma_load_3d(dst + C::SLOT_TQ * C::OWN_BYTES, &maps.tq, own_staged + h, 0, it.own0, it.bh);
-            tma_load_3d(dst + C::SLOT_G * C::OWN_BYTES, &maps.g, own_staged + h, 0, it.own0, it.bh);
+            tma_load_4d(dst + C::SLOT_TQ * C::OWN_BYTES, &maps.tq, own_staged + h, 0, it.own0, it.h, it.b);
+            tma_load_4d(dst + C::SLOT_G * C::OWN_BYTES, &maps.g, own_staged + h, 0, it.own0, it.h, it.b);
           }
         }
       }
@@ -332,18 +333,18 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             unsigned char* base = sLoop + st * C::STAGE_BYTES;
             mbar_expect_tx(loop_full + st, C::STAGE_BYTES);
             if constexpr (OWN_KEYS) {
-              tma_load_3d(base + C::SLOT_Q * C::LOOP_BYTES, &maps.q, loop_full + st, 0, l0, it.bh);
-              if constexpr (HAS_GO) tma_load_3d(base + C::SLOT_GO * C::LOOP_BYTES, &maps.go, loop_full + st, 0, l0, it.bh);
+              tma_load_4d(base + C::SLOT_Q * C::LOOP_BYTES, &maps.q, loop_full + st, 0, l0, it.h, it.b);
+              if constexpr (HAS_GO) tma_load_4d(base + C::SLOT_GO * C::LOOP_BYTES, &maps.go, loop_full + st, 0, l0, it.h, it.b);
               if constexpr (HAS_GT) {
-                tma_load_3d(base + C::SLOT_TQ * C::LOOP_BYTES, &maps.tq, loop_full + st, 0, l0, it.bh);
-                tma_load_3d(base + C::SLOT_G * C::LOOP_BYTES, &maps.g, loop_full + st, 0, l0, it.bh);
+                tma_load_4d(base + C::SLOT_TQ * C::LOOP_BYTES, &maps.tq, loop_full + st, 0, l0, it.h, it.b);
+                tma_load_4d(base + C::SLOT_G * C::LOOP_BYTES, &maps.g, loop_full + st, 0, l0, it.h, it.b);
               }
             } else {
-              tma_load_3d(base + C::SLOT_K * C::LOOP_BYTES, &maps.k, loop_full + st, 0, l0, it.bh);
-              tma_load_3d(base + C::SLOT_V * C::LOOP_BYTES, &maps.v, loop_full + st, 0, l0, it.bh);
+              tma_load_4d(base + C::SLOT_K * C::LOOP_BYTES, &maps.k, loop_full + st, 0, l0, it.h, it.b);
+              tma_load_4d(base + C::SLOT_V * C::LOOP_BYTES, &maps.v, loop_full + st, 0, l0, it.h, it.b);
               if constexpr (HAS_GT) {
-                tma_load_3d(base + C::SLOT_TK * C::LOOP_BYTES, &maps.tk, loop_full + st, 0, l0, it.bh);
-                tma_load_3d(base + C::SLOT_TV * C::LOOP_BYTES, &maps.tv, loop_full + st, 0, l0, it.bh);
+                tma_load_4d(base + C::SLOT_TK * C::LOOP_BYTES, &maps.tk, loop_full + st, 0, l0, it.h, it.b);
+                tma_load_4d(base + C::SLOT_TV * C::LOOP_BYTES, &maps.tv, loop_full + st, 0, l0, it.h, it.b);
               }
             }
           }
@@ -784,14 +785,16 @@ static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* stat
   const CUtensorMapDataType dt = Fmt<T>::kTma;
   const int key_rows = OWN_KEYS ? C::OWN : C::BL;
   const int qry_rows = OWN_KEYS ? C::BL : C::OWN;
-  bool ok = encode_map(&m.k, dt, a.k, 64, a.L, BH, key_rows) && encode_map(&m.v, dt, a.v, 64, a.L, BH, key_rows) &&
-            encode_map(&m.q, dt, a.q, 64, a.L, BH, qry_rows);
+  // (64, L, H, B) maps; q, k, v and their tangents may be strided views (in_stride), the cotangents are row-major
+  const int64_t* st = a.in_stride;
+  bool ok = encode_map4(&m.k, dt, a.k, a.L, a.H, a.B, st, key_rows) && encode_map4(&m.v, dt, a.v, a.L, a.H, a.B, st, key_rows) &&
+            encode_map4(&m.q, dt, a.q, a.L, a.H, a.B, st, qry_rows);
   m.tk = m.tv = m.k;
   m.go = m.tq = m.g = m.q;
-  if (HAS_GO) ok = ok && encode_map(&m.go, dt, a.go, 64, a.L, BH, qry_rows);
+  if (HAS_GO) ok = ok && encode_map4(&m.go, dt, a.go, a.L, a.H, a.B, nullptr, qry_rows);
   if (HAS_GT)
-    ok = ok && encode_map(&m.tk, dt, a.tk, 64, a.L, BH, key_rows) && encode_map(&m.tv, dt, a.tv, 64, a.L, BH, key_rows) &&
-         encode_map(&m.tq, dt, a.tq, 64, a.L, BH, qry_rows) && encode_map(&m.g, dt, a.gto, 64, a.L, BH, qry_rows);
+    ok = ok && encode_map4(&m.tk, dt, a.tk, a.L, a.H, a.B, st, key_rows) && encode_map4(&m.tv, dt, a.tv, a.L, a.H, a.B, st, key_rows) &&
+         encode_map4(&m.tq, dt, a.tq, a.L, a.H, a.B, st, qry_rows) && encode_map4(&m.g, dt, a.gto, a.L, a.H, a.B, nullptr, qry_rows);
   if (!ok) {
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(bwd d64)");
     return JVPFA_ERR_CUDA;

@@ -432,6 +432,23 @@ bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, 
   return r == CUDA_SUCCESS;
 }
 
+bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* st,
+                 int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const bool dense = st == nullptr || (st[0] == 0 && st[1] == 0 && st[2] == 0);
+  const cuuint64_t sb = dense ? (cuuint64_t)H * L * 64 : (cuuint64_t)st[0];
+  const cuuint64_t sh = dense ? (cuuint64_t)L * 64 : (cuuint64_t)st[1];
+  const cuuint64_t sl = dense ? 64 : (cuuint64_t)st[2];
+  cuuint64_t dims[4] = {64, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {sl * 2, sh * 2, sb * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 template <typename T, int D, bool DUAL>
 static int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D, DUAL>;

@@ -51,7 +51,7 @@ __device__ __forceinline__ float2 ff2(uint32_t a, uint32_t b) { return make_floa
 
 // One work item of the persistent loop: a 128-row query tile of one (batch, head).
 struct FwdItem {
-  int bh, m0, n_valid, n_tiles;
+  int bh, b, h, m0, n_valid, n_tiles;
 };
 
 template <typename T, bool DUAL>
@@ -102,9 +102,11 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
       it.bh = w / n_q_tiles;
       it.m0 = (w - it.bh * n_q_tiles) * BM;
     }
+    it.b = it.bh / a.H;
+    it.h = it.bh - it.b * a.H;
     it.n_valid = L;
     if (a.mask.kind == JVPFA_MASK_KVLEN) {
-      const int n = a.mask.kv_len[it.bh / a.H];
+      const int n = a.mask.kv_len[it.b];
       it.n_valid = n < 0 ? 0 : (n > L ? L : n);
     }
     int n_end = it.n_valid;
@@ -153,8 +155,8 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         // The Q tiles are single-buffered: issuer A must be through with the previous item's.
         if (kact > 0 && !mbar_wait(q_empty, (kact - 1) & 1, ab, kAbortQFull)) break;
         mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
-        tma_load_3d(sQ, &maps.q, q_full, 0, it.m0, it.bh);
-        if constexpr (DUAL) tma_load_3d(sTQ, &maps.tq, q_full, 0, it.m0, it.bh);
+        tma_load_4d(sQ, &maps.q, q_full, 0, it.m0, it.h, it.b);
+        if constexpr (DUAL) tma_load_4d(sTQ, &maps.tq, q_full, 0, it.m0, it.h, it.b);
         for (int t = 0; t < it.n_tiles; ++t, ++g) {
           const int st = g % STAGES;
           const uint32_t ph = (g / STAGES) & 1;
@@ -165,11 +167,11 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
           unsigned char* base = sKV + st * (C::N_KV * C::KV_BYTES);
           mbar_expect_tx(kv_full + st, C::N_KV * C::KV_BYTES);
           const int n0 = t * BN;
-          tma_load_3d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, it.bh);
-          tma_load_3d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, it.bh);
+          tma_load_4d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, it.h, it.b);
+          tma_load_4d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, it.h, it.b);
           if constexpr (DUAL) {
-            tma_load_3d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, it.bh);
-            tma_load_3d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, it.bh);
+            tma_load_4d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, it.h, it.b);
+            tma_load_4d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, it.h, it.b);
           }
         }
         ++kact;
@@ -510,11 +512,13 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
   Fwd64Maps maps;
   const long long BH = (long long)a.B * a.H;
   const CUtensorMapDataType dt = Fmt<T>::kTma;
-  bool ok = encode_map(&maps.q, dt, a.q, 64, a.L, BH, C::BM) && encode_map(&maps.k, dt, a.k, 64, a.L, BH, C::BN) &&
-            encode_map(&maps.v, dt, a.v, 64, a.L, BH, C::BN);
+  // (64, L, H, B) maps: the inputs may be strided views (in_stride), e.g. (B,L,H,D) tensors seen as (B,H,L,D)
+  const int64_t* st = a.in_stride;
+  bool ok = encode_map4(&maps.q, dt, a.q, a.L, a.H, a.B, st, C::BM) && encode_map4(&maps.k, dt, a.k, a.L, a.H, a.B, st, C::BN) &&
+            encode_map4(&maps.v, dt, a.v, a.L, a.H, a.B, st, C::BN);
   if (DUAL)
-    ok = ok && encode_map(&maps.tq, dt, a.tq, 64, a.L, BH, C::BM) && encode_map(&maps.tk, dt, a.tk, 64, a.L, BH, C::BN) &&
-         encode_map(&maps.tv, dt, a.tv, 64, a.L, BH, C::BN);
+    ok = ok && encode_map4(&maps.tq, dt, a.tq, a.L, a.H, a.B, st, C::BM) &&
+         encode_map4(&maps.tk, dt, a.tk, a.L, a.H, a.B, st, C::BN) && encode_map4(&maps.tv, dt, a.tv, a.L, a.H, a.B, st, C::BN);
   else
     maps.tq = maps.tk = maps.tv = maps.q;
   if (!ok) {

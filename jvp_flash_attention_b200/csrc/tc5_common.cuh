@@ -56,6 +56,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Host: (D, L, B*H) view of a contiguous (B, H, L, D) 16-bit tensor, box = 64 columns x box_rows
 // rows, 128-byte swizzle, out-of-range rows read as zero.  Defined in fwd_tc5.cu.
 bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH, int box_rows);
+// Host: (64, L, H, B) view of a 16-bit tensor whose batch / head / row strides (in elements) are given
+// (all zero: (B,H,L,64) row-major); same box, swizzle and fill.  Defined in fwd_tc5.cu.
+bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* stride_bhl,
+                 int box_rows);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -155,6 +159,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y,
+                                            int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
       : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {

@@ -110,16 +110,32 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
     return _lib.MaskSpec(_lib.MASK_BIAS, m, bstrides(m), _lib.DTYPE_ENUM[m.dtype]), 2, attn_mask
 
 
+def _in_place_layout(ts):
+    """``(tensors, in_stride)`` for the kernels: the tensors as they are together with their common (batch, head,
+    row) strides when they share a layout the kernels can read in place (e.g. the (B,H,L,D) view of a
+    (B,L,H,D) tensor; upstream always copies, jvp_attention.py:2733-2734), else contiguous copies and None."""
+    try:
+        return ts, _lib.common_strides(*ts)
+    except ValueError:
+        return [None if t is None else t.contiguous() for t in ts], None
+
+
 def _launch_fwd(q, k, v, tq, tk, tv, spec: _lib.MaskSpec, sm_scale: float):
     """Allocates outputs and runs the fused forward.  Returns (o, to | None, lse, mu | None)."""
-    q, k, v, tq, tk, tv = (_unwrap(x) for x in (q, k, v, tq, tk, tv))
-    Z, H, N, _ = q.shape
-    o = torch.empty_like(q)
-    lse = torch.empty((Z, H, N), device=q.device, dtype=torch.float32)
-    dual = tq is not None
-    to = torch.empty_like(q) if dual else None
+    ins, st = _in_place_layout([_unwrap(x) for x in (q, k, v, tq, tk, tv)])
+    Z, H, N, _ = ins[0].shape
+    o = torch.empty(ins[0].shape, device=ins[0].device, dtype=ins[0].dtype)
+    lse = torch.empty((Z, H, N), device=o.device, dtype=torch.float32)
+    dual = ins[3] is not None
+    to = torch.empty_like(o) if dual else None
     mu = torch.empty_like(lse) if dual else None
-    _lib.fwd(q, k, v, tq, tk, tv, o, to, lse, mu, spec, sm_scale, KERNEL_IMPL)
+    if st is not None:
+        try:
+            _lib.fwd(*ins, o, to, lse, mu, spec, sm_scale, KERNEL_IMPL, in_stride=st)
+            return o, to, lse, mu
+        except _lib.Unsupported:  # this kernel family wants row-major inputs
+            ins = [None if t is None else t.contiguous() for t in ins]
+    _lib.fwd(*ins, o, to, lse, mu, spec, sm_scale, KERNEL_IMPL)
     return o, to, lse, mu
 
 
@@ -134,22 +150,28 @@ def _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec: _lib.MaskSpe
         gto = gto.contiguous()
     if gto is None:
         tq = tk = tv = to = mu = None
+    ins, st = _in_place_layout([q, k, v, tq, tk, tv])
     Z, H, N, _ = q.shape
     stats = torch.empty((3, Z, H, N), device=q.device, dtype=torch.float32)
     delta, eps, cterm = stats[0], stats[1], stats[2]
     _lib.bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    _lib.bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL)
+    dq, dk, dv = (torch.empty(q.shape, device=q.device, dtype=q.dtype) for _ in range(3))
+    if st is not None:
+        try:
+            _lib.bwd(*ins, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL, in_stride=st)
+            return dq, dk, dv
+        except _lib.Unsupported:
+            ins = [None if t is None else t.contiguous() for t in ins]
+    _lib.bwd(*ins, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL)
     return dq, dk, dv
 
 
 def _check_bwd_layout(q, k, v, o):
-    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and o.is_contiguous()):
-        raise ValueError(
-            "JVPAttn expected q, k, v, o to be contiguous; got "
-            f"q.is_contiguous()={q.is_contiguous()}, k.is_contiguous()={k.is_contiguous()}, "
-            f"v.is_contiguous()={v.is_contiguous()}, o.is_contiguous()={o.is_contiguous()}"
-        )
+    """Upstream refuses non-contiguous saved tensors in backward (jvp_attention.py:2858-2877).  Here q, k, v may
+    keep the strided layout they had in forward (they are read in place or copied by _launch_bwd); the
+    output, which this library allocated itself, must still be row-major."""
+    if not o.is_contiguous():
+        raise ValueError(f"JVPAttn expected o to be contiguous; got o.is_contiguous()={o.is_contiguous()}")
 
 
 class _AttnBwd(Function):
@@ -338,9 +360,8 @@ class JVPAttn(Function):
         tangents = [q_t, k_t, v_t]
         if any(t is not None for t in tangents):
             tangents = [torch.zeros_like(q) if t is None else t for t in tangents]
-        qc, kc, vc = (x if x.is_contiguous() else x.contiguous() for x in (q, k, v))
-        tq, tk, tv = (None if t is None else (t if t.is_contiguous() else t.contiguous()).to(q.dtype)
-                      for t in tangents)
+        qc, kc, vc = q, k, v  # strided views are read in place where the kernels can (_launch_fwd)
+        tq, tk, tv = (None if t is None else t.to(q.dtype) for t in tangents)
 
         spec, MASK_TYPE, mask_tensor = classify_mask(attn_mask, causal, Z, H, N_CTX, q.dtype, verify_attn_mask)
         o, o_t, M, mu = _launch_fwd(qc, kc, vc, tq, tk, tv, spec, sm_scale)
@@ -383,8 +404,6 @@ class JVPAttn(Function):
         USE_TMA: bool = True,
     ) -> Tensor:
         """Primal-only attention (upstream: jvp_attention.py:2701-2752).  Returns O."""
-        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
-            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         out = JVPAttn.apply(q, k, v, None, None, None, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
                             USE_TMA)
         a, _ = out
@@ -408,8 +427,6 @@ class JVPAttn(Function):
         is a dual tensor whose tangent is tO.  Tangents are unpacked here, before autograd sees
         them, and travel to the kernel as explicit arguments.
         """
-        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
-            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         _, q_t = fwAD.unpack_dual(q)
         _, k_t = fwAD.unpack_dual(k)
         _, v_t = fwAD.unpack_dual(v)

@@ -568,3 +568,58 @@ def test_reference_harness_grid_short_lengths(dt):
     assert len(rows) == 12
     bad = [(r["seq_len"], r["mask"], r["causal"], r["max_error"]) for r in rows if not r["pass"]]
     assert not bad, bad
+
+
+@pytest.mark.parametrize("dt,kind", [("bf16", "causal"), ("fp16", "kvlen"), ("bf16", "none")])
+def test_strided_views_are_read_in_place(dt, kind):
+    """q, k, v (and tangents) given as the (B,H,L,D) view of (B,L,H,D) tensors -- what a model's projection layer
+    produces before `.transpose(1, 2)` -- go to the D = 64 tcgen05 kernels with their strides (no copy; the
+    reference always calls `.contiguous()`, jvp_attention.py:2733-2734).  Results must equal those from
+    contiguous copies bit for bit, through the C ABI and through the public API with gradients."""
+    dtype, dev = DT[dt], torch.device("cuda:0")
+    B, H, L, D = 3, 5, 200, 64
+    g = torch.Generator().manual_seed(11)
+    base = [torch.randn(B, L, H, D, generator=g) for _ in range(8)]
+    for i in (3, 4, 5):
+        base[i] = base[i] * 0.1
+    views = [x.to(dtype).to(dev).transpose(1, 2) for x in base]  # (B,H,L,D), strides (L*H*D, D, H*D, 1)
+    q, k, v, tq, tk, tv, w1, w2 = views
+    assert not q.is_contiguous()
+    mask, causal = _mask(kind, B, H, L, dtype, seed=3)
+    spec, _, _ = ja.classify_mask(None if mask is None else mask.to(dev), causal, B, H, L, dtype, False)
+
+    def run_abi(ins, st):
+        o, to = torch.empty(B, H, L, D, device=dev, dtype=dtype), torch.empty(B, H, L, D, device=dev, dtype=dtype)
+        lse, mu = torch.empty(B, H, L, device=dev), torch.empty(B, H, L, device=dev)
+        _lib.fwd(*ins, o, to, lse, mu, spec, D**-0.5, _lib.IMPL_TCGEN05, in_stride=st)
+        go, gto = w1.contiguous(), w2.contiguous()
+        stats = torch.empty(3, B, H, L, device=dev)
+        _lib.bwd_preprocess(o, to, go, gto, mu, stats[0], stats[1], stats[2])
+        dq, dk, dv = (torch.empty(B, H, L, D, device=dev, dtype=dtype) for _ in range(3))
+        _lib.bwd(*ins, go, gto, lse, mu, stats[0], stats[1], stats[2], dq, dk, dv, spec, D**-0.5, _lib.IMPL_TCGEN05,
+                 in_stride=st)
+        torch.cuda.synchronize()
+        return o, to, lse, mu, dq, dk, dv
+
+    st = _lib.common_strides(q, k, v, tq, tk, tv)
+    assert st == (L * H * D, D, H * D)
+    strided = run_abi([q, k, v, tq, tk, tv], st)
+    dense = run_abi([x.contiguous() for x in (q, k, v, tq, tk, tv)], None)
+    assert _lib.device_status() == 0
+    for name, a, b in zip(("o", "to", "lse", "mu", "dq", "dk", "dv"), strided, dense):
+        assert torch.equal(a, b), name
+
+    # public API: views in, gradients w.r.t. the views out
+    def api(qq, kk, vv):
+        a = [x.detach().clone().requires_grad_() if x.is_contiguous() else x.detach().requires_grad_() for x in (qq, kk, vv)]
+        o, to = torch.func.jvp(lambda x, y, z: ja.JVPAttn.fwd_dual(x, y, z, attn_mask=None if mask is None else mask.to(dev),
+                                                                  causal=causal), tuple(a), (tq, tk, tv))
+        loss = (o.float() * w1.float()).sum() + (to.float() * w2.float()).sum()
+        return (o.detach(), to.detach()) + torch.autograd.grad(loss, a)
+
+    for a, b in zip(api(q, k, v), api(q.contiguous(), k.contiguous(), v.contiguous())):
+        assert torch.equal(a.contiguous(), b.contiguous())
+    # a layout the kernels cannot read in place (fp32 goes to the register-tiled family) is still served
+    o32 = ja.JVPAttn.fwd(q.float(), k.float(), v.float(), causal=causal)
+    ro = orc.sdpa_primal(q.float().cpu(), k.float().cpu(), v.float().cpu(), causal=causal)
+    assert orc.rel_err(o32, ro) < 1e-5
