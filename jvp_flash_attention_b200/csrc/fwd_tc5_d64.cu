@@ -1,5 +1,5 @@
 // Fused primal (+ tangent) attention forward for head dimension 64 (bf16 / fp16; none, causal,
-// key padding) on tcgen05 / TMA / TMEM: the variant of fwd_tc5.cu tuned to how the B200 tensor
+// key padding, and -- template parameter MK -- boolean masks and additive bias) on tcgen05 / TMA / TMEM: the variant of fwd_tc5.cu tuned to how the B200 tensor
 // pipe is fed.  A single thread can issue a tcgen05.mma only about every 58-70 cycles whatever
 // N <= 128 is, so the kernel (a) halves the instruction count by letting one N=128 instruction
 // cover two accumulators that share the A operand and whose B tiles are neighbours in shared
@@ -16,6 +16,13 @@
 // P and W = P*tS*scale are written as packed 16-bit values over the head of S and tS and feed
 // issuer B's MMAs as TMEM A operands.  Online softmax with lazy rescaling as in fwd_tc5.cu; the
 // per-row arithmetic uses packed fp32x2 instructions.
+//
+// Masks and bias (MK = 1: uint8 mask, MK = 2: bias of the element type T).  A softmax thread owns one
+// query row, so its share of a mask tile is 64 consecutive elements of one mask row: 64 or 128 bytes,
+// fetched as 16-byte read-only loads that are issued before the thread waits for the tile's scores,
+// and applied while the scores are scaled.  Broadcast dimensions are strides of zero.  The key
+// stride must be 1, every row start 16-byte aligned and L a multiple of 16 (checked by the host
+// code, which otherwise sends the request to the register-tiled kernels).
 #include "tc5_common.cuh"
 
 namespace jvpfa {
@@ -54,7 +61,24 @@ struct FwdItem {
   int bh, b, h, m0, n_valid, n_tiles;
 };
 
-template <typename T, bool DUAL>
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t w);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+template <typename T, bool DUAL, int MK>
 __global__ void __launch_bounds__(224, 2)
 fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps maps, int* status) {
   using C = Fwd64Cfg<DUAL>;
@@ -353,8 +377,25 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         continue;
       }
       float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
+      // MK != 0: this thread's row of the mask / bias (rows past L are clamped; their results are not stored)
+      constexpr int MESZ = MK == 1 ? 1 : 2;          // bytes per mask element
+      constexpr int MW = MK == 0 ? 1 : 16 * MESZ;    // 32-bit words per row of a 64-key tile
+      const unsigned char* mrow = nullptr;
+      if constexpr (MK != 0)
+        mrow = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
+               ((long long)it.b * a.mask.stride[0] + (long long)it.h * a.mask.stride[1] +
+                (long long)min(i, L - 1) * a.mask.stride[2]) * MESZ;
       for (int t = 0; t < it.n_tiles; ++t, ++g) {
         const int n0 = t * BN;
+        uint32_t mw[MW];
+        if constexpr (MK != 0) {  // issued before the wait: the loads fly while the scores are formed
+#pragma unroll
+          for (int j = 0; j < MW / 4; ++j) {
+            uint4 r = make_uint4(0u, 0u, 0u, 0u);
+            if (n0 + (j + 1) * (16 / MESZ) <= L) r = ldg_nc_v4(mrow + (size_t)n0 * MESZ + 16 * j);
+            mw[4 * j] = r.x, mw[4 * j + 1] = r.y, mw[4 * j + 2] = r.z, mw[4 * j + 3] = r.w;
+          }
+        }
         if (!mbar_wait(s_full, g & 1, ab, kAbortSFull)) {
           alive = false;
           break;
@@ -373,6 +414,19 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         for (int c = 0; c < 16; ++c) {
           float2 v0 = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), c2);
           float2 v1 = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), c2);
+          if constexpr (MK == 1) {  // one byte per key: columns 2c, 2c+1 and 32+2c, 33+2c
+            constexpr uint32_t kLoByte = 0xffu, kHiByte = 0xff00u;
+            const uint32_t wa = mw[c >> 1] >> ((c & 1) * 16), wb = mw[8 + (c >> 1)] >> ((c & 1) * 16);
+            if (!(wa & kLoByte)) v0.x = -INFINITY;
+            if (!(wa & kHiByte)) v0.y = -INFINITY;
+            if (!(wb & kLoByte)) v1.x = -INFINITY;
+            if (!(wb & kHiByte)) v1.y = -INFINITY;
+          }
+          if constexpr (MK == 2) {  // scores are in log2 units: bias * log2(e)
+            const float2 l2 = make_float2(kLog2e, kLog2e);
+            v0 = __ffma2_rn(unpack2<T>(mw[c]), l2, v0);
+            v1 = __ffma2_rn(unpack2<T>(mw[16 + c]), l2, v1);
+          }
           if (partial) {
             if (2 * c >= col_hi) v0.x = -INFINITY;
             if (2 * c + 1 >= col_hi) v0.y = -INFINITY;
@@ -501,7 +555,7 @@ static int fwd_sm_count() {
   return cache[dev];
 }
 
-template <typename T, bool DUAL>
+template <typename T, bool DUAL, int MK>
 static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = Fwd64Cfg<DUAL>;
   int* status = tc5_status_device_ptr();
@@ -525,7 +579,7 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(fwd d64)");
     return JVPFA_ERR_CUDA;
   }
-  auto kern = fwd_tc5_d64_kernel<T, DUAL>;
+  auto kern = fwd_tc5_d64_kernel<T, DUAL, MK>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(fwd_tc5_d64)");
@@ -545,7 +599,7 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const long long rounds = (n_items + slots - 1) / slots;
   bool persistent = n_items > slots;
   if (persistent && a.mask.kind != JVPFA_MASK_CAUSAL)
-    persistent = a.mask.kind == JVPFA_MASK_NONE ? (n_items * 100 >= rounds * slots * 95) : rounds >= 8;
+    persistent = a.mask.kind != JVPFA_MASK_KVLEN ? (n_items * 100 >= rounds * slots * 95) : rounds >= 8;
   const int grid = (int)(persistent ? slots : n_items);
   kern<<<grid, C::NTHREADS, C::SMEM_BYTES, stream>>>(a, maps, status);
   e = cudaGetLastError();
@@ -558,12 +612,19 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
 
 }  // namespace tc5
 
-int launch_fwd_tc5_d64(const jvpfa_fwd_args& a, cudaStream_t s) {
+template <typename T>
+static int launch_fwd64_t(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
+  if (a.mask.kind == JVPFA_MASK_BOOL)
+    return dual ? tc5::launch_fwd64<T, true, 1>(a, s) : tc5::launch_fwd64<T, false, 1>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BIAS)
+    return dual ? tc5::launch_fwd64<T, true, 2>(a, s) : tc5::launch_fwd64<T, false, 2>(a, s);
   if (!dual) return launch_fwd_tc5_sub32(a, s);  // primal only: 32-key sub-tile pipeline (fwd_tc5_sub32.cu)
-  if (a.dtype == JVPFA_BF16)
-    return dual ? tc5::launch_fwd64<__nv_bfloat16, true>(a, s) : tc5::launch_fwd64<__nv_bfloat16, false>(a, s);
-  return dual ? tc5::launch_fwd64<__half, true>(a, s) : tc5::launch_fwd64<__half, false>(a, s);
+  return tc5::launch_fwd64<T, true, 0>(a, s);
+}
+
+int launch_fwd_tc5_d64(const jvpfa_fwd_args& a, cudaStream_t s) {
+  return a.dtype == JVPFA_BF16 ? launch_fwd64_t<__nv_bfloat16>(a, s) : launch_fwd64_t<__half>(a, s);
 }
 
 }  // namespace jvpfa

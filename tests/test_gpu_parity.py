@@ -69,6 +69,11 @@ def _mask(kind, B, H, L, dtype, seed):
         m = torch.rand(1, H, L, L, generator=g) > 0.3
         m[..., 0] = True
         return m, False
+    if kind == "bool_keys":  # one row of keys per batch entry, not a prefix: stays a boolean mask with row stride 0
+        m = torch.rand(B, 1, 1, L, generator=g) > 0.4
+        m[..., 0] = False
+        m[..., 1] = True
+        return m, False
     if kind == "bias":
         return torch.randn(B, H, L, L, generator=g).clamp_(-5, 5).to(dtype), False
     if kind == "bias_f32_bcast":
@@ -136,6 +141,10 @@ TC5_CASES = [
     ("bf16", 1, 2, 160, 64, "causal", True), ("bf16", 1, 2, 256, 128, "none", True),
     ("fp16", 2, 1, 320, 128, "causal", True), ("fp16", 1, 3, 96, 128, "kvlen", False),
     ("bf16", 2, 2, 1024, 64, "causal", True), ("fp16", 1, 2, 34, 64, "none", True),
+    # boolean masks and bias of the element type, read row by row by the softmax threads (D = 64)
+    ("bf16", 2, 2, 256, 64, "bool", True), ("fp16", 2, 3, 192, 64, "bias", True), ("bf16", 1, 2, 160, 64, "bool_bcast", True),
+    ("bf16", 2, 2, 128, 64, "bias", False), ("fp16", 1, 2, 96, 64, "bool", False), ("fp16", 3, 2, 224, 64, "bool_keys", True),
+    ("bf16", 2, 2, 48, 64, "bias", True),
 ]
 
 
@@ -247,9 +256,25 @@ def test_tcgen05_dispatch_rules():
     assert lib.jvpfa_fwd(C.byref(a), None) == -9  # forcing an ineligible shape is an error, not a fallback
     a.impl, a.D, a.dtype = _lib.IMPL_AUTO, 64, _lib.FP32
     assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
-    a.dtype = _lib.FP16
+    # boolean masks / bias: D = 64, unit key stride, 16-byte aligned rows, L % 16 == 0, bias of the element type
+    a.dtype, a.sm_scale = _lib.FP16, 0.125
     a.mask.kind = _lib.MASK_BOOL
     a.mask.ptr = x.data_ptr()
+    a.mask.stride[:] = [0, 0, 64, 1]
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 1
+    a.mask.stride[:] = [0, 0, 128, 2]
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.mask.stride[:] = [0, 0, 72, 1]
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.mask.stride[:] = [0, 0, 64, 1]
+    a.mask.ptr = x.data_ptr() + 8
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.mask.ptr = x.data_ptr()
+    a.mask.kind, a.mask.bias_dtype = _lib.MASK_BIAS, _lib.FP16
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 1
+    a.mask.bias_dtype = _lib.FP32
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.mask.bias_dtype, a.D = _lib.FP16, 128
     assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
 
 
@@ -288,6 +313,15 @@ def test_fully_masked_rows_give_zero_and_no_nan():
     for x, r_, n in ((o, ro, "O"), (to, rto, "tO"), (dq, rdq, "dq"), (dk, rdk, "dk"), (dv, rdv, "dv")):
         assert torch.isfinite(x).all(), n
         _close(x, r_, torch.float32, n)
+    # the same rows through the tcgen05 forward (16-bit inputs)
+    h = lambda x: x.to(torch.bfloat16)  # noqa: E731
+    o, to, lse, mu, *_ = _run_kernels(h(q), h(k), h(v), h(tq), h(tk), h(tv), None, None, mask, False, impl=_lib.IMPL_TCGEN05)
+    assert _lib.device_status() == 0
+    assert o[0, 0, 5].abs().max() == 0 and to[0, 1, 40:48].abs().max() == 0 and torch.isinf(lse[0, 0, 5])
+    assert torch.isfinite(o).all() and torch.isfinite(to).all() and torch.isfinite(mu).all()
+    ro, rto = orc.sdpa_jvp(h(q), h(k), h(v), h(tq), h(tk), h(tv), attn_mask=mask)
+    _close(o, ro, torch.bfloat16, "O (tcgen05)")
+    _close(to, rto, torch.bfloat16, "tO (tcgen05)")
 
 
 def test_kvlen_zero_and_full():
