@@ -210,6 +210,28 @@ typedef struct {
 
 int jvpfa_bwd_noalloc(const jvpfa_bwd_noalloc_args* args, void* stream);
 
+/*
+ * jvpfa_mask_check -- the checks upstream makes on a user mask before a forward, in one pass.
+ * Replaces the eager reductions `attn_mask.any(dim=(-1, -2)).all()`, `torch.isinf(attn_mask).any()`,
+ * `torch.isnan(attn_mask).any()` and `(attn_mask != MASK_CONST).any(dim=(-1, -2)).all()`
+ * (jvp_attention.py:2438-2457), each of which sweeps the whole mask and synchronises with the host.
+ *
+ * mask describes the tensor as for jvpfa_fwd (kind BOOL or BIAS; strides in elements); n_b, n_h,
+ * n_rows are the mask's OWN extents along batch, head and query (1 where it broadcasts), L its key
+ * extent.  out points to 1 + n_b*n_h int32 that the caller has zeroed:
+ *   out[0]            bit 0: a floating-point mask holds an inf; bit 1: it holds a NaN
+ *   out[1 + b*n_h+h]  1 if head (b, h) has an entry that is true (BOOL) / not -100.0 (BIAS)
+ * The caller copies out back to the host (the one synchronisation) and raises what upstream raises.
+ */
+typedef struct {
+  int32_t struct_size; /* sizeof(jvpfa_mask_check_args) */
+  int32_t n_b, n_h, n_rows, L;
+  jvpfa_mask mask;
+  int32_t* out;
+} jvpfa_mask_check_args;
+
+int jvpfa_mask_check(const jvpfa_mask_check_args* args, void* stream);
+
 /* Human-readable text for a jvpfa_status (static storage, never NULL). */
 const char* jvpfa_strerror(int status);
 

@@ -32,6 +32,7 @@ EXPORTS = (
     "jvpfa_bwd_uses_tcgen05",
     "jvpfa_device_status",
     "jvpfa_bwd_noalloc",
+    "jvpfa_mask_check",
 )
 
 NOALLOC_MAX_ROWS = 524288  # JVPFA_NOALLOC_MAX_ROWS
@@ -151,6 +152,18 @@ class BwdNoAllocArgs(C.Structure):
     ]
 
 
+class MaskCheckArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("n_b", C.c_int32),
+        ("n_h", C.c_int32),
+        ("n_rows", C.c_int32),
+        ("L", C.c_int32),
+        ("mask", Mask),
+        ("out", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -185,6 +198,8 @@ def load() -> C.CDLL:
     lib.jvpfa_device_status.restype = C.c_int
     lib.jvpfa_bwd_noalloc.argtypes = [C.POINTER(BwdNoAllocArgs), C.c_void_p]
     lib.jvpfa_bwd_noalloc.restype = C.c_int
+    lib.jvpfa_mask_check.argtypes = [C.POINTER(MaskCheckArgs), C.c_void_p]
+    lib.jvpfa_mask_check.restype = C.c_int
     _lib = lib
     return lib
 
@@ -288,6 +303,25 @@ def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, im
     if rc == ERR_UNSUPPORTED and in_stride is not None:
         raise Unsupported("jvpfa_fwd cannot read this layout in place")
     check(rc, "jvpfa_fwd")
+
+
+def mask_check(mask: "MaskSpec", shape) -> tuple[bool, bool]:
+    """Launches jvpfa_mask_check over a boolean or floating-point mask of the given own shape
+    (n_b, n_h, n_rows, L) and reads the answer back (one synchronisation).  Returns
+    ``(every head has a live entry, an inf is present, a NaN is present)``."""
+    lib = load()
+    t = mask.tensor
+    n_b, n_h, n_rows, L = (int(x) for x in shape)
+    out = torch.zeros(1 + n_b * n_h, device=t.device, dtype=torch.int32)
+    a = MaskCheckArgs()
+    a.struct_size = C.sizeof(MaskCheckArgs)
+    a.n_b, a.n_h, a.n_rows, a.L = n_b, n_h, n_rows, L
+    a.mask = mask.to_c()
+    a.out = out.data_ptr()
+    with torch.cuda.device(t.device):
+        check(lib.jvpfa_mask_check(C.byref(a), _stream(t)), "jvpfa_mask_check")
+    flags = out.tolist()
+    return all(flags[1:]), bool(flags[0] & 1), bool(flags[0] & 2)
 
 
 def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:

@@ -182,6 +182,22 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   return launch_bwd_generic(*a, s);
 }
 
+int jvpfa_mask_check(const jvpfa_mask_check_args* a, void* stream) {
+  if (!a) return JVPFA_ERR_NULL;
+  if (a->struct_size != (int32_t)sizeof(jvpfa_mask_check_args)) return JVPFA_ERR_STRUCT;
+  if (a->n_b < 1 || a->n_h < 1 || a->n_rows < 1 || a->L < 1) return JVPFA_ERR_SHAPE;
+  if ((long long)a->n_b * a->n_h > 65535LL) return JVPFA_ERR_TOO_LARGE;  // grid.y limit
+  if (!a->out) return JVPFA_ERR_NULL;
+  if (a->mask.kind != JVPFA_MASK_BOOL && a->mask.kind != JVPFA_MASK_BIAS) return JVPFA_ERR_MASK;
+  int rc = check_mask(a->mask);
+  if (rc) return rc;
+  for (int d = 0; d < 4; ++d)
+    if (a->mask.stride[d] < 0) return JVPFA_ERR_MASK;
+  rc = check_arch();
+  if (rc) return rc;
+  return launch_mask_check(*a, static_cast<cudaStream_t>(stream));
+}
+
 int jvpfa_device_status(int* status, int clear) {
   if (!status) return JVPFA_ERR_NULL;
   return tc5_read_status(status, clear);

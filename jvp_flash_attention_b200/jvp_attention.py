@@ -86,8 +86,11 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
         return tuple(0 if t.shape[d] == 1 else t.stride(d) for d in range(4))
 
     if m.dtype == torch.bool:
+        m8 = m.view(torch.uint8) if m.is_contiguous() or m.stride(-1) == 1 else m.contiguous().view(torch.uint8)
+        spec = _lib.MaskSpec(_lib.MASK_BOOL, m8, bstrides(m8))
         if verify:
-            assert m.any(dim=(-1, -2)).all(), "The attention mask cannot be all False for any head."
+            every_head_live, _, _ = _lib.mask_check(spec, m8.shape)
+            assert every_head_live, "The attention mask cannot be all False for any head."
         if mh == 1 and mi == 1:
             # Candidate key-padding mask: valid keys form a prefix of each row.
             rows = m.reshape(mz, N)
@@ -96,18 +99,18 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
             if bool((prefix == rows).all()):
                 kv_len = lens.expand(Z).contiguous() if mz == 1 else lens.contiguous()
                 return _lib.MaskSpec(_lib.MASK_KVLEN, kv_len), 1, attn_mask
-        m8 = m.view(torch.uint8) if m.is_contiguous() or m.stride(-1) == 1 else m.contiguous().view(torch.uint8)
-        return _lib.MaskSpec(_lib.MASK_BOOL, m8, bstrides(m8)), 1, attn_mask
+        return spec, 1, attn_mask
 
     if m.dtype not in _lib.DTYPE_ENUM:
         m = m.to(torch.float32)
+    spec = _lib.MaskSpec(_lib.MASK_BIAS, m, bstrides(m), _lib.DTYPE_ENUM[m.dtype])
     if verify:
-        assert not torch.isinf(m).any(), "The attention mask cannot contain -inf or inf."
-        assert not torch.isnan(m).any(), "The attention mask cannot contain NaNs."
-        assert (m != MASK_CONST).any(dim=(-1, -2)).all(), (
-            f"The attention mask cannot be all {MASK_CONST} (the masking constant) for any head."
-        )
-    return _lib.MaskSpec(_lib.MASK_BIAS, m, bstrides(m), _lib.DTYPE_ENUM[m.dtype]), 2, attn_mask
+        # one pass and one read-back for upstream's isinf / isnan / "all MASK_CONST" sweeps (jvp_attention.py:2447-2457)
+        every_head_live, has_inf, has_nan = _lib.mask_check(spec, m.shape)
+        assert not has_inf, "The attention mask cannot contain -inf or inf."
+        assert not has_nan, "The attention mask cannot contain NaNs."
+        assert every_head_live, f"The attention mask cannot be all {MASK_CONST} (the masking constant) for any head."
+    return spec, 2, attn_mask
 
 
 def _in_place_layout(ts):

@@ -38,3 +38,12 @@ def launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec, sm_scale):
     d = orc.closed_form_backward(q, k, v, tq, tk, tv, go, gto, lse.double(), None if mu is None else mu.double(),
                                  attn_mask=mask, causal=causal, scale=sm_scale)
     return tuple(torch.from_numpy(x).to(q.dtype) for x in d)
+
+
+def mask_check(spec, shape):
+    """Stand-in for the device pass jvpfa_mask_check: the same three answers from eager reductions
+    (what upstream computes, jvp_attention.py:2438-2457)."""
+    t = spec.tensor.reshape(tuple(shape)) if spec.tensor.numel() == int(torch.tensor(tuple(shape)).prod()) else spec.tensor
+    if spec.kind == _lib.MASK_BOOL:
+        return bool(t.bool().any(dim=(-1, -2)).all()), False, False
+    return bool((t != -100.0).any(dim=(-1, -2)).all()), bool(torch.isinf(t).any()), bool(torch.isnan(t).any())

@@ -657,3 +657,57 @@ def test_strided_views_are_read_in_place(dt, kind):
     o32 = ja.JVPAttn.fwd(q.float(), k.float(), v.float(), causal=causal)
     ro = orc.sdpa_primal(q.float().cpu(), k.float().cpu(), v.float().cpu(), causal=causal)
     assert orc.rel_err(o32, ro) < 1e-5
+
+
+def test_mask_verification_is_one_device_pass():
+    """`verify_attn_mask=True` (the default, as upstream: jvp_attention.py:2438-2457) raises what upstream raises,
+    from the flags of one jvpfa_mask_check pass: a boolean head without a True, an inf, a NaN, a float head that
+    is all MASK_CONST.  Vector and element-wise reading paths, broadcast extents, all mask dtypes."""
+    dev = torch.device("cuda:0")
+    B, H, L, D = 2, 3, 64, 64
+    q, k, v, *_ = (x.to(dev) for x in _make(B, H, L, D, torch.bfloat16, seed=21))
+    g = torch.Generator().manual_seed(5)
+    ok = (torch.rand(B, H, L, L, generator=g) > 0.9)
+    ok[..., 7] = True
+    ja.attention(q, k, v, attn_mask=ok.to(dev))
+    bad = ok.clone()
+    bad[1, 2] = False
+    with pytest.raises(AssertionError, match="all False"):
+        ja.attention(q, k, v, attn_mask=bad.to(dev))
+    # not looked at when switched off (the trailing optional argument of apply, as upstream: jvp_attention.py:2324)
+    ja.JVPAttn.apply(q, k, v, None, None, None, bad.to(dev), 0.0, False, None, True, True, False)
+    for own in ((1, H, L, L), (B, 1, 1, L), (B, H, L, L)):
+        m = torch.rand(*own, generator=g) > 0.5
+        m[..., 3] = True
+        m[..., 5] = False  # never a key-padding prefix
+        ja.attention(q, k, v, attn_mask=m.to(dev))
+        m[own[0] - 1, own[1] - 1] = False
+        with pytest.raises(AssertionError, match="all False"):
+            ja.attention(q, k, v, attn_mask=m.to(dev))
+    odd = ok.to(dev)[..., ::2].repeat_interleave(2, dim=-1)  # fresh tensor
+    view = torch.zeros(B, H, L, 2 * L, dtype=torch.bool, device=dev)[..., ::2]  # key stride 2: element-wise path
+    view.copy_(odd)
+    spec, _, _ = ja.classify_mask(view, False, B, H, L, torch.bfloat16, True)
+    for mdt in (torch.bfloat16, torch.float16, torch.float32):
+        bias = torch.where(ok, 0.0, ja.MASK_CONST).to(mdt).to(dev)
+        ja.attention(q, k, v, attn_mask=bias)
+        x = bias.clone()
+        x[0, 1] = ja.MASK_CONST
+        with pytest.raises(AssertionError, match="masking constant"):
+            ja.attention(q, k, v, attn_mask=x)
+        x = bias.clone()
+        x[1, 0, 5, 9] = float("inf")
+        with pytest.raises(AssertionError, match="-inf or inf"):
+            ja.attention(q, k, v, attn_mask=x)
+        x[1, 0, 5, 9] = float("-inf")
+        with pytest.raises(AssertionError, match="-inf or inf"):
+            ja.attention(q, k, v, attn_mask=x)
+        x[1, 0, 5, 9] = float("nan")
+        with pytest.raises(AssertionError, match="NaNs"):
+            ja.attention(q, k, v, attn_mask=x)
+        sl = torch.zeros(B, H, L, L + 8, dtype=mdt, device=dev)[..., 4:L + 4]  # rows not 16-byte aligned
+        sl.copy_(bias)
+        ja.attention(q, k, v, attn_mask=sl)
+        sl[0, 0] = ja.MASK_CONST
+        with pytest.raises(AssertionError, match="masking constant"):
+            ja.attention(q, k, v, attn_mask=sl)
