@@ -111,6 +111,9 @@ typedef struct {
    * JVPFA_ERR_UNSUPPORTED and the caller passes contiguous copies instead (upstream always copies:
    * jvp_attention.py:2733-2734, 2787-2788).  Outputs are always (B,H,L,D) row-major. */
   int64_t in_stride[3];
+  /* Optional, JVPFA_MASK_BOOL only: the bitmap written by jvpfa_mask_tiles for this mask.  The tcgen05
+   * kernel then steps over 128 x 64 tiles without a true entry; other kernels ignore it.  NULL = none. */
+  const void* mask_tile_live;
 } jvpfa_fwd_args;
 
 int jvpfa_fwd(const jvpfa_fwd_args* args, void* stream);
@@ -231,6 +234,31 @@ typedef struct {
 } jvpfa_mask_check_args;
 
 int jvpfa_mask_check(const jvpfa_mask_check_args* args, void* stream);
+
+/*
+ * jvpfa_mask_tiles -- per-tile summary of a boolean mask for block skipping, and the per-head check of
+ * jvpfa_mask_check from the same pass.  No upstream counterpart: upstream reads every L x L mask tile
+ * in every kernel (jvp_attention.py:453) and has no block skipping.
+ *
+ * The mask (kind BOOL) must have key stride 1, 16-byte aligned rows and L % 16 == 0 (else
+ * JVPFA_ERR_UNSUPPORTED).  n_b, n_h, n_rows are its own extents (1 where it broadcasts, i.e. where its
+ * stride is 0; n_rows is 1 or L).  Tiles are 128 queries x 64 keys (one tile row when n_rows == 1).
+ *   tile_live  n_b*n_h * n_qt * n_words uint64, n_qt = n_rows == 1 ? 1 : ceil(L/128),
+ *              n_words = ceil(ceil(L/64) / 64); bit (t % 64) of word t / 64 of entry [b*n_h + h][qt] is
+ *              set iff tile (qt, t) of head (b, h) has a true entry.  Caller zeroes it first.
+ *   head_live  n_b*n_h + 1 int32 (caller-zeroed): 1 iff the head has a true entry, and in the last
+ *              element the number of live tiles of the whole mask (a caller that reads it back can leave
+ *              the bitmap away when nearly every tile is live); may be NULL.
+ */
+typedef struct {
+  int32_t struct_size; /* sizeof(jvpfa_mask_tiles_args) */
+  int32_t n_b, n_h, n_rows, L;
+  jvpfa_mask mask;
+  void* tile_live;
+  int32_t* head_live;
+} jvpfa_mask_tiles_args;
+
+int jvpfa_mask_tiles(const jvpfa_mask_tiles_args* args, void* stream);
 
 /* Human-readable text for a jvpfa_status (static storage, never NULL). */
 const char* jvpfa_strerror(int status);

@@ -33,6 +33,7 @@ EXPORTS = (
     "jvpfa_device_status",
     "jvpfa_bwd_noalloc",
     "jvpfa_mask_check",
+    "jvpfa_mask_tiles",
 )
 
 NOALLOC_MAX_ROWS = 524288  # JVPFA_NOALLOC_MAX_ROWS
@@ -70,6 +71,7 @@ class FwdArgs(C.Structure):
         ("mu", C.c_void_p),
         ("mask", Mask),
         ("in_stride", C.c_int64 * 3),
+        ("mask_tile_live", C.c_void_p),
     ]
 
 
@@ -164,6 +166,19 @@ class MaskCheckArgs(C.Structure):
     ]
 
 
+class MaskTilesArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("n_b", C.c_int32),
+        ("n_h", C.c_int32),
+        ("n_rows", C.c_int32),
+        ("L", C.c_int32),
+        ("mask", Mask),
+        ("tile_live", C.c_void_p),
+        ("head_live", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -200,6 +215,8 @@ def load() -> C.CDLL:
     lib.jvpfa_bwd_noalloc.restype = C.c_int
     lib.jvpfa_mask_check.argtypes = [C.POINTER(MaskCheckArgs), C.c_void_p]
     lib.jvpfa_mask_check.restype = C.c_int
+    lib.jvpfa_mask_tiles.argtypes = [C.POINTER(MaskTilesArgs), C.c_void_p]
+    lib.jvpfa_mask_tiles.restype = C.c_int
     _lib = lib
     return lib
 
@@ -232,13 +249,14 @@ class MaskSpec:
     bias, or int32 kv_len) and ``strides`` are the broadcast element strides of a (B,H,L,L) view.
     """
 
-    __slots__ = ("kind", "tensor", "strides", "bias_dtype")
+    __slots__ = ("kind", "tensor", "strides", "bias_dtype", "tile_live")
 
     def __init__(self, kind=MASK_NONE, tensor=None, strides=(0, 0, 0, 0), bias_dtype=FP32):
         self.kind = kind
         self.tensor = tensor
         self.strides = tuple(int(s) for s in strides)
         self.bias_dtype = bias_dtype
+        self.tile_live = None  # MASK_BOOL: bitmap from mask_tiles(), lets the forward step over dead tiles
 
     def to_c(self) -> Mask:
         m = Mask()
@@ -296,6 +314,7 @@ def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, im
     a.tq, a.tk, a.tv = ptr(tq), ptr(tk), ptr(tv)
     a.o, a.to, a.lse, a.mu = ptr(o), ptr(to), ptr(lse), ptr(mu)
     a.mask = mask.to_c()
+    a.mask_tile_live = ptr(mask.tile_live)
     if in_stride is not None:
         a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
     with torch.cuda.device(q.device):
@@ -322,6 +341,35 @@ def mask_check(mask: "MaskSpec", shape) -> tuple[bool, bool]:
         check(lib.jvpfa_mask_check(C.byref(a), _stream(t)), "jvpfa_mask_check")
     flags = out.tolist()
     return all(flags[1:]), bool(flags[0] & 1), bool(flags[0] & 2)
+
+
+def mask_tiles(mask: "MaskSpec", L: int):
+    """Launches jvpfa_mask_tiles over a boolean mask (no synchronisation).  Returns ``(tile_live, head_live)``:
+    the int64 bitmap of 128 x 64 tiles with a true entry, which jvpfa_fwd takes for block skipping, and the
+    int32 per-head flags followed by the count of live tiles.  The mask's own extents follow its strides (0 = broadcast).  Raises Unsupported when the
+    layout cannot be read as 16-byte pieces (key stride, alignment, L % 16)."""
+    lib = load()
+    t = mask.tensor
+    n_b, n_h = (t.shape[d] if mask.strides[d] else 1 for d in (0, 1))
+    n_rows = L if mask.strides[2] else 1
+    n_qt = 1 if n_rows == 1 else (L + 127) // 128
+    n_words = ((L + 63) // 64 + 63) // 64
+    n_bitmap = n_b * n_h * n_qt * n_words * 2
+    buf = torch.zeros(n_bitmap + n_b * n_h + 1, device=t.device, dtype=torch.int32)  # one memset for both
+    tile_live = buf[:n_bitmap].view(torch.int64)
+    head_live = buf[n_bitmap:]
+    a = MaskTilesArgs()
+    a.struct_size = C.sizeof(MaskTilesArgs)
+    a.n_b, a.n_h, a.n_rows, a.L = n_b, n_h, n_rows, L
+    a.mask = mask.to_c()
+    a.tile_live = tile_live.data_ptr()
+    a.head_live = head_live.data_ptr()
+    with torch.cuda.device(t.device):
+        rc = lib.jvpfa_mask_tiles(C.byref(a), _stream(t))
+    if rc == ERR_UNSUPPORTED:
+        raise Unsupported("jvpfa_mask_tiles cannot read this mask layout")
+    check(rc, "jvpfa_mask_tiles")
+    return tile_live, head_live
 
 
 def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:

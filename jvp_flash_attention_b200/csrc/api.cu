@@ -198,6 +198,23 @@ int jvpfa_mask_check(const jvpfa_mask_check_args* a, void* stream) {
   return launch_mask_check(*a, static_cast<cudaStream_t>(stream));
 }
 
+int jvpfa_mask_tiles(const jvpfa_mask_tiles_args* a, void* stream) {
+  if (!a) return JVPFA_ERR_NULL;
+  if (a->struct_size != (int32_t)sizeof(jvpfa_mask_tiles_args)) return JVPFA_ERR_STRUCT;
+  if (a->n_b < 1 || a->n_h < 1 || a->L < 1 || (a->n_rows != 1 && a->n_rows != a->L)) return JVPFA_ERR_SHAPE;
+  if ((long long)a->n_b * a->n_h > 65535LL || (a->L + 127) / 128 > 65535) return JVPFA_ERR_TOO_LARGE;  // grid limits
+  if (!a->tile_live) return JVPFA_ERR_NULL;
+  if (a->mask.kind != JVPFA_MASK_BOOL || !a->mask.ptr) return JVPFA_ERR_MASK;
+  for (int d = 0; d < 4; ++d)
+    if (a->mask.stride[d] < 0) return JVPFA_ERR_MASK;
+  if (a->mask.stride[3] != 1 || (a->L & 15) != 0 || !aligned16(a->mask.ptr) || (a->mask.stride[0] & 15) != 0 ||
+      (a->mask.stride[1] & 15) != 0 || (a->mask.stride[2] & 15) != 0)
+    return JVPFA_ERR_UNSUPPORTED;
+  const int rc = check_arch();
+  if (rc) return rc;
+  return launch_mask_tiles(*a, static_cast<cudaStream_t>(stream));
+}
+
 int jvpfa_device_status(int* status, int clear) {
   if (!status) return JVPFA_ERR_NULL;
   return tc5_read_status(status, clear);

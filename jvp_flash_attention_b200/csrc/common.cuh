@@ -310,6 +310,7 @@ int launch_fwd_generic(const jvpfa_fwd_args& a, cudaStream_t stream);
 int launch_pre(const jvpfa_pre_args& a, cudaStream_t stream);
 int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream);
 int launch_mask_check(const jvpfa_mask_check_args& a, cudaStream_t stream);
+int launch_mask_tiles(const jvpfa_mask_tiles_args& a, cudaStream_t stream);
 int launch_fwd_tc5(const jvpfa_fwd_args& a, cudaStream_t stream);
 bool fwd_tc5_eligible(const jvpfa_fwd_args& a);
 int tc5_read_status(int* out, int clear);

@@ -23,6 +23,12 @@
 // and applied while the scores are scaled.  Broadcast dimensions are strides of zero.  The key
 // stride must be 1, every row start 16-byte aligned and L a multiple of 16 (checked by the host
 // code, which otherwise sends the request to the register-tiled kernels).
+//
+// Tile skipping (MK = 3: uint8 mask with a tile bitmap): mask_tile_live holds one bit per 128-query x 64-key tile of the
+// mask, set when the tile has a true entry (written by jvpfa_mask_tiles).  Every role reads the
+// item's words and steps over dead tiles in the same way, so the barrier phases (counted in live
+// tiles) stay in step; an item without a live tile takes the "no key" path.  It is an instantiation of
+// its own so that the kernels without a bitmap keep their plain tile loops.
 #include "tc5_common.cuh"
 
 namespace jvpfa {
@@ -59,6 +65,19 @@ __device__ __forceinline__ float2 ff2(uint32_t a, uint32_t b) { return make_floa
 // One work item of the persistent loop: a 128-row query tile of one (batch, head).
 struct FwdItem {
   int bh, b, h, m0, n_valid, n_tiles;
+  const unsigned long long* live;  // MK = 3: this item's words of the tile bitmap, or nullptr
+};
+
+// Walks an item's key tiles, telling the live ones (bit t of the item's bitmap words) from the dead.
+struct LiveTiles {
+  const unsigned long long* words;
+  unsigned long long bits;
+  __device__ __forceinline__ explicit LiveTiles(const unsigned long long* w) : words(w), bits(~0ull) {}
+  __device__ __forceinline__ bool operator()(int t) {
+    if (words == nullptr) return true;
+    if ((t & 63) == 0) bits = __ldg(words + (t >> 6));
+    return (bits >> (t & 63)) & 1ull;
+  }
 };
 
 template <typename T>
@@ -136,6 +155,20 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
     int n_end = it.n_valid;
     if (causal) n_end = min(n_end, it.m0 + BM);
     it.n_tiles = (n_end + BN - 1) / BN;
+    it.live = nullptr;
+    if constexpr (MK == 3) {
+      {
+        // the bitmap has the mask's own extents: broadcast dimensions (stride 0) have one entry
+        const int n_words = (it.n_tiles + 63) >> 6;
+        const long long hm = (a.mask.stride[0] ? (long long)it.b * (a.mask.stride[1] ? a.H : 1) : 0) +
+                             (a.mask.stride[1] ? it.h : 0);
+        const long long qm = a.mask.stride[2] ? hm * n_q_tiles + it.m0 / BM : hm;
+        it.live = reinterpret_cast<const unsigned long long*>(a.mask_tile_live) + qm * n_words;
+        bool any = false;
+        for (int w = 0; w < n_words; ++w) any = any || __ldg(it.live + w) != 0ull;
+        if (!any) it.n_tiles = 0;  // nothing to attend to: zeros and lse = +inf, as for kv_len = 0
+      }
+    }
     return true;
   };
 
@@ -181,7 +214,10 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
         tma_load_4d(sQ, &maps.q, q_full, 0, it.m0, it.h, it.b);
         if constexpr (DUAL) tma_load_4d(sTQ, &maps.tq, q_full, 0, it.m0, it.h, it.b);
-        for (int t = 0; t < it.n_tiles; ++t, ++g) {
+        LiveTiles live(it.live);
+        for (int t = 0; t < it.n_tiles; ++t) {
+          if constexpr (MK == 3)
+            if (!live(t)) continue;
           const int st = g % STAGES;
           const uint32_t ph = (g / STAGES) & 1;
           if (!mbar_wait(kv_empty + st, ph ^ 1, ab, kAbortKvEmpty)) {
@@ -197,6 +233,7 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
             tma_load_4d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, it.h, it.b);
             tma_load_4d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, it.h, it.b);
           }
+          ++g;
         }
         ++kact;
       }
@@ -213,7 +250,10 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
       for (int k = 0; ok && k < k_max; ++k) {
         if (!get_item(k, it) || it.n_tiles == 0) continue;
         if (!mbar_wait(q_full, kact & 1, ab, kAbortQFull)) break;
-        for (int t = 0; t < it.n_tiles; ++t, ++g) {
+        LiveTiles live(it.live);
+        for (int t = 0; t < it.n_tiles; ++t) {
+          if constexpr (MK == 3)
+            if (!live(t)) continue;
           const int st = g % STAGES;
           // S / tS still hold P / W of the previous tile (of this item or of the one before) until
           // issuer B's chain for it has completed.
@@ -243,6 +283,7 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
                       idesc_s, ks > 0);
           }
           tc_commit(s_full);
+          ++g;
         }
         if (ok) tc_commit(q_empty);  // arrives when the item's last scores are complete
         ++kact;
@@ -258,14 +299,19 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
       FwdItem it;
       for (int k = 0; ok && k < k_max; ++k) {
         if (!get_item(k, it) || it.n_tiles == 0) continue;
-        for (int t = 0; t < it.n_tiles; ++t, ++g) {
+        LiveTiles live(it.live);
+        bool first = true;  // the item's first live tile
+        for (int t = 0; t < it.n_tiles; ++t) {
+          if constexpr (MK == 3)
+            if (!live(t)) continue;
           const int st = g % STAGES;
           if (!mbar_wait(p_full, g & 1, ab, kAbortPFull)) {
             ok = false;
             break;
           }
           // The item's first tile overwrites O / tO': the previous item's epilogue must have read them.
-          if (t == 0 && kact > 0 && !mbar_wait(o_free, (kact - 1) & 1, ab, kAbortOFull)) {
+          if constexpr (MK != 3) first = t == 0;
+          if (first && kact > 0 && !mbar_wait(o_free, (kact - 1) & 1, ab, kAbortOFull)) {
             ok = false;
             break;
           }
@@ -275,7 +321,7 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk)  // [O | tO'] += P [V | tV]   (64-column chunks KV_BYTES apart)
               umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
-                      idesc_o2, (t > 0 || kk > 0));
+                      idesc_o2, (!first || kk > 0));
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk)  // tO' += W V
               umma_ts(tmem + C::COL_TO, tmem + C::COL_TS + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
@@ -284,9 +330,11 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk)
               umma_ts(tmem + C::COL_O, tmem + C::COL_S + kk * 8, make_smem_desc(aV + kk * 2048, C::KV_BYTES, 1024),
-                      idesc_o, (t > 0 || kk > 0));
+                      idesc_o, (!first || kk > 0));
           }
           tc_commit(kv_empty + st);
+          first = false;
+          ++g;
         }
         if (ok) tc_commit(o_full);
         ++kact;
@@ -378,15 +426,21 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
       }
       float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
       // MK != 0: this thread's row of the mask / bias (rows past L are clamped; their results are not stored)
-      constexpr int MESZ = MK == 1 ? 1 : 2;          // bytes per mask element
+      constexpr bool BOOLM = MK == 1 || MK == 3;
+      constexpr int MESZ = BOOLM ? 1 : 2;            // bytes per mask element
       constexpr int MW = MK == 0 ? 1 : 16 * MESZ;    // 32-bit words per row of a 64-key tile
       const unsigned char* mrow = nullptr;
       if constexpr (MK != 0)
         mrow = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
                ((long long)it.b * a.mask.stride[0] + (long long)it.h * a.mask.stride[1] +
                 (long long)min(i, L - 1) * a.mask.stride[2]) * MESZ;
-      for (int t = 0; t < it.n_tiles; ++t, ++g) {
+      LiveTiles live(it.live);
+      bool first = true;  // the item's first live tile
+      for (int t = 0; t < it.n_tiles; ++t) {
+        if constexpr (MK == 3)
+          if (!live(t)) continue;
         const int n0 = t * BN;
+        if constexpr (MK != 3) first = t == 0;
         uint32_t mw[MW];
         if constexpr (MK != 0) {  // issued before the wait: the loads fly while the scores are formed
 #pragma unroll
@@ -414,7 +468,7 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         for (int c = 0; c < 16; ++c) {
           float2 v0 = __fmul2_rn(ff2(x0[2 * c], x0[2 * c + 1]), c2);
           float2 v1 = __fmul2_rn(ff2(x1[2 * c], x1[2 * c + 1]), c2);
-          if constexpr (MK == 1) {  // one byte per key: columns 2c, 2c+1 and 32+2c, 33+2c
+          if constexpr (BOOLM) {  // one byte per key: columns 2c, 2c+1 and 32+2c, 33+2c
             constexpr uint32_t kLoByte = 0xffu, kHiByte = 0xff00u;
             const uint32_t wa = mw[c >> 1] >> ((c & 1) * 16), wb = mw[8 + (c >> 1)] >> ((c & 1) * 16);
             if (!(wa & kLoByte)) v0.x = -INFINITY;
@@ -446,7 +500,7 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
           m_used = mx;
         }
         const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-        if (t > 0 && __any_sync(0xffffffffu, grow)) {
+        if (!first && __any_sync(0xffffffffu, grow)) {
           const float2 al2 = make_float2(alpha, alpha);
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
@@ -521,6 +575,8 @@ fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps map
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full);
+        first = false;
+        ++g;
       }
       if (!alive) break;
       // (Deferring this behind the softmax of the next item's first tile, as the backward does, was
@@ -615,6 +671,8 @@ static int launch_fwd64(const jvpfa_fwd_args& a, cudaStream_t stream) {
 template <typename T>
 static int launch_fwd64_t(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
+  if (a.mask.kind == JVPFA_MASK_BOOL && a.mask_tile_live != nullptr)
+    return dual ? tc5::launch_fwd64<T, true, 3>(a, s) : tc5::launch_fwd64<T, false, 3>(a, s);
   if (a.mask.kind == JVPFA_MASK_BOOL)
     return dual ? tc5::launch_fwd64<T, true, 1>(a, s) : tc5::launch_fwd64<T, false, 1>(a, s);
   if (a.mask.kind == JVPFA_MASK_BIAS)

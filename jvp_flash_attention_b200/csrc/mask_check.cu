@@ -95,7 +95,64 @@ __global__ void __launch_bounds__(kCheckThreads) mask_check_kernel(const jvpfa_m
   }
 }
 
+// Tile summary of a boolean mask.  One CTA = one 128-row tile row of one head x eight 64-key tiles
+// (512 bytes of each row): lane l of a warp reads bytes [16 l, 16 l + 16) of a row, so four
+// neighbouring lanes cover one tile; the eight warps share out the rows.
+__global__ void __launch_bounds__(256) mask_tiles_kernel(const jvpfa_mask m, int n_h, int n_rows, int L, int n_qt,
+                                                         int n_words, unsigned char* tile_live, int32_t* head_live) {
+  __shared__ unsigned int s_bits;
+  const int head = blockIdx.z, qt = blockIdx.y, kg = blockIdx.x;  // kg: group of eight key tiles
+  const int b = head / n_h, h = head - b * n_h;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned char* base = reinterpret_cast<const unsigned char*>(m.ptr) + (long long)b * m.stride[0] +
+                              (long long)h * m.stride[1];
+  if (threadIdx.x == 0) s_bits = 0u;
+  __syncthreads();
+  const int col = kg * 512 + lane * 16;
+  const int r0 = qt * 128, r1 = min(n_rows, r0 + 128);
+  unsigned int any = 0u;
+  if (col + 16 <= L) {
+#pragma unroll 4
+    for (int r = r0 + warp; r < r1; r += 8) {
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(base + (long long)r * m.stride[2] + col));
+      any |= x.x | x.y | x.z | x.w;
+    }
+  }
+  const unsigned int vote = __ballot_sync(0xffffffffu, any != 0u);  // bit l: lane l saw a true entry
+  if (lane == 0 && vote != 0u) {
+    unsigned int tiles = 0u;
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+      if (vote & (0xfu << (4 * t))) tiles |= 1u << t;
+    atomicOr(&s_bits, tiles);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_bits != 0u) {
+    // byte kg of the entry's words (little endian: byte k of a word holds its bits 8k .. 8k+7)
+    tile_live[((long long)head * n_qt + qt) * n_words * 8 + kg] = (unsigned char)s_bits;
+    if (head_live) {
+      head_live[head] = 1;
+      atomicAdd(head_live + gridDim.z, __popc(s_bits));  // live tiles of the whole mask
+    }
+  }
+}
+
 }  // namespace
+
+int launch_mask_tiles(const jvpfa_mask_tiles_args& a, cudaStream_t stream) {
+  const int n_kt = (a.L + 63) / 64;
+  const int n_words = (n_kt + 63) / 64;
+  const int n_qt = a.n_rows == 1 ? 1 : (a.L + 127) / 128;
+  const dim3 grid((unsigned)((n_kt + 7) / 8), (unsigned)n_qt, (unsigned)(a.n_b * a.n_h));
+  mask_tiles_kernel<<<grid, 256, 0, stream>>>(a.mask, a.n_h, a.n_rows, a.L, n_qt, n_words,
+                                              reinterpret_cast<unsigned char*>(a.tile_live), a.head_live);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "launch mask_tiles");
+    return JVPFA_ERR_CUDA;
+  }
+  return JVPFA_OK;
+}
 
 int launch_mask_check(const jvpfa_mask_check_args& a, cudaStream_t stream) {
   const int n_heads = a.n_b * a.n_h;

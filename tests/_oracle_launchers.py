@@ -47,3 +47,8 @@ def mask_check(spec, shape):
     if spec.kind == _lib.MASK_BOOL:
         return bool(t.bool().any(dim=(-1, -2)).all()), False, False
     return bool((t != -100.0).any(dim=(-1, -2)).all()), bool(torch.isinf(t).any()), bool(torch.isnan(t).any())
+
+
+def mask_tiles(spec, L):
+    """Stand-in for jvpfa_mask_tiles: no tile bitmap on the host, so the caller takes its element-wise route."""
+    raise _lib.Unsupported("no tile bitmap without the device pass")

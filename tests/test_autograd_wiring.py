@@ -17,6 +17,7 @@ def cpu_kernels(monkeypatch):
     monkeypatch.setattr(ja, "_launch_bwd", stand_in.launch_bwd)
     monkeypatch.setattr(ja, "_require_cuda", lambda *a: None)
     monkeypatch.setattr(_lib, "mask_check", stand_in.mask_check)
+    monkeypatch.setattr(_lib, "mask_tiles", stand_in.mask_tiles)
     monkeypatch.setitem(_lib.DTYPE_ENUM, torch.float64, _lib.FP32)  # stand-ins compute in float64
 
 
@@ -117,7 +118,7 @@ def test_cpu_tensors_are_refused_without_the_stand_in():
         ja.attention(q.float(), k.float(), v.float())
 
 
-def test_mask_classification():
+def test_mask_classification(cpu_kernels):
     # (verification of mask contents is a device pass, jvpfa_mask_check: covered by the GPU tests)
     Z, H, N = 2, 3, 32
     spec, mt, _ = ja.classify_mask(None, True, Z, H, N, torch.float32, False)

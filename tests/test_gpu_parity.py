@@ -711,3 +711,89 @@ def test_mask_verification_is_one_device_pass():
         sl[0, 0] = ja.MASK_CONST
         with pytest.raises(AssertionError, match="masking constant"):
             ja.attention(q, k, v, attn_mask=sl)
+
+
+def _tile_bitmap_reference(mask, L):
+    """bit t of word t // 64 of entry [b][h][qt]: tile (128 queries x 64 keys) has a True."""
+    B, H, R, _ = mask.shape
+    n_kt, n_qt = (L + 63) // 64, 1 if R == 1 else (L + 127) // 128
+    n_words = (n_kt + 63) // 64
+    out = torch.zeros(B, H, n_qt, n_words, dtype=torch.int64)
+    for qt in range(n_qt):
+        rows = mask[:, :, qt * 128:(qt + 1) * 128] if R > 1 else mask
+        for t in range(n_kt):
+            live = rows[..., t * 64:(t + 1) * 64].any(dim=(-1, -2))
+            bit = 1 << (t % 64)
+            bit = bit - (1 << 64) if bit >= 1 << 63 else bit
+            out[:, :, qt, t // 64] |= torch.where(live, bit, 0)
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("dt,B,H,L,kind,dual", [
+    ("bf16", 2, 3, 512, "documents", True), ("fp16", 1, 2, 1024, "window", True), ("bf16", 2, 2, 384, "documents", False),
+    ("bf16", 3, 2, 448, "keys", True), ("fp16", 1, 2, 4224, "window", True),
+])
+def test_tcgen05_forward_steps_over_dead_mask_tiles(dt, B, H, L, kind, dual):
+    """Boolean masks with whole 128 x 64 tiles of False (documents packed into one sequence, a sliding window,
+    dropped key ranges): jvpfa_mask_tiles must report exactly the tiles with a True, and the forward given that
+    bitmap must equal the forward without it (which visits every tile) and the oracle.  One query tile of one head
+    is dead altogether: zeros and lse = +inf."""
+    dtype, dev = DT[dt], torch.device("cuda:0")
+    g = torch.Generator().manual_seed(L)
+    i, j = torch.arange(L)[:, None], torch.arange(L)[None, :]
+    if kind == "documents":
+        cuts = torch.sort(torch.randint(1, L, (B, 3), generator=g), dim=1).values
+        doc = (torch.arange(L)[None, :, None] >= cuts[:, None, :]).sum(-1)  # (B, L) document index
+        mask = (doc[:, :, None] == doc[:, None, :])[:, None].expand(B, H, L, L).clone()
+        mask &= torch.rand(B, H, L, L, generator=g) > 0.2
+        mask[..., 0, 0] = True
+    elif kind == "window":
+        mask = ((i - j).abs() < 100)[None, None].expand(B, H, L, L).clone()
+    else:  # keys dropped for all queries: one mask row per batch entry
+        mask = torch.rand(B, 1, 1, L, generator=g) > 0.3
+        mask[..., 64:192] = False
+        mask[..., 5] = True
+    if mask.shape[2] > 1:
+        mask[0, H - 1, 128:256] = False  # a query tile without any key
+    q, k, v, tq, tk, tv, *_ = _make(B, H, L, 64, dtype, seed=L + 1)
+    if not dual:
+        tq = tk = tv = None
+    md = mask.to(dev)
+    spec = _lib.MaskSpec(_lib.MASK_BOOL, md.view(torch.uint8), tuple(0 if md.shape[d] == 1 else md.stride(d) for d in range(4)))
+    tile_live, head_live = _lib.mask_tiles(spec, L)
+    assert torch.equal(tile_live.cpu(), _tile_bitmap_reference(mask, L))
+    assert torch.equal(head_live[:-1].cpu().bool(), mask.any(dim=(-1, -2)).reshape(-1))
+    n_kt = (L + 63) // 64
+    n_live = sum(bin(x & (2**64 - 1)).count("1") for x in tile_live.tolist())
+    assert head_live[-1].item() == n_live
+    assert 0 < n_live < n_kt * (tile_live.numel() // ((n_kt + 63) // 64))  # the case does have dead tiles
+
+    cu = lambda x: None if x is None else x.to(dev)  # noqa: E731
+    outs = []
+    for bitmap in (None, tile_live):
+        spec.tile_live = bitmap
+        o = torch.empty(B, H, L, 64, device=dev, dtype=dtype)
+        to = torch.empty_like(o) if dual else None
+        lse = torch.empty(B, H, L, device=dev)
+        mu = torch.empty_like(lse) if dual else None
+        _lib.fwd(cu(q), cu(k), cu(v), cu(tq), cu(tk), cu(tv), o, to, lse, mu, spec, 0.125, _lib.IMPL_TCGEN05)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        outs.append((o, to, lse, mu))
+    for a_, b_ in zip(outs[0], outs[1]):
+        if a_ is not None:
+            assert torch.equal(a_, b_)  # dead tiles contribute exact zeros either way
+    o, to, lse, mu = outs[1]
+    if mask.shape[2] > 1:
+        assert o[0, H - 1, 128:256].abs().max() == 0 and torch.isinf(lse[0, H - 1, 128:256]).all()
+    if dual:
+        ro, rto = orc.sdpa_jvp(q, k, v, tq, tk, tv, attn_mask=mask)
+        _close(to, rto, dtype, "tO")
+    else:
+        ro = orc.sdpa_primal(q, k, v, attn_mask=mask)
+    _close(o, ro, dtype, "O")
+    # and through the public API (classification builds the bitmap), with gradients through the generic backward
+    a = [cu(x).requires_grad_() for x in (q, k, v)]
+    out = ja.attention(*a, attn_mask=md)
+    assert torch.equal(out.detach(), o)
+    torch.autograd.grad(out.float().sum(), a)
