@@ -514,7 +514,15 @@ bool bwd_tc5_eligible(const jvpfa_bwd_args& a) {
   if (a.dtype != JVPFA_BF16 && a.dtype != JVPFA_FP16) return false;
   if (a.D != 64 && a.D != 128) return false;
   const int k = a.mask.kind;
-  return k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN;
+  if (k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN) return true;
+  // Boolean masks and bias: the D = 64 kernel reads 16-byte pieces of mask rows (bwd_tc5_d64.cu)
+  if (a.D != 64 || (a.L & 15) != 0) return false;
+  if (k == JVPFA_MASK_BIAS && a.mask.bias_dtype != a.dtype) return false;
+  const long long esz = k == JVPFA_MASK_BOOL ? 1 : 2;
+  if (a.mask.stride[3] != 1 || (reinterpret_cast<uintptr_t>(a.mask.ptr) & 15u) != 0) return false;
+  for (int d = 0; d < 3; ++d)
+    if (a.mask.stride[d] < 0 || ((a.mask.stride[d] * esz) & 15) != 0) return false;
+  return true;
 }
 
 int launch_bwd_tc5(const jvpfa_bwd_args& a, cudaStream_t s) {

@@ -124,7 +124,12 @@ struct BwdItem {
   int bh, b, h, own0, loop_begin, n_sub;
 };
 
-template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+// MK: 0 = none / causal / key padding (index comparisons); 1 = uint8 mask; 2 = additive bias of the
+// element type T.  For 1 and 2 an elementwise thread fetches its own row's share of the sub-tile from
+// global memory before it waits for the sub-tile's scores: with own queries 32 consecutive mask
+// elements (16-byte loads), with own keys one element of each of the 32 query rows (lanes read
+// neighbouring keys).  The key stride must be 1, rows 16-byte aligned and L a multiple of 16.
+template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
 __global__ void __launch_bounds__(480, 1)
 bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps maps, int* status) {
   using C = Bwd64Cfg<OWN_KEYS, HAS_GO, HAS_GT>;
@@ -628,6 +633,15 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       }
       const int n_valid = valid_keys(it.b);
       const size_t stat_off = (size_t)it.bh * L;
+      // MK != 0: start of this head's mask / bias and its row pitch, in bytes
+      constexpr int MESZ = MK == 1 ? 1 : 2;
+      const unsigned char* mbase = nullptr;
+      long long mpitch = 0;
+      if constexpr (MK != 0) {
+        mbase = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
+                ((long long)it.b * a.mask.stride[0] + (long long)it.h * a.mask.stride[1]) * MESZ;
+        mpitch = a.mask.stride[2] * MESZ;
+      }
 
       float r_nlse = -INFINITY, r_nmu = 0.f, r_neps = 0.f, r_nsub = 0.f;
       if constexpr (!OWN_KEYS) {
@@ -651,6 +665,28 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         const int st = g % STAGES, buf = g % NBUF;
         const uint32_t tbuf = tbase + buf * C::COL_BUF;
         const int l0 = it.loop_begin + s * BL;
+        // MK != 0: the thread's 32 mask / bias elements of this sub-tile, requested before the waits.
+        // Indices are clamped into the tensor; what lies outside is switched off by col_lo / col_hi below.
+        constexpr int NRAW = MK == 0 ? 1 : (OWN_KEYS ? 32 : 8 * MESZ);
+        uint32_t raw[NRAW];
+        if constexpr (MK != 0) {
+          if constexpr (OWN_KEYS) {
+            const unsigned char* p = mbase + (long long)min(own_idx, L - 1) * MESZ;
+#pragma unroll
+            for (int col = 0; col < 32; ++col) {
+              const unsigned char* e = p + (long long)min(l0 + col, L - 1) * mpitch;
+              raw[col] = MK == 1 ? ldg_nc_u8(e) : ldg_nc_u16(e);
+            }
+          } else {
+            const unsigned char* p = mbase + (long long)min(own_idx, L - 1) * mpitch + (size_t)l0 * MESZ;
+#pragma unroll
+            for (int j = 0; j < 2 * MESZ; ++j) {
+              uint4 r = make_uint4(0u, 0u, 0u, 0u);
+              if (l0 + (j + 1) * (16 / MESZ) <= L) r = ldg_nc_v4(p + 16 * j);
+              raw[4 * j] = r.x, raw[4 * j + 1] = r.y, raw[4 * j + 2] = r.z, raw[4 * j + 3] = r.w;
+            }
+          }
+        }
         if constexpr (OWN_KEYS) {
           if (!mbar_wait(stat_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull)) {
             alive = false;
@@ -675,6 +711,27 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           col_hi = min(BL, n_valid - l0);
           if (causal) col_hi = min(col_hi, own_idx - l0 + 1);  // j <= i
         }
+        // MK = 1: bit col of live = column col may attend (mask and index range together);
+        // MK = 2: mb[x] = the bias of columns 2x, 2x+1 as a packed pair
+        uint32_t live = 0xffffffffu;
+        uint32_t mb[MK == 2 ? 16 : 1];
+        if constexpr (MK == 1) {
+          live = 0u;
+          if constexpr (OWN_KEYS) {
+#pragma unroll
+            for (int col = 0; col < 32; ++col) live |= (raw[col] != 0u ? 1u : 0u) << col;
+          } else {
+#pragma unroll
+            for (int w = 0; w < 8; ++w)  // bytes -> 0/1 -> four bits
+              live |= (((__vcmpne4(raw[w], 0u) & 0x01010101u) * 0x01020408u) >> 24) << (4 * w);
+          }
+          const int lo = max(col_lo, 0), hi = min(col_hi, BL);
+          live &= hi > lo ? ((hi - lo >= 32 ? 0xffffffffu : ((1u << (hi - lo)) - 1u)) << lo) : 0u;
+        }
+        if constexpr (MK == 2) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) mb[x] = OWN_KEYS ? (raw[2 * x] | (raw[2 * x + 1] << 16)) : raw[x];
+        }
         const float4* stat = sStat + st * (BL / 2) * 2;
         // Two halves of 16 columns, as a real loop: the body exists once, which keeps the instruction
         // footprint of the eight elementwise warps small next to the single-thread MMA issuers.
@@ -690,6 +747,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           tmem_wait_ld();
           if (row == 0 && c == 0) TRACE(g, 13);
           const int lo_c = col_lo - 16 * c, hi_c = col_hi - 16 * c;  // live columns of this half: [lo_c, hi_c)
+          const uint32_t live_c = live >> (16 * c);
           uint32_t pk_gs[8], pk_gt[8], pk_av[8], pk_p[8];
 #pragma unroll
           for (int x = 0; x < 8; ++x) {
@@ -703,10 +761,17 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
               nl = make_float2(r_nlse, r_nlse), nmu = make_float2(r_nmu, r_nmu);
               neps = make_float2(r_neps, r_neps), nsub = make_float2(r_nsub, r_nsub);
             }
-            const float2 xs = __ffma2_rn(f2(sv[2 * x], sv[2 * x + 1]), c2, nl);
+            float2 xs = __ffma2_rn(f2(sv[2 * x], sv[2 * x + 1]), c2, nl);
+            if constexpr (MK == 2)  // scores are in log2 units: + bias * log2(e)
+              xs = __ffma2_rn(unpack2<T>(c ? mb[8 + x] : mb[x]), make_float2(kLog2e, kLog2e), xs);
             float2 p;
-            p.x = (col >= lo_c && col < hi_c) ? fast_exp2(xs.x) : 0.f;
-            p.y = (col + 1 >= lo_c && col + 1 < hi_c) ? fast_exp2(xs.y) : 0.f;
+            if constexpr (MK == 1) {
+              p.x = (live_c & (1u << col)) ? fast_exp2(xs.x) : 0.f;
+              p.y = (live_c & (2u << col)) ? fast_exp2(xs.y) : 0.f;
+            } else {
+              p.x = (col >= lo_c && col < hi_c) ? fast_exp2(xs.x) : 0.f;
+              p.y = (col + 1 >= lo_c && col + 1 < hi_c) ? fast_exp2(xs.y) : 0.f;
+            }
             if constexpr (HAS_GT) {
               const float2 tm = __ffma2_rn(f2(ts[2 * x], ts[2 * x + 1]), sc2, nmu);
               const float2 eb = __fadd2_rn(f2(ev[2 * x], ev[2 * x + 1]), neps);
@@ -777,7 +842,7 @@ static int sm_count_of_current_device() {
   return cache[dev];
 }
 
-template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* status) {
   using C = Bwd64Cfg<OWN_KEYS, HAS_GO, HAS_GT>;
   Bwd64Maps m;
@@ -804,7 +869,7 @@ static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* stat
     set_last_cuda_error(cudaErrorUnknown, "multiprocessor count");
     return JVPFA_ERR_CUDA;
   }
-  auto kern = bwd_tc5_d64_kernel<T, OWN_KEYS, HAS_GO, HAS_GT>;
+  auto kern = bwd_tc5_d64_kernel<T, OWN_KEYS, HAS_GO, HAS_GT, MK>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(bwd_tc5_d64)");
@@ -821,7 +886,7 @@ static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* stat
   return JVPFA_OK;
 }
 
-template <typename T, bool HAS_GO, bool HAS_GT>
+template <typename T, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_both64(const jvpfa_bwd_args& a, cudaStream_t s) {
   int* status = tc5_status_device_ptr();
   if (!status) {
@@ -829,18 +894,25 @@ static int launch_both64(const jvpfa_bwd_args& a, cudaStream_t s) {
     return JVPFA_ERR_CUDA;
   }
   int rc = JVPFA_OK;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half64<T, true, HAS_GO, HAS_GT>(a, s, status);
+  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half64<T, true, HAS_GO, HAS_GT, MK>(a, s, status);
   if (rc) return rc;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half64<T, false, HAS_GO, HAS_GT>(a, s, status);
+  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half64<T, false, HAS_GO, HAS_GT, MK>(a, s, status);
   return rc;
+}
+
+template <typename T, int MK>
+static int launch_mk64(const jvpfa_bwd_args& a, cudaStream_t s) {
+  const bool go = a.go != nullptr, gt = a.gto != nullptr;
+  if (go && gt) return launch_both64<T, true, true, MK>(a, s);
+  if (gt) return launch_both64<T, false, true, MK>(a, s);
+  return launch_both64<T, true, false, MK>(a, s);
 }
 
 template <typename T>
 static int launch_t64(const jvpfa_bwd_args& a, cudaStream_t s) {
-  const bool go = a.go != nullptr, gt = a.gto != nullptr;
-  if (go && gt) return launch_both64<T, true, true>(a, s);
-  if (gt) return launch_both64<T, false, true>(a, s);
-  return launch_both64<T, true, false>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BOOL) return launch_mk64<T, 1>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BIAS) return launch_mk64<T, 2>(a, s);
+  return launch_mk64<T, 0>(a, s);
 }
 
 }  // namespace tc5

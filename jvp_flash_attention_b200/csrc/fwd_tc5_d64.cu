@@ -80,23 +80,6 @@ struct LiveTiles {
   }
 };
 
-template <typename T>
-__device__ __forceinline__ float2 unpack2(uint32_t w);
-template <>
-__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
-  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-template <>
-__device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
-  return __half22float2(*reinterpret_cast<const __half2*>(&w));
-}
-
-__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
-  uint4 r;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-  return r;
-}
-
 template <typename T, bool DUAL, int MK>
 __global__ void __launch_bounds__(224, 2)
 fwd_tc5_d64_kernel(const jvpfa_fwd_args a, const __grid_constant__ Fwd64Maps maps, int* status) {

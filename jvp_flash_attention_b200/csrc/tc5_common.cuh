@@ -56,6 +56,35 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Host: (D, L, B*H) view of a contiguous (B, H, L, D) 16-bit tensor, box = 64 columns x box_rows
 // rows, 128-byte swizzle, out-of-range rows read as zero.  Defined in fwd_tc5.cu.
 bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH, int box_rows);
+// Read-only global loads and 16-bit unpacking used for user masks and bias.
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t w);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t ldg_nc_u8(const void* p) {
+  uint32_t r;
+  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(r) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
+  uint16_t r;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
+  return r;
+}
+
 // Host: (64, L, H, B) view of a 16-bit tensor whose batch / head / row strides (in elements) are given
 // (all zero: (B,H,L,64) row-major); same box, swizzle and fill.  Defined in fwd_tc5.cu.
 bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* stride_bhl,

@@ -193,7 +193,7 @@ def test_tcgen05_forward_many_items_per_cta(dt, B, H, L, kind):
     assert orc.max_abs_err(o, o2) <= HALF_ABS and orc.max_abs_err(to, to2) <= HALF_ABS
     assert orc.max_abs_err(lse, lse2) < 1e-4 and orc.max_abs_err(mu, mu2) < 1e-3
     sl = lambda x: x[B - 1:, H - 1:]  # noqa: E731
-    msl = None if mask is None else mask[B - 1:]
+    msl = None if mask is None else mask[min(B, mask.shape[0]) - 1:, min(H, mask.shape[1]) - 1:]
     ro, rto = orc.sdpa_jvp(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), attn_mask=msl, causal=causal)
     _close(sl(o), ro, dtype, "O")
     _close(sl(to), rto, dtype, "tO")
@@ -205,6 +205,10 @@ PERSISTENT_CASES = [
     # sub-tile counts, items without any live key, all three cotangent modes
     ("gt", "kvlen", "bf16", 40, 12, 96), ("both", "kvlen", "fp16", 40, 12, 128), ("go", "causal", "bf16", 40, 12, 160),
     ("gt", "none", "bf16", 64, 12, 32), ("both", "none", "bf16", 8, 12, 1024), ("gt", "causal", "fp16", 24, 8, 224),
+    # boolean masks and bias, fetched by the elementwise threads
+    ("both", "bool", "bf16", 2, 3, 256), ("gt", "bias", "fp16", 2, 2, 192), ("go", "bool_bcast", "bf16", 2, 2, 160),
+    ("gt", "bool_keys", "bf16", 3, 2, 224), ("both", "bias", "bf16", 40, 12, 96), ("gt", "bool", "fp16", 20, 12, 128),
+    ("go", "bias", "bf16", 1, 2, 48),
 ]
 
 
@@ -226,7 +230,7 @@ def test_tcgen05_backward_many_items_per_cta(cot, kind, dt, B, H, L):
         _close(a, b.float(), dtype, name)
     # one (batch, head) slice against the float64 oracle
     sl = lambda x: None if x is None else x[B - 1:, H - 1:]  # noqa: E731
-    msl = None if mask is None else mask[B - 1:]
+    msl = None if mask is None else mask[min(B, mask.shape[0]) - 1:, min(H, mask.shape[1]) - 1:]
     _, _, rdq, rdk, rdv = orc.grads_through_both(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), sl(go), sl(gto),
                                                  attn_mask=msl, causal=causal)
     _close(dq[B - 1:, H - 1:], rdq, dtype, "dq")
