@@ -43,7 +43,14 @@ typedef enum {
   JVPFA_ERR_TOO_LARGE = -10   /* problem exceeds a fixed internal capacity          */
 } jvpfa_status;
 
-typedef enum { JVPFA_BF16 = 0, JVPFA_FP16 = 1, JVPFA_FP32 = 2 } jvpfa_dtype;
+typedef enum {
+  JVPFA_BF16 = 0,
+  JVPFA_FP16 = 1,
+  JVPFA_FP32 = 2,      /* fp32 tensors; every product as three TF32 MMAs on a hi/lo split (error ~1e-6 relative) */
+  JVPFA_FP32_TF32 = 3  /* fp32 tensors; every product as one TF32 MMA, the precision of upstream's fp32 path
+                          (tl.dot on TF32 tensor cores, jvp_attention.py:233-236); error ~5e-4 relative, about
+                          2.5x faster.  Not a bias dtype: an fp32 bias is JVPFA_FP32. */
+} jvpfa_dtype;
 
 /* How scores are masked / biased inside the tile loop. */
 typedef enum {

@@ -20,6 +20,18 @@ IMPL_AUTO, IMPL_GENERIC, IMPL_TCGEN05 = 0, 1, 2
 IMPL_ONLY_DKDV, IMPL_ONLY_DQ = 0x100, 0x200  # measurement aids for jvpfa_bwd
 
 DTYPE_ENUM = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32}
+FP32_TF32 = 3  # JVPFA_FP32_TF32: fp32 tensors, products as one TF32 MMA
+
+# How fp32 inputs are multiplied: "3xtf32" (default; error ~1e-6 relative) or "tf32" (one TF32 MMA per product, the
+# precision of upstream's fp32 path; error ~5e-4, about 2.5x faster).  Set through jvp_attention.set_fp32_precision.
+FP32_PRECISION = "3xtf32"
+
+
+def compute_enum(t: torch.Tensor) -> int:
+    """jvpfa_dtype for the arithmetic on tensors like ``t``."""
+    if t.dtype == torch.float32 and FP32_PRECISION == "tf32":
+        return FP32_TF32
+    return DTYPE_ENUM[t.dtype]
 
 EXPORTS = (
     "jvpfa_fwd",
@@ -306,7 +318,7 @@ def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, im
     B, H, L, D = q.shape
     a = FwdArgs()
     a.struct_size = C.sizeof(FwdArgs)
-    a.dtype = DTYPE_ENUM[q.dtype]
+    a.dtype = compute_enum(q)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.impl = impl
     a.sm_scale = sm_scale
@@ -378,7 +390,7 @@ def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
     B, H, L, D = o.shape
     a = PreArgs()
     a.struct_size = C.sizeof(PreArgs)
-    a.dtype = DTYPE_ENUM[o.dtype]
+    a.dtype = compute_enum(o)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.o, a.to, a.go, a.gto = ptr(o), ptr(to), ptr(go), ptr(gto)
     a.mu, a.delta, a.eps, a.cterm = ptr(mu), ptr(delta), ptr(eps), ptr(cterm)
@@ -393,7 +405,7 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
     B, H, L, D = q.shape
     a = BwdArgs()
     a.struct_size = C.sizeof(BwdArgs)
-    a.dtype = DTYPE_ENUM[q.dtype]
+    a.dtype = compute_enum(q)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.impl = impl
     a.sm_scale = sm_scale
@@ -425,7 +437,7 @@ def bwd_noalloc(q, k, v, tq, tk, tv, o, to, go, gto, lse, mu, dq, dk, dv, mask: 
     B, H, L, D = q.shape
     a = BwdNoAllocArgs()
     a.struct_size = C.sizeof(BwdNoAllocArgs)
-    a.dtype = DTYPE_ENUM[q.dtype]
+    a.dtype = compute_enum(q)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.impl = impl
     a.sm_scale = sm_scale

@@ -39,7 +39,7 @@ static int check_arch() {
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int check_shape(int dtype, int B, int H, int L, int D) {
-  if (dtype != JVPFA_BF16 && dtype != JVPFA_FP16 && dtype != JVPFA_FP32) return JVPFA_ERR_DTYPE;
+  if (dtype != JVPFA_BF16 && dtype != JVPFA_FP16 && dtype != JVPFA_FP32 && dtype != JVPFA_FP32_TF32) return JVPFA_ERR_DTYPE;
   if (B < 1 || H < 1 || L < 1) return JVPFA_ERR_SHAPE;
   if (D != 32 && D != 64 && D != 128) return JVPFA_ERR_SHAPE;
   if ((long long)B * H > 65535LL) return JVPFA_ERR_TOO_LARGE;  // grid.y limit

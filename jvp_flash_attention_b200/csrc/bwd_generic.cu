@@ -113,6 +113,7 @@ int launch_pre(const jvpfa_pre_args& a, cudaStream_t s) {
     case JVPFA_FP16:
       return launch_pre_t<__half>(a, s);
     case JVPFA_FP32:
+    case JVPFA_FP32_TF32:  // no products in this kernel
       return launch_pre_t<float>(a, s);
     default:
       return JVPFA_ERR_DTYPE;
@@ -657,6 +658,8 @@ int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t s) {
       return launch_bwd_t<__half>(a, s);
     case JVPFA_FP32:
       return launch_bwd_t<float>(a, s);
+    case JVPFA_FP32_TF32:
+      return launch_bwd_t<tf32x1>(a, s);
     default:
       return JVPFA_ERR_DTYPE;
   }

@@ -51,10 +51,26 @@ struct Elem<__half> {
 template <>
 struct Elem<float> {
   static constexpr bool k16 = false;
+  static constexpr bool kSplit = true;  // every product is three TF32 MMAs on a hi/lo split
   static constexpr int kPad = 4;
   static constexpr int kKStep = 8;
   __device__ static __forceinline__ float to_float(float x) { return x; }
   __device__ static __forceinline__ float from_float(float x) { return x; }
+};
+
+// fp32 in memory, products as one TF32 MMA (JVPFA_FP32_TF32): the precision of upstream's fp32 path, whose
+// tl.dot calls run on TF32 tensor cores (jvp_attention.py:233-236, 314-322).  Relative error about 5e-4.
+struct tf32x1 {
+  float v;
+};
+template <>
+struct Elem<tf32x1> {
+  static constexpr bool k16 = false;
+  static constexpr bool kSplit = false;
+  static constexpr int kPad = 4;
+  static constexpr int kKStep = 8;
+  __device__ static __forceinline__ float to_float(tf32x1 x) { return x.v; }
+  __device__ static __forceinline__ tf32x1 from_float(float x) { return tf32x1{x}; }
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -91,6 +107,16 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
   float r = x - __uint_as_float(hi);
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
 }
+// The same for element type T: types that multiply in one pass have no lo part.
+template <typename T>
+__device__ __forceinline__ void split_t(float x, uint32_t& hi, uint32_t& lo) {
+  if constexpr (Elem<T>::kSplit) {
+    split_tf32(x, hi, lo);
+  } else {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    lo = 0u;
+  }
+}
 
 // ----------------------------------------------------------------------------------------------
 // Fragments.  For 16-bit types a fragment is the packed register set of m16n8k16; for fp32 it
@@ -124,8 +150,10 @@ __device__ __forceinline__ void mma(float c[4], const FragA<T, true>& a, const F
 }
 template <typename T>
 __device__ __forceinline__ void mma(float c[4], const FragA<T, false>& a, const FragB<T, false>& b) {
-  mma_1688_tf32(c, a.lo, b.hi);
-  mma_1688_tf32(c, a.hi, b.lo);
+  if constexpr (Elem<T>::kSplit) {
+    mma_1688_tf32(c, a.lo, b.hi);
+    mma_1688_tf32(c, a.hi, b.lo);
+  }
   mma_1688_tf32(c, a.hi, b.hi);
 }
 
@@ -144,12 +172,12 @@ __device__ __forceinline__ void load_a(FragA<T, true>& f, const T* s, int ld, in
 template <typename T>
 __device__ __forceinline__ void load_a(FragA<T, false>& f, const T* s, int ld, int r0, int k0, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  const float* p0 = s + (r0 + g) * ld + k0 + t;
+  const float* p0 = reinterpret_cast<const float*>(s) + (r0 + g) * ld + k0 + t;
   const float* p1 = p0 + 8 * ld;
-  split_tf32(p0[0], f.hi[0], f.lo[0]);
-  split_tf32(p1[0], f.hi[1], f.lo[1]);
-  split_tf32(p0[4], f.hi[2], f.lo[2]);
-  split_tf32(p1[4], f.hi[3], f.lo[3]);
+  split_t<T>(p0[0], f.hi[0], f.lo[0]);
+  split_t<T>(p1[0], f.hi[1], f.lo[1]);
+  split_t<T>(p0[4], f.hi[2], f.lo[2]);
+  split_t<T>(p1[4], f.hi[3], f.lo[3]);
 }
 
 // B fragment, "NT": the smem tile is s[n][k] with k contiguous (C = A * s^T).
@@ -163,9 +191,9 @@ __device__ __forceinline__ void load_b_nt(FragB<T, true>& f, const T* s, int ld,
 template <typename T>
 __device__ __forceinline__ void load_b_nt(FragB<T, false>& f, const T* s, int ld, int n0, int k0, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  const float* p = s + (n0 + g) * ld + k0 + t;
-  split_tf32(p[0], f.hi[0], f.lo[0]);
-  split_tf32(p[4], f.hi[1], f.lo[1]);
+  const float* p = reinterpret_cast<const float*>(s) + (n0 + g) * ld + k0 + t;
+  split_t<T>(p[0], f.hi[0], f.lo[0]);
+  split_t<T>(p[4], f.hi[1], f.lo[1]);
 }
 
 // B fragment, "NN": the smem tile is s[k][n] with n contiguous (C = A * s).
@@ -184,9 +212,9 @@ __device__ __forceinline__ void load_b_nn(FragB<T, true>& f, const T* s, int ld,
 template <typename T>
 __device__ __forceinline__ void load_b_nn(FragB<T, false>& f, const T* s, int ld, int k0, int n0, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  const float* p = s + (k0 + 2 * t) * ld + n0 + g;
-  split_tf32(p[0], f.hi[0], f.lo[0]);
-  split_tf32(p[ld], f.hi[1], f.lo[1]);
+  const float* p = reinterpret_cast<const float*>(s) + (k0 + 2 * t) * ld + n0 + g;
+  split_t<T>(p[0], f.hi[0], f.lo[0]);
+  split_t<T>(p[ld], f.hi[1], f.lo[1]);
 }
 
 // A fragment taken from an accumulator-layout tile acc[n_tile][4] (16 rows x 8*n_tiles cols),
@@ -203,10 +231,10 @@ __device__ __forceinline__ void a_from_acc(FragA<T, true>& f, const float (*acc)
 template <typename T>
 __device__ __forceinline__ void a_from_acc(FragA<T, false>& f, const float (*acc)[4], int kk) {
   const float* c = acc[kk];
-  split_tf32(c[0], f.hi[0], f.lo[0]);  // slot t    <- column 2t,   row g
-  split_tf32(c[2], f.hi[1], f.lo[1]);  // slot t    <- column 2t,   row g+8
-  split_tf32(c[1], f.hi[2], f.lo[2]);  // slot t+4  <- column 2t+1, row g
-  split_tf32(c[3], f.hi[3], f.lo[3]);  // slot t+4  <- column 2t+1, row g+8
+  split_t<T>(c[0], f.hi[0], f.lo[0]);  // slot t    <- column 2t,   row g
+  split_t<T>(c[2], f.hi[1], f.lo[1]);  // slot t    <- column 2t,   row g+8
+  split_t<T>(c[1], f.hi[2], f.lo[2]);  // slot t+4  <- column 2t+1, row g
+  split_t<T>(c[3], f.hi[3], f.lo[3]);  // slot t+4  <- column 2t+1, row g+8
 }
 
 // ----------------------------------------------------------------------------------------------

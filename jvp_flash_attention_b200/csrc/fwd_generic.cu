@@ -373,6 +373,8 @@ int launch_fwd_generic(const jvpfa_fwd_args& a, cudaStream_t s) {
       return launch_t<__half>(a, s);
     case JVPFA_FP32:
       return launch_t<float>(a, s);
+    case JVPFA_FP32_TF32:
+      return launch_t<tf32x1>(a, s);
     default:
       return JVPFA_ERR_DTYPE;
   }

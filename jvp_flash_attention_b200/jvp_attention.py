@@ -60,6 +60,19 @@ def _require_cuda(*ts: Tensor) -> None:
             )
 
 
+def set_fp32_precision(mode: str) -> str:
+    """How fp32 inputs are multiplied from now on; returns the previous mode.
+
+    ``"3xtf32"`` (default): every product as three TF32 MMAs on a hi/lo split, about 1e-6 relative error.
+    ``"tf32"``: one TF32 MMA per product, about 5e-4 -- what upstream's fp32 path computes (its ``tl.dot`` calls
+    run on TF32 tensor cores, jvp_attention.py:233-236; its fp32 tolerance is 2.35e-2), about 2.5x faster.
+    Forward and backward of one call must run under the same mode."""
+    if mode not in ("3xtf32", "tf32"):
+        raise ValueError("fp32 precision is '3xtf32' or 'tf32'")
+    prev, _lib.FP32_PRECISION = _lib.FP32_PRECISION, mode
+    return prev
+
+
 def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int, qdtype: torch.dtype,
                   verify: bool) -> tuple[_lib.MaskSpec, int, Tensor | None]:
     """Turns the user's mask into the kernel's description.

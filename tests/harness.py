@@ -7,7 +7,7 @@ dv) and times the fused forward against SDPA-MATH (test_jvp_attention.py:670-975
 shapes 225-227, 291; seeds 290-304, 331-340; tolerances 688-693; flop convention 49-83).  This
 script does the same for this library so that the two sets of tables can be put side by side:
 
-    python tests/harness.py --dtype bfloat16 [--json out.json] [--max-len 2048]
+    python tests/harness.py --dtype bfloat16 [--json out.json] [--max-len 2048] [--fp32-precision tf32]
 
 Same grid (L in 32..2048, mask in none/boolean/additive, causal on/off, causal+mask skipped: 28
 cases), same shapes (B=2, 12 heads, D=64), same seeds and mask density (90 % masked, additive mask
@@ -33,7 +33,7 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-from jvp_flash_attention_b200.jvp_attention import JVPAttn  # noqa: E402
+from jvp_flash_attention_b200.jvp_attention import JVPAttn, set_fp32_precision  # noqa: E402
 
 MASK_CONST = -100.0
 TOL = {torch.float16: 4e-3, torch.float32: 2.35e-2, torch.bfloat16: 3.2e-2}
@@ -154,14 +154,17 @@ def main():
     ap.add_argument("--max-len", type=int, default=2048)
     ap.add_argument("--no-benchmark-performance", action="store_true")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--fp32-precision", default="3xtf32", choices=["3xtf32", "tf32"],
+                    help="float32 only: products as three TF32 MMAs (default) or as one, which is what the reference computes")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("the harness needs a CUDA device: this library has no CPU path")
+    set_fp32_precision(args.fp32_precision)
     rows = run(getattr(torch, args.dtype), args.max_len, bench=not args.no_benchmark_performance)
     n_ok = sum(r["pass"] for r in rows)
     print(f"{n_ok} of {len(rows)} cases within the reference's tolerance for {args.dtype}")
     if args.json:
-        Path(args.json).write_text(json.dumps({"dtype": args.dtype, "rows": rows}, indent=1))
+        Path(args.json).write_text(json.dumps({"dtype": args.dtype, "fp32_precision": args.fp32_precision, "rows": rows}, indent=1))
 
 
 if __name__ == "__main__":

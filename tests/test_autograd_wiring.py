@@ -162,3 +162,17 @@ def test_flop_model_headline():
     w = workloads.Workload("x", torch.bfloat16, 4, 16, 2048, 64, causal=True)
     f = workloads.flops(w, ("fwd_dual", "bwd_to"))
     assert abs(f / 1e9 - 275.0) < 0.6  # 16 MMAs x 17.19 GFLOP
+
+
+def test_fp32_precision_switch():
+    assert _lib.FP32_PRECISION == "3xtf32"
+    x32, x16 = torch.zeros(1), torch.zeros(1, dtype=torch.bfloat16)
+    assert _lib.compute_enum(x32) == _lib.FP32
+    prev = ja.set_fp32_precision("tf32")
+    try:
+        assert prev == "3xtf32" and _lib.compute_enum(x32) == _lib.FP32_TF32 and _lib.compute_enum(x16) == _lib.BF16
+        with pytest.raises(ValueError):
+            ja.set_fp32_precision("fp16")
+    finally:
+        ja.set_fp32_precision(prev)
+    assert _lib.compute_enum(x32) == _lib.FP32

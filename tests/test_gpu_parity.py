@@ -801,3 +801,28 @@ def test_tcgen05_forward_steps_over_dead_mask_tiles(dt, B, H, L, kind, dual):
     out = ja.attention(*a, attn_mask=md)
     assert torch.equal(out.detach(), o)
     torch.autograd.grad(out.float().sum(), a)
+
+
+@pytest.mark.parametrize("D,L,kind", [(64, 160, "causal"), (128, 96, "bias"), (32, 128, "bool"), (64, 256, "none")])
+def test_fp32_single_pass_tf32_mode(D, L, kind):
+    """`set_fp32_precision("tf32")`: fp32 tensors multiplied with one TF32 MMA per product, the precision of upstream's
+    fp32 path (jvp_attention.py:233-236; its tolerance is 2.35e-2 absolute, tests/test_jvp_attention.py:688-693).
+    Stated error of this mode: 5e-3 of max|ref| on every output here; the default three-pass mode on the same inputs
+    stays at 1e-5."""
+    B, H = 2, 2
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, D, torch.float32, seed=D + L)
+    mask, causal = _mask(kind, B, H, L, torch.float32, seed=L)
+    refs = orc.grads_through_both(q, k, v, tq, tk, tv, go, gto, attn_mask=mask, causal=causal)
+    exact = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal)
+    prev = ja.set_fp32_precision("tf32")
+    try:
+        fast = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal)
+    finally:
+        assert ja.set_fp32_precision(prev) == "tf32"
+    worst_fast = 0.0
+    for name, r, x3, x1 in zip(("O", "tO", "dq", "dk", "dv"), refs, (exact[0], exact[1], *exact[4:]), (fast[0], fast[1], *fast[4:])):
+        assert orc.rel_err(x3, r) < 1e-5, name
+        e = orc.rel_err(x1, r)
+        assert e < 5e-3, (name, e)
+        worst_fast = max(worst_fast, e)
+    assert worst_fast > 2e-5  # the mode really multiplies in one pass
