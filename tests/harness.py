@@ -100,11 +100,11 @@ def timed(fn, iters=100, warmup=10):
     return (time.perf_counter() - t0) / iters * 1e3
 
 
-def run(dtype, max_len, bench=True):
+def run(dtype, max_len, bench=True, min_len=0, masks=("none", "boolean", "additive")):
     dev = torch.device("cuda", 0)
     rows = []
-    for L in [s for s in SEQ_LENS if s <= max_len]:
-        for mask_type in ("none", "boolean", "additive"):
+    for L in [s for s in SEQ_LENS if min_len <= s <= max_len]:
+        for mask_type in masks:
             for causal in (False, True):
                 if causal and mask_type != "none":
                     continue
@@ -152,6 +152,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dtype", default="bfloat16", choices=["float16", "bfloat16", "float32"])
     ap.add_argument("--max-len", type=int, default=2048)
+    ap.add_argument("--min-len", type=int, default=0)
+    ap.add_argument("--masks", default="none,boolean,additive", help="comma-separated subset of the grid's mask types")
     ap.add_argument("--no-benchmark-performance", action="store_true")
     ap.add_argument("--json", default=None)
     ap.add_argument("--fp32-precision", default="3xtf32", choices=["3xtf32", "tf32"],
@@ -160,7 +162,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("the harness needs a CUDA device: this library has no CPU path")
     set_fp32_precision(args.fp32_precision)
-    rows = run(getattr(torch, args.dtype), args.max_len, bench=not args.no_benchmark_performance)
+    rows = run(getattr(torch, args.dtype), args.max_len, bench=not args.no_benchmark_performance, min_len=args.min_len,
+               masks=tuple(args.masks.split(",")))
     n_ok = sum(r["pass"] for r in rows)
     print(f"{n_ok} of {len(rows)} cases within the reference's tolerance for {args.dtype}")
     if args.json:
