@@ -135,6 +135,10 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   using C = Bwd64Cfg<OWN_KEYS, HAS_GO, HAS_GT>;
   constexpr int D = 64, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES, NBUF = C::NBUF;
 
+  // The own-queries launch that follows an own-keys launch reads nothing this kernel writes, so it is
+  // launched with programmatic stream serialization and may take over each SM as soon as this
+  // kernel's CTA there has exited (both need a whole SM): the tails of the two launches overlap.
+  if constexpr (OWN_KEYS) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (*(volatile int*)status != 0) return;
 
   extern __shared__ unsigned char smem_raw[];
@@ -843,7 +847,7 @@ static int sm_count_of_current_device() {
 }
 
 template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
-static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* status) {
+static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* status, bool overlap_previous) {
   using C = Bwd64Cfg<OWN_KEYS, HAS_GO, HAS_GT>;
   Bwd64Maps m;
   const long long BH = (long long)a.B * a.H;
@@ -877,8 +881,15 @@ static int launch_half64(const jvpfa_bwd_args& a, cudaStream_t stream, int* stat
   }
   const long long n_items = (long long)((a.L + C::OWN - 1) / C::OWN) * BH;
   const int grid = (int)(n_items < sms ? n_items : sms);
-  kern<<<grid, C::NTHREADS, C::SMEM_BYTES, stream>>>(a, m, status);
-  e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid), cfg.blockDim = dim3(C::NTHREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = overlap_previous ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, a, m, status);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "launch bwd_tc5_d64");
     return JVPFA_ERR_CUDA;
@@ -894,9 +905,10 @@ static int launch_both64(const jvpfa_bwd_args& a, cudaStream_t s) {
     return JVPFA_ERR_CUDA;
   }
   int rc = JVPFA_OK;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half64<T, true, HAS_GO, HAS_GT, MK>(a, s, status);
+  const bool both = !(a.impl & (JVPFA_IMPL_ONLY_DQ | JVPFA_IMPL_ONLY_DKDV));
+  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half64<T, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
   if (rc) return rc;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half64<T, false, HAS_GO, HAS_GT, MK>(a, s, status);
+  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half64<T, false, HAS_GO, HAS_GT, MK>(a, s, status, both);
   return rc;
 }
 
