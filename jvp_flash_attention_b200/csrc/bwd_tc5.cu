@@ -64,6 +64,9 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
   constexpr int KSTEPS_L = BL / 16;
   constexpr int HALVES = D / 64;
 
+  // The own-queries launch that follows reads nothing this kernel writes: it is launched with programmatic
+  // stream serialization and fills the SMs as this kernel's last CTAs leave them.
+  if constexpr (OWN_KEYS) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (*(volatile int*)status != 0) return;
 
   extern __shared__ unsigned char smem_raw[];
@@ -444,7 +447,7 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
 // Host side
 // ---------------------------------------------------------------------------------------------
 template <typename T, int D, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
-static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status) {
+static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status, bool overlap_previous) {
   using C = BwdCfg<D, OWN_KEYS, HAS_GO, HAS_GT>;
   BwdMaps m;
   const long long BH = (long long)a.B * a.H;
@@ -470,8 +473,15 @@ static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status
     return JVPFA_ERR_CUDA;
   }
   dim3 grid((a.L + C::OWN - 1) / C::OWN, a.B * a.H);
-  kern<<<grid, C::NTHREADS, C::SMEM_BYTES, stream>>>(a, m, status);
-  e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = dim3(C::NTHREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = overlap_previous ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, a, m, status);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "launch bwd_tc5");
     return JVPFA_ERR_CUDA;
@@ -487,9 +497,10 @@ static int launch_both(const jvpfa_bwd_args& a, cudaStream_t s) {
     return JVPFA_ERR_CUDA;
   }
   int rc = JVPFA_OK;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half<T, D, true, HAS_GO, HAS_GT>(a, s, status);
+  const bool both = !(a.impl & (JVPFA_IMPL_ONLY_DQ | JVPFA_IMPL_ONLY_DKDV));
+  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half<T, D, true, HAS_GO, HAS_GT>(a, s, status, false);
   if (rc) return rc;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half<T, D, false, HAS_GO, HAS_GT>(a, s, status);
+  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half<T, D, false, HAS_GO, HAS_GT>(a, s, status, both);
   return rc;
 }
 
