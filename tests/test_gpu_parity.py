@@ -826,3 +826,34 @@ def test_fp32_single_pass_tf32_mode(D, L, kind):
         assert e < 5e-3, (name, e)
         worst_fast = max(worst_fast, e)
     assert worst_fast > 2e-5  # the mode really multiplies in one pass
+
+
+@pytest.mark.parametrize("mask_type", ["boolean", "additive"])
+def test_reference_grid_largest_masked_case_on_tcgen05(mask_type):
+    """The largest masked cases of the reference's grid (B=2, 12 heads, L=2048, D=64, 90 % masked; boolean and {0, -100}
+    additive): forward and backward through both outputs on the tcgen05 kernels against the register-tiled family on
+    all heads, and against the float64 oracle on one head."""
+    from tests import harness as hz
+
+    dev = torch.device("cuda:0")
+    B, H, L, D = 2, 12, 2048, 64
+    q, k, v, tq, tk, tv, target, mask = hz.make_case(L, mask_type, torch.bfloat16, dev)
+    tq, tk, tv = tq * 0.1, tk * 0.1, tv * 0.1
+    g = torch.Generator(device=dev).manual_seed(7)
+    go, gto = (torch.randn(B, H, L, D, device=dev, dtype=torch.bfloat16, generator=g) for _ in range(2))
+    c = lambda x: x.cpu()  # noqa: E731
+    fast = _run_kernels(c(q), c(k), c(v), c(tq), c(tk), c(tv), c(go), c(gto), c(mask), False, impl=_lib.IMPL_TCGEN05)
+    assert _lib.device_status() == 0
+    slow = _run_kernels(c(q), c(k), c(v), c(tq), c(tk), c(tv), c(go), c(gto), c(mask), False, impl=_lib.IMPL_GENERIC)
+    for name, x, y in zip(("O", "tO", "lse", "mu", "dq", "dk", "dv"), fast, slow):
+        assert torch.isfinite(x.float()).all(), name
+        if name in ("lse", "mu"):
+            assert orc.max_abs_err(x, y) < 2e-3, name
+        else:
+            _close(x, y.float(), torch.bfloat16, name)
+    b, h = 1, 7
+    sl = lambda x: c(x)[b:b + 1, h:h + 1]  # noqa: E731
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), sl(go), sl(gto),
+                                                    attn_mask=sl(mask))
+    for name, x, r in zip(("O", "tO", "dq", "dk", "dv"), (fast[0], fast[1], fast[4], fast[5], fast[6]), (ro, rto, rdq, rdk, rdv)):
+        _close(x[b:b + 1, h:h + 1], r, torch.bfloat16, name)
