@@ -176,6 +176,10 @@ typedef struct {
   void *dq, *dk, *dv;
   jvpfa_mask mask;
   int64_t in_stride[3]; /* of q, k, v, tq, tk, tv, as in jvpfa_fwd_args; go, gto, dq, dk, dv are row-major */
+  /* Optional, JVPFA_MASK_BOOL only, both or neither, L <= 8192: tile_live and tile_live_t of jvpfa_mask_tiles.  The
+   * D = 64 tcgen05 kernels then visit only the 32-row sub-tiles of live tiles; other kernels ignore them. */
+  const void* mask_tile_live;
+  const void* mask_tile_live_t;
 } jvpfa_bwd_args;
 
 int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
@@ -256,6 +260,9 @@ int jvpfa_mask_check(const jvpfa_mask_check_args* args, void* stream);
  *   head_live  n_b*n_h + 1 int32 (caller-zeroed): 1 iff the head has a true entry, and in the last
  *              element the number of live tiles of the whole mask (a caller that reads it back can leave
  *              the bitmap away when nearly every tile is live); may be NULL.
+ *   tile_live_t  the same summary the other way round, for the backward launch that owns key tiles:
+ *              n_b*n_h * ceil(L/128) * ceil(n_qt/64) uint64 (caller-zeroed); bit (qt % 64) of word qt / 64 of
+ *              entry [b*n_h + h][kt] is set iff the 128-query x 128-key tile (qt, kt) has a true entry.  May be NULL.
  */
 typedef struct {
   int32_t struct_size; /* sizeof(jvpfa_mask_tiles_args) */
@@ -263,6 +270,7 @@ typedef struct {
   jvpfa_mask mask;
   void* tile_live;
   int32_t* head_live;
+  void* tile_live_t;
 } jvpfa_mask_tiles_args;
 
 int jvpfa_mask_tiles(const jvpfa_mask_tiles_args* args, void* stream);

@@ -134,6 +134,8 @@ class BwdArgs(C.Structure):
         ("dv", C.c_void_p),
         ("mask", Mask),
         ("in_stride", C.c_int64 * 3),
+        ("mask_tile_live", C.c_void_p),
+        ("mask_tile_live_t", C.c_void_p),
     ]
 
 
@@ -188,6 +190,7 @@ class MaskTilesArgs(C.Structure):
         ("mask", Mask),
         ("tile_live", C.c_void_p),
         ("head_live", C.c_void_p),
+        ("tile_live_t", C.c_void_p),
     ]
 
 
@@ -261,7 +264,7 @@ class MaskSpec:
     bias, or int32 kv_len) and ``strides`` are the broadcast element strides of a (B,H,L,L) view.
     """
 
-    __slots__ = ("kind", "tensor", "strides", "bias_dtype", "tile_live")
+    __slots__ = ("kind", "tensor", "strides", "bias_dtype", "tile_live", "tile_live_t")
 
     def __init__(self, kind=MASK_NONE, tensor=None, strides=(0, 0, 0, 0), bias_dtype=FP32):
         self.kind = kind
@@ -269,6 +272,7 @@ class MaskSpec:
         self.strides = tuple(int(s) for s in strides)
         self.bias_dtype = bias_dtype
         self.tile_live = None  # MASK_BOOL: bitmap from mask_tiles(), lets the forward step over dead tiles
+        self.tile_live_t = None  # ... and its transpose (per 128-key tile), for the backward launch that owns keys
 
     def to_c(self) -> Mask:
         m = Mask()
@@ -356,9 +360,9 @@ def mask_check(mask: "MaskSpec", shape) -> tuple[bool, bool]:
 
 
 def mask_tiles(mask: "MaskSpec", L: int):
-    """Launches jvpfa_mask_tiles over a boolean mask (no synchronisation).  Returns ``(tile_live, head_live)``:
-    the int64 bitmap of 128 x 64 tiles with a true entry, which jvpfa_fwd takes for block skipping, and the
-    int32 per-head flags followed by the count of live tiles.  The mask's own extents follow its strides (0 = broadcast).  Raises Unsupported when the
+    """Launches jvpfa_mask_tiles over a boolean mask (no synchronisation).  Returns ``(tile_live, head_live,
+    tile_live_t)``: the int64 bitmap of 128 x 64 tiles with a true entry, which jvpfa_fwd / jvpfa_bwd take for block
+    skipping, the int32 per-head flags followed by the count of live tiles, and the bitmap per 128-key tile.  The mask's own extents follow its strides (0 = broadcast).  Raises Unsupported when the
     layout cannot be read as 16-byte pieces (key stride, alignment, L % 16)."""
     lib = load()
     t = mask.tensor
@@ -367,21 +371,24 @@ def mask_tiles(mask: "MaskSpec", L: int):
     n_qt = 1 if n_rows == 1 else (L + 127) // 128
     n_words = ((L + 63) // 64 + 63) // 64
     n_bitmap = n_b * n_h * n_qt * n_words * 2
-    buf = torch.zeros(n_bitmap + n_b * n_h + 1, device=t.device, dtype=torch.int32)  # one memset for both
+    n_bitmap_t = n_b * n_h * ((L + 127) // 128) * ((n_qt + 63) // 64) * 2
+    buf = torch.zeros(n_bitmap + n_bitmap_t + n_b * n_h + 1, device=t.device, dtype=torch.int32)  # one memset for all
     tile_live = buf[:n_bitmap].view(torch.int64)
-    head_live = buf[n_bitmap:]
+    tile_live_t = buf[n_bitmap:n_bitmap + n_bitmap_t].view(torch.int64)
+    head_live = buf[n_bitmap + n_bitmap_t:]
     a = MaskTilesArgs()
     a.struct_size = C.sizeof(MaskTilesArgs)
     a.n_b, a.n_h, a.n_rows, a.L = n_b, n_h, n_rows, L
     a.mask = mask.to_c()
     a.tile_live = tile_live.data_ptr()
     a.head_live = head_live.data_ptr()
+    a.tile_live_t = tile_live_t.data_ptr()
     with torch.cuda.device(t.device):
         rc = lib.jvpfa_mask_tiles(C.byref(a), _stream(t))
     if rc == ERR_UNSUPPORTED:
         raise Unsupported("jvpfa_mask_tiles cannot read this mask layout")
     check(rc, "jvpfa_mask_tiles")
-    return tile_live, head_live
+    return tile_live, head_live, tile_live_t
 
 
 def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
@@ -416,6 +423,8 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
     a.delta, a.eps, a.cterm = ptr(delta), ptr(eps), ptr(cterm)
     a.dq, a.dk, a.dv = ptr(dq), ptr(dk), ptr(dv)
     a.mask = mask.to_c()
+    if mask.tile_live is not None and mask.tile_live_t is not None and L <= 8192:
+        a.mask_tile_live, a.mask_tile_live_t = ptr(mask.tile_live), ptr(mask.tile_live_t)
     if in_stride is not None:
         a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
     with torch.cuda.device(q.device):

@@ -122,7 +122,34 @@ __device__ long long g_bwd_items[2][3][24];
 // One work item of the persistent loop.
 struct BwdItem {
   int bh, b, h, own0, loop_begin, n_sub;
+  // MK = 3: the item's words of the tile bitmap (bit t: streamed tile t has a true entry) and how many
+  // 32-row sub-tiles one bit stands for; sparse == false: every sub-tile from loop_begin is visited.
+  unsigned long long w0, w1;
+  int per_bit;
+  bool sparse;
 };
+
+// Position of the n-th (0-based) set bit of the 128-bit word (w1:w0); the caller guarantees it exists.
+__device__ __forceinline__ int nth_set_bit(unsigned long long w0, unsigned long long w1, int n) {
+  const uint32_t part[4] = {(uint32_t)w0, (uint32_t)(w0 >> 32), (uint32_t)w1, (uint32_t)(w1 >> 32)};
+  int pos = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = __popc(part[i]);
+    if (n < c) return pos + (int)__fns(part[i], 0u, n + 1);
+    n -= c;
+    pos += 32;
+  }
+  return 127;
+}
+
+// First streamed row of the item's s-th visited sub-tile.
+template <int BL>
+__device__ __forceinline__ int sub_l0(const BwdItem& it, int s) {
+  if (!it.sparse) return it.loop_begin + s * BL;
+  const int t = nth_set_bit(it.w0, it.w1, s / it.per_bit);
+  return (t * it.per_bit + s % it.per_bit) * BL;
+}
 
 // MK: 0 = none / causal / key padding (index comparisons); 1 = uint8 mask; 2 = additive bias of the
 // element type T.  For 1 and 2 an elementwise thread fetches its own row's share of the sub-tile from
@@ -193,6 +220,50 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       int n_end = n_valid;
       if (causal) n_end = min(n_end, it.own0 + OWN);
       it.n_sub = (n_end + BL - 1) / BL;
+    }
+    it.sparse = false;
+    it.w0 = it.w1 = 0ull;
+    it.per_bit = 1;
+    if constexpr (MK == 3) {
+      // Bitmaps have the mask's own extents: a broadcast dimension (stride 0) has one entry.
+      const long long hm = (a.mask.stride[0] ? (long long)it.b * (a.mask.stride[1] ? a.H : 1) : 0) +
+                           (a.mask.stride[1] ? it.h : 0);
+      const int n_t128 = (L + 127) / 128;
+      const bool rows = a.mask.stride[2] != 0;
+      if constexpr (OWN_KEYS) {
+        // bit qt of the transposed bitmap's entry [head][own 128-key tile]: four 32-query sub-tiles each
+        const int n_words_t = rows ? (n_t128 + 63) / 64 : 1;
+        const unsigned long long* w =
+            reinterpret_cast<const unsigned long long*>(a.mask_tile_live_t) + (hm * n_t128 + it.own0 / OWN) * n_words_t;
+        if (!rows) {  // one mask row for all queries: the own tile is live for all of them or for none
+          if (!(__ldg(w) & 1ull)) it.n_sub = 0;
+        } else {
+          it.w0 = __ldg(w);
+          it.w1 = n_words_t > 1 ? __ldg(w + 1) : 0ull;
+          it.per_bit = 128 / BL;
+          it.sparse = true;
+        }
+      } else {
+        // bit kt of the bitmap's entry [head][own 128-query tile]: 64-key tiles, two 32-key sub-tiles each
+        const int n_words = ((L + 63) / 64 + 63) / 64;
+        const unsigned long long* w = reinterpret_cast<const unsigned long long*>(a.mask_tile_live) +
+                                      (rows ? hm * n_t128 + it.own0 / OWN : hm) * n_words;
+        it.w0 = __ldg(w);
+        it.w1 = n_words > 1 ? __ldg(w + 1) : 0ull;
+        it.per_bit = 64 / BL;
+        it.sparse = true;
+      }
+      if (it.sparse) {
+        const int n_bits = __popcll(it.w0) + __popcll(it.w1);
+        int n = n_bits * it.per_bit;
+        if (n_bits > 0) {  // the highest live tile may reach past L
+          const int top = it.w1 ? 127 - __clzll(it.w1) : 63 - __clzll(it.w0);
+          const int rows_left = L - top * it.per_bit * BL;
+          const int subs_top = min(it.per_bit, (rows_left + BL - 1) / BL);
+          n -= it.per_bit - subs_top;
+        }
+        it.n_sub = n;
+      }
     }
     return true;
   };
@@ -293,9 +364,10 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       auto load_stats = [&](int s_first, Stat(&r)[CH]) {
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-          const int i = it.loop_begin + (s_first + j) * BL + lane;
           r[j] = Stat{INFINITY, 0.f, 0.f, 0.f, 0.f};
-          if (s_first + j < it.n_sub && i < L) {
+          if (s_first + j >= it.n_sub) continue;
+          const int i = sub_l0<BL>(it, s_first + j) + lane;
+          if (i < L) {
             r[j].lse = a.lse[stat_off + i];
             r[j].delta = a.delta[stat_off + i];
             if constexpr (HAS_GT) {
@@ -336,7 +408,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             ok = false;
             continue;
           }
-          const int l0 = it.loop_begin + s * BL;
+          const int l0 = sub_l0<BL>(it, s);
           if (lane == 0) TRACE(g, 18);
           if (lane == 0) {
             unsigned char* base = sLoop + st * C::STAGE_BYTES;
@@ -638,7 +710,8 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
       const int n_valid = valid_keys(it.b);
       const size_t stat_off = (size_t)it.bh * L;
       // MK != 0: start of this head's mask / bias and its row pitch, in bytes
-      constexpr int MESZ = MK == 1 ? 1 : 2;
+      constexpr bool BOOLM = MK == 1 || MK == 3;
+      constexpr int MESZ = BOOLM ? 1 : 2;
       const unsigned char* mbase = nullptr;
       long long mpitch = 0;
       if constexpr (MK != 0) {
@@ -668,7 +741,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         const int g = gbase + s;
         const int st = g % STAGES, buf = g % NBUF;
         const uint32_t tbuf = tbase + buf * C::COL_BUF;
-        const int l0 = it.loop_begin + s * BL;
+        const int l0 = sub_l0<BL>(it, s);
         // MK != 0: the thread's 32 mask / bias elements of this sub-tile, requested before the waits.
         // Indices are clamped into the tensor; what lies outside is switched off by col_lo / col_hi below.
         constexpr int NRAW = MK == 0 ? 1 : (OWN_KEYS ? 32 : 8 * MESZ);
@@ -679,7 +752,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
 #pragma unroll
             for (int col = 0; col < 32; ++col) {
               const unsigned char* e = p + (long long)min(l0 + col, L - 1) * mpitch;
-              raw[col] = MK == 1 ? ldg_nc_u8(e) : ldg_nc_u16(e);
+              raw[col] = BOOLM ? ldg_nc_u8(e) : ldg_nc_u16(e);
             }
           } else {
             const unsigned char* p = mbase + (long long)min(own_idx, L - 1) * mpitch + (size_t)l0 * MESZ;
@@ -719,7 +792,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
         // MK = 2: mb[x] = the bias of columns 2x, 2x+1 as a packed pair
         uint32_t live = 0xffffffffu;
         uint32_t mb[MK == 2 ? 16 : 1];
-        if constexpr (MK == 1) {
+        if constexpr (BOOLM) {
           live = 0u;
           if constexpr (OWN_KEYS) {
 #pragma unroll
@@ -769,7 +842,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             if constexpr (MK == 2)  // scores are in log2 units: + bias * log2(e)
               xs = __ffma2_rn(unpack2<T>(c ? mb[8 + x] : mb[x]), make_float2(kLog2e, kLog2e), xs);
             float2 p;
-            if constexpr (MK == 1) {
+            if constexpr (BOOLM) {
               p.x = (live_c & (1u << col)) ? fast_exp2(xs.x) : 0.f;
               p.y = (live_c & (2u << col)) ? fast_exp2(xs.y) : 0.f;
             } else {
@@ -922,6 +995,7 @@ static int launch_mk64(const jvpfa_bwd_args& a, cudaStream_t s) {
 
 template <typename T>
 static int launch_t64(const jvpfa_bwd_args& a, cudaStream_t s) {
+  if (a.mask.kind == JVPFA_MASK_BOOL && a.mask_tile_live && a.mask_tile_live_t && a.L <= 8192) return launch_mk64<T, 3>(a, s);
   if (a.mask.kind == JVPFA_MASK_BOOL) return launch_mk64<T, 1>(a, s);
   if (a.mask.kind == JVPFA_MASK_BIAS) return launch_mk64<T, 2>(a, s);
   return launch_mk64<T, 0>(a, s);

@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(kCheckThreads) mask_check_kernel(const jvpfa_m
 // (512 bytes of each row): lane l of a warp reads bytes [16 l, 16 l + 16) of a row, so four
 // neighbouring lanes cover one tile; the eight warps share out the rows.
 __global__ void __launch_bounds__(256) mask_tiles_kernel(const jvpfa_mask m, int n_h, int n_rows, int L, int n_qt,
-                                                         int n_words, unsigned char* tile_live, int32_t* head_live) {
+                                                         int n_words, unsigned char* tile_live, int32_t* head_live,
+                                                         unsigned long long* tile_live_t, int n_kt128, int n_words_t) {
   __shared__ unsigned int s_bits;
   const int head = blockIdx.z, qt = blockIdx.y, kg = blockIdx.x;  // kg: group of eight key tiles
   const int b = head / n_h, h = head - b * n_h;
@@ -134,6 +135,12 @@ __global__ void __launch_bounds__(256) mask_tiles_kernel(const jvpfa_mask m, int
       head_live[head] = 1;
       atomicAdd(head_live + gridDim.z, __popc(s_bits));  // live tiles of the whole mask
     }
+    if (tile_live_t) {  // the transposed summary: per 128-key tile, one bit per 128-query tile
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if ((s_bits >> (2 * j)) & 3u)
+          atomicOr(tile_live_t + ((long long)head * n_kt128 + 4 * kg + j) * n_words_t + (qt >> 6), 1ull << (qt & 63));
+    }
   }
 }
 
@@ -144,8 +151,11 @@ int launch_mask_tiles(const jvpfa_mask_tiles_args& a, cudaStream_t stream) {
   const int n_words = (n_kt + 63) / 64;
   const int n_qt = a.n_rows == 1 ? 1 : (a.L + 127) / 128;
   const dim3 grid((unsigned)((n_kt + 7) / 8), (unsigned)n_qt, (unsigned)(a.n_b * a.n_h));
+  const int n_kt128 = (a.L + 127) / 128;
+  const int n_words_t = (n_qt + 63) / 64;
   mask_tiles_kernel<<<grid, 256, 0, stream>>>(a.mask, a.n_h, a.n_rows, a.L, n_qt, n_words,
-                                              reinterpret_cast<unsigned char*>(a.tile_live), a.head_live);
+                                              reinterpret_cast<unsigned char*>(a.tile_live), a.head_live,
+                                              reinterpret_cast<unsigned long long*>(a.tile_live_t), n_kt128, n_words_t);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "launch mask_tiles");

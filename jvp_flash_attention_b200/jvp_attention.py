@@ -103,14 +103,14 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
         spec = _lib.MaskSpec(_lib.MASK_BOOL, m8, bstrides(m8))
         try:
             # one pass: which 128 x 64 tiles have a True (the forward steps over the others) and which heads do
-            spec.tile_live, head_live = _lib.mask_tiles(spec, N)
+            spec.tile_live, head_live, spec.tile_live_t = _lib.mask_tiles(spec, N)
             every_head_live = True
             if verify:
                 *heads, n_live = head_live.tolist()  # the one read-back
                 every_head_live = all(heads)
                 n_entries = spec.tile_live.numel() // (((N + 63) // 64 + 63) // 64)
                 if n_live > 0.85 * n_entries * ((N + 63) // 64):
-                    spec.tile_live = None  # (nearly) every tile is live: the plain tile loop is quicker
+                    spec.tile_live = spec.tile_live_t = None  # (nearly) every tile is live: the plain loops are quicker
         except _lib.Unsupported:  # layout not readable as 16-byte pieces: no skipping, element-wise check
             every_head_live = _lib.mask_check(spec, m8.shape)[0] if verify else True
         assert every_head_live, "The attention mask cannot be all False for any head."

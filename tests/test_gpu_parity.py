@@ -764,7 +764,7 @@ def test_tcgen05_forward_steps_over_dead_mask_tiles(dt, B, H, L, kind, dual):
         tq = tk = tv = None
     md = mask.to(dev)
     spec = _lib.MaskSpec(_lib.MASK_BOOL, md.view(torch.uint8), tuple(0 if md.shape[d] == 1 else md.stride(d) for d in range(4)))
-    tile_live, head_live = _lib.mask_tiles(spec, L)
+    tile_live, head_live, tile_live_t = _lib.mask_tiles(spec, L)
     assert torch.equal(tile_live.cpu(), _tile_bitmap_reference(mask, L))
     assert torch.equal(head_live[:-1].cpu().bool(), mask.any(dim=(-1, -2)).reshape(-1))
     n_kt = (L + 63) // 64
@@ -796,7 +796,37 @@ def test_tcgen05_forward_steps_over_dead_mask_tiles(dt, B, H, L, kind, dual):
     else:
         ro = orc.sdpa_primal(q, k, v, attn_mask=mask)
     _close(o, ro, dtype, "O")
-    # and through the public API (classification builds the bitmap), with gradients through the generic backward
+    # the same summary per 128-key tile: bit qt of entry [head][kt]
+    n_qt, n_kt128 = (1 if mask.shape[2] == 1 else (L + 127) // 128), (L + 127) // 128
+    ref_t = torch.zeros(mask.shape[0], mask.shape[1], n_kt128, (n_qt + 63) // 64, dtype=torch.int64)
+    for kt in range(n_kt128):
+        for qt in range(n_qt):
+            rows = mask[:, :, qt * 128:(qt + 1) * 128] if mask.shape[2] > 1 else mask
+            ref_t[:, :, kt, qt // 64] |= torch.where(rows[..., kt * 128:(kt + 1) * 128].any(dim=(-1, -2)), 1 << (qt % 64), 0)
+    assert torch.equal(tile_live_t.cpu(), ref_t.reshape(-1))
+    # backward: visiting only the sub-tiles of live tiles gives the gradients of visiting all of them
+    if dual:
+        gg = torch.Generator().manual_seed(L + 2)
+        go, gto = (torch.randn(B, H, L, 64, generator=gg).to(dtype).to(dev) for _ in range(2))
+        grads = []
+        for bitmaps in ((None, None), (tile_live, tile_live_t)):
+            spec.tile_live, spec.tile_live_t = bitmaps
+            stats = torch.empty(3, B, H, L, device=dev)
+            _lib.bwd_preprocess(o, to, go, gto, mu, stats[0], stats[1], stats[2])
+            dq, dk, dv = (torch.empty(B, H, L, 64, device=dev, dtype=dtype) for _ in range(3))
+            _lib.bwd(cu(q), cu(k), cu(v), cu(tq), cu(tk), cu(tv), go, gto, lse, mu, stats[0], stats[1], stats[2], dq, dk, dv,
+                     spec, 0.125, _lib.IMPL_TCGEN05)
+            torch.cuda.synchronize()
+            assert _lib.device_status() == 0
+            grads.append((dq, dk, dv))
+        for name, x, y in zip(("dq", "dk", "dv"), grads[1], grads[0]):
+            assert torch.isfinite(x.float()).all(), name
+            _close(x, y.float(), dtype, name)  # summation order over sub-tiles is the same; dead ones add zeros
+        _, _, rdq, rdk, rdv = orc.grads_through_both(q[:1, :1], k[:1, :1], v[:1, :1], tq[:1, :1], tk[:1, :1], tv[:1, :1],
+                                                     go[:1, :1].cpu(), gto[:1, :1].cpu(), attn_mask=mask[:1, :1])
+        for name, x, r in zip(("dq", "dk", "dv"), grads[1], (rdq, rdk, rdv)):
+            _close(x[:1, :1], r, dtype, name)
+    # and through the public API (classification builds the bitmaps), with gradients
     a = [cu(x).requires_grad_() for x in (q, k, v)]
     out = ja.attention(*a, attn_mask=md)
     assert torch.equal(out.detach(), o)
