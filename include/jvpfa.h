@@ -113,9 +113,9 @@ typedef struct {
   jvpfa_mask mask;
   /* Element strides of the batch, head and row dimensions of q, k, v, tq, tk, tv (all six alike; the
    * head dimension D is always contiguous).  {0,0,0} means (B,H,L,D) row-major.  Anything else, e.g. the
-   * (B,H,L,D) view of a (B,L,H,D) tensor, {L*H*D, D, H*D}, is read in place by the tcgen05 kernels for
-   * D = 64 with tangents (strides must be multiples of 8 elements); other requests with strides return
-   * JVPFA_ERR_UNSUPPORTED and the caller passes contiguous copies instead (upstream always copies:
+   * (B,H,L,D) view of a (B,L,H,D) tensor, {L*H*D, D, H*D}, is read in place by the tcgen05 kernels
+   * (strides must be multiples of 8 elements); requests with strides that go to the register-tiled kernels
+   * return JVPFA_ERR_UNSUPPORTED and the caller passes contiguous copies instead (upstream always copies:
    * jvp_attention.py:2733-2734, 2787-2788).  Outputs are always (B,H,L,D) row-major. */
   int64_t in_stride[3];
   /* Optional, JVPFA_MASK_BOOL only: the bitmap written by jvpfa_mask_tiles for this mask.  The tcgen05

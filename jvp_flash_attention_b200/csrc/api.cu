@@ -152,10 +152,8 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc5 = fwd_tc5_eligible(*a);
   if (a->impl == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
-  // strided inputs are read in place only by the D = 64 kernel with tangents
-  if (has_strides(a->in_stride) &&
-      !(tc5 && a->impl != JVPFA_IMPL_GENERIC && a->D == 64 && a->tq != nullptr && a->sm_scale > 0.f))
-    return JVPFA_ERR_UNSUPPORTED;
+  // strided inputs are read in place by the tcgen05 kernels (their tensor maps carry the strides)
+  if (has_strides(a->in_stride) && !(tc5 && a->impl != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
   if (tc5 && a->impl != JVPFA_IMPL_GENERIC) return launch_fwd_tc5(*a, s);
   return launch_fwd_generic(*a, s);
 }
@@ -177,7 +175,7 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   const bool tc5 = bwd_tc5_eligible(*a);
   const int fam = impl_family(a->impl);
   if (fam == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
-  if (has_strides(a->in_stride) && !(tc5 && fam != JVPFA_IMPL_GENERIC && a->D == 64)) return JVPFA_ERR_UNSUPPORTED;
+  if (has_strides(a->in_stride) && !(tc5 && fam != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
   if (tc5 && fam != JVPFA_IMPL_GENERIC) return launch_bwd_tc5(*a, s);
   return launch_bwd_generic(*a, s);
 }

@@ -88,6 +88,7 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
   const int bh = blockIdx.y;
+  const int tma_b = bh / a.H, tma_h = bh - tma_b * a.H;  // coordinates in the (D, L, H, B) tensor maps
   const int b = bh / a.H;
   const bool causal = a.mask.kind == JVPFA_MASK_CAUSAL;
   int n_valid = L;
@@ -142,18 +143,18 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
         for (int hf = 0; hf < HALVES; ++hf) {
           const int x = hf * 64, o = hf * (OWN * 128);
           if constexpr (OWN_KEYS) {
-            tma_load_3d(sOwn + C::SLOT_K * C::OWN_BYTES + o, &maps.k, own_full, x, own0, bh);
-            tma_load_3d(sOwn + C::SLOT_V * C::OWN_BYTES + o, &maps.v, own_full, x, own0, bh);
+            tma_load_4d(sOwn + C::SLOT_K * C::OWN_BYTES + o, &maps.k, own_full, x, own0, tma_h, tma_b);
+            tma_load_4d(sOwn + C::SLOT_V * C::OWN_BYTES + o, &maps.v, own_full, x, own0, tma_h, tma_b);
             if constexpr (HAS_GT) {
-              tma_load_3d(sOwn + C::SLOT_TK * C::OWN_BYTES + o, &maps.tk, own_full, x, own0, bh);
-              tma_load_3d(sOwn + C::SLOT_TV * C::OWN_BYTES + o, &maps.tv, own_full, x, own0, bh);
+              tma_load_4d(sOwn + C::SLOT_TK * C::OWN_BYTES + o, &maps.tk, own_full, x, own0, tma_h, tma_b);
+              tma_load_4d(sOwn + C::SLOT_TV * C::OWN_BYTES + o, &maps.tv, own_full, x, own0, tma_h, tma_b);
             }
           } else {
-            tma_load_3d(sOwn + C::SLOT_Q * C::OWN_BYTES + o, &maps.q, own_full, x, own0, bh);
-            if constexpr (HAS_GO) tma_load_3d(sOwn + C::SLOT_GO * C::OWN_BYTES + o, &maps.go, own_full, x, own0, bh);
+            tma_load_4d(sOwn + C::SLOT_Q * C::OWN_BYTES + o, &maps.q, own_full, x, own0, tma_h, tma_b);
+            if constexpr (HAS_GO) tma_load_4d(sOwn + C::SLOT_GO * C::OWN_BYTES + o, &maps.go, own_full, x, own0, tma_h, tma_b);
             if constexpr (HAS_GT) {
-              tma_load_3d(sOwn + C::SLOT_TQ * C::OWN_BYTES + o, &maps.tq, own_full, x, own0, bh);
-              tma_load_3d(sOwn + C::SLOT_G * C::OWN_BYTES + o, &maps.g, own_full, x, own0, bh);
+              tma_load_4d(sOwn + C::SLOT_TQ * C::OWN_BYTES + o, &maps.tq, own_full, x, own0, tma_h, tma_b);
+              tma_load_4d(sOwn + C::SLOT_G * C::OWN_BYTES + o, &maps.g, own_full, x, own0, tma_h, tma_b);
             }
           }
         }
@@ -169,18 +170,18 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
           for (int hf = 0; hf < HALVES; ++hf) {
             const int x = hf * 64, o = hf * (BL * 128);
             if constexpr (OWN_KEYS) {
-              tma_load_3d(base + C::SLOT_Q * C::LOOP_BYTES + o, &maps.q, loop_full + st, x, l0, bh);
-              if constexpr (HAS_GO) tma_load_3d(base + C::SLOT_GO * C::LOOP_BYTES + o, &maps.go, loop_full + st, x, l0, bh);
+              tma_load_4d(base + C::SLOT_Q * C::LOOP_BYTES + o, &maps.q, loop_full + st, x, l0, tma_h, tma_b);
+              if constexpr (HAS_GO) tma_load_4d(base + C::SLOT_GO * C::LOOP_BYTES + o, &maps.go, loop_full + st, x, l0, tma_h, tma_b);
               if constexpr (HAS_GT) {
-                tma_load_3d(base + C::SLOT_TQ * C::LOOP_BYTES + o, &maps.tq, loop_full + st, x, l0, bh);
-                tma_load_3d(base + C::SLOT_G * C::LOOP_BYTES + o, &maps.g, loop_full + st, x, l0, bh);
+                tma_load_4d(base + C::SLOT_TQ * C::LOOP_BYTES + o, &maps.tq, loop_full + st, x, l0, tma_h, tma_b);
+                tma_load_4d(base + C::SLOT_G * C::LOOP_BYTES + o, &maps.g, loop_full + st, x, l0, tma_h, tma_b);
               }
             } else {
-              tma_load_3d(base + C::SLOT_K * C::LOOP_BYTES + o, &maps.k, loop_full + st, x, l0, bh);
-              tma_load_3d(base + C::SLOT_V * C::LOOP_BYTES + o, &maps.v, loop_full + st, x, l0, bh);
+              tma_load_4d(base + C::SLOT_K * C::LOOP_BYTES + o, &maps.k, loop_full + st, x, l0, tma_h, tma_b);
+              tma_load_4d(base + C::SLOT_V * C::LOOP_BYTES + o, &maps.v, loop_full + st, x, l0, tma_h, tma_b);
               if constexpr (HAS_GT) {
-                tma_load_3d(base + C::SLOT_TK * C::LOOP_BYTES + o, &maps.tk, loop_full + st, x, l0, bh);
-                tma_load_3d(base + C::SLOT_TV * C::LOOP_BYTES + o, &maps.tv, loop_full + st, x, l0, bh);
+                tma_load_4d(base + C::SLOT_TK * C::LOOP_BYTES + o, &maps.tk, loop_full + st, x, l0, tma_h, tma_b);
+                tma_load_4d(base + C::SLOT_TV * C::LOOP_BYTES + o, &maps.tv, loop_full + st, x, l0, tma_h, tma_b);
               }
             }
           }
@@ -454,14 +455,14 @@ static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status
   const CUtensorMapDataType dt = Fmt<T>::kTma;
   const int key_rows = OWN_KEYS ? C::OWN : C::BL;
   const int qry_rows = OWN_KEYS ? C::BL : C::OWN;
-  bool ok = encode_map(&m.k, dt, a.k, D, a.L, BH, key_rows) && encode_map(&m.v, dt, a.v, D, a.L, BH, key_rows) &&
-            encode_map(&m.q, dt, a.q, D, a.L, BH, qry_rows);
+  bool ok = encode_map4d(&m.k, dt, a.k, D, a.L, a.H, a.B, a.in_stride, key_rows) && encode_map4d(&m.v, dt, a.v, D, a.L, a.H, a.B, a.in_stride, key_rows) &&
+            encode_map4d(&m.q, dt, a.q, D, a.L, a.H, a.B, a.in_stride, qry_rows);
   m.tk = m.tv = m.k;
   m.go = m.tq = m.g = m.q;
-  if (HAS_GO) ok = ok && encode_map(&m.go, dt, a.go, D, a.L, BH, qry_rows);
+  if (HAS_GO) ok = ok && encode_map4d(&m.go, dt, a.go, D, a.L, a.H, a.B, nullptr, qry_rows);
   if (HAS_GT)
-    ok = ok && encode_map(&m.tk, dt, a.tk, D, a.L, BH, key_rows) && encode_map(&m.tv, dt, a.tv, D, a.L, BH, key_rows) &&
-         encode_map(&m.tq, dt, a.tq, D, a.L, BH, qry_rows) && encode_map(&m.g, dt, a.gto, D, a.L, BH, qry_rows);
+    ok = ok && encode_map4d(&m.tk, dt, a.tk, D, a.L, a.H, a.B, a.in_stride, key_rows) && encode_map4d(&m.tv, dt, a.tv, D, a.L, a.H, a.B, a.in_stride, key_rows) &&
+         encode_map4d(&m.tq, dt, a.tq, D, a.L, a.H, a.B, a.in_stride, qry_rows) && encode_map4d(&m.g, dt, a.gto, D, a.L, a.H, a.B, nullptr, qry_rows);
   if (!ok) {
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(bwd)");
     return JVPFA_ERR_CUDA;

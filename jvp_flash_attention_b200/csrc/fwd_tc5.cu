@@ -96,6 +96,7 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
   const int bh = blockIdx.y;
+  const int tma_b = bh / a.H, tma_h = bh - tma_b * a.H;  // coordinates in the (D, L, H, B) tensor maps
   const int b = bh / a.H;
   const int mt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
   const int m0 = mt * BM;
@@ -139,8 +140,8 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
       prefetch_tmap(&maps.v);
       mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
       for (int hf = 0; hf < HALVES; ++hf) {
-        tma_load_3d(sQ + hf * (BM * 128), &maps.q, q_full, hf * 64, m0, bh);
-        if constexpr (DUAL) tma_load_3d(sTQ + hf * (BM * 128), &maps.tq, q_full, hf * 64, m0, bh);
+        tma_load_4d(sQ + hf * (BM * 128), &maps.q, q_full, hf * 64, m0, tma_h, tma_b);
+        if constexpr (DUAL) tma_load_4d(sTQ + hf * (BM * 128), &maps.tq, q_full, hf * 64, m0, tma_h, tma_b);
       }
       for (int it = 0; it < n_tiles; ++it) {
         const int st = it % STAGES;
@@ -150,11 +151,11 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
         mbar_expect_tx(kv_full + st, C::N_KV * C::KV_BYTES);
         const int n0 = it * BN;
         for (int hf = 0; hf < HALVES; ++hf) {
-          tma_load_3d(base + hf * (BN * 128), &maps.k, kv_full + st, hf * 64, n0, bh);
-          tma_load_3d(base + C::KV_BYTES + hf * (BN * 128), &maps.v, kv_full + st, hf * 64, n0, bh);
+          tma_load_4d(base + hf * (BN * 128), &maps.k, kv_full + st, hf * 64, n0, tma_h, tma_b);
+          tma_load_4d(base + C::KV_BYTES + hf * (BN * 128), &maps.v, kv_full + st, hf * 64, n0, tma_h, tma_b);
           if constexpr (DUAL) {
-            tma_load_3d(base + 2 * C::KV_BYTES + hf * (BN * 128), &maps.tk, kv_full + st, hf * 64, n0, bh);
-            tma_load_3d(base + 3 * C::KV_BYTES + hf * (BN * 128), &maps.tv, kv_full + st, hf * 64, n0, bh);
+            tma_load_4d(base + 2 * C::KV_BYTES + hf * (BN * 128), &maps.tk, kv_full + st, hf * 64, n0, tma_h, tma_b);
+            tma_load_4d(base + 3 * C::KV_BYTES + hf * (BN * 128), &maps.tv, kv_full + st, hf * 64, n0, tma_h, tma_b);
           }
         }
       }
@@ -419,28 +420,15 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH,
-                       int box_rows) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)L * D * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
-bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* st,
-                 int box_rows) {
+bool encode_map4d(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, int H, int B, const int64_t* st,
+                  int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   const bool dense = st == nullptr || (st[0] == 0 && st[1] == 0 && st[2] == 0);
-  const cuuint64_t sb = dense ? (cuuint64_t)H * L * 64 : (cuuint64_t)st[0];
-  const cuuint64_t sh = dense ? (cuuint64_t)L * 64 : (cuuint64_t)st[1];
-  const cuuint64_t sl = dense ? 64 : (cuuint64_t)st[2];
-  cuuint64_t dims[4] = {64, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  const cuuint64_t sb = dense ? (cuuint64_t)H * L * D : (cuuint64_t)st[0];
+  const cuuint64_t sh = dense ? (cuuint64_t)L * D : (cuuint64_t)st[1];
+  const cuuint64_t sl = dense ? (cuuint64_t)D : (cuuint64_t)st[2];
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t strides[3] = {sl * 2, sh * 2, sb * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -449,17 +437,22 @@ bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L,
   return r == CUDA_SUCCESS;
 }
 
+bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* st,
+                 int box_rows) {
+  return encode_map4d(m, dt, ptr, 64, L, H, B, st, box_rows);
+}
+
 template <typename T, int D, bool DUAL>
 static int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D, DUAL>;
   FwdMaps maps;
   const long long BH = (long long)a.B * a.H;
   const CUtensorMapDataType dt = Fmt<T>::kTma;
-  bool ok = encode_map(&maps.q, dt, a.q, D, a.L, BH, C::BM) && encode_map(&maps.k, dt, a.k, D, a.L, BH, C::BN) &&
-            encode_map(&maps.v, dt, a.v, D, a.L, BH, C::BN);
+  bool ok = encode_map4d(&maps.q, dt, a.q, D, a.L, a.H, a.B, a.in_stride, C::BM) && encode_map4d(&maps.k, dt, a.k, D, a.L, a.H, a.B, a.in_stride, C::BN) &&
+            encode_map4d(&maps.v, dt, a.v, D, a.L, a.H, a.B, a.in_stride, C::BN);
   if (DUAL)
-    ok = ok && encode_map(&maps.tq, dt, a.tq, D, a.L, BH, C::BM) && encode_map(&maps.tk, dt, a.tk, D, a.L, BH, C::BN) &&
-         encode_map(&maps.tv, dt, a.tv, D, a.L, BH, C::BN);
+    ok = ok && encode_map4d(&maps.tq, dt, a.tq, D, a.L, a.H, a.B, a.in_stride, C::BM) && encode_map4d(&maps.tk, dt, a.tk, D, a.L, a.H, a.B, a.in_stride, C::BN) &&
+         encode_map4d(&maps.tv, dt, a.tv, D, a.L, a.H, a.B, a.in_stride, C::BN);
   else
     maps.tq = maps.tk = maps.tv = maps.q;
   if (!ok) {

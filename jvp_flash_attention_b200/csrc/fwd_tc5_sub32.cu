@@ -83,6 +83,7 @@ fwd_tc5_sub32_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdSub32Map
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
   const int bh = blockIdx.y;
+  const int tma_b = bh / a.H, tma_h = bh - tma_b * a.H;  // coordinates in the (D, L, H, B) tensor maps
   const int b = bh / a.H;
   const int mt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
   const int m0 = mt * BM;
@@ -124,8 +125,8 @@ fwd_tc5_sub32_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdSub32Map
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_sub > 0) {
       mbar_expect_tx(q_full, C::N_Q * C::Q_BYTES);
-      tma_load_3d(sQ, &maps.q, q_full, 0, m0, bh);
-      if constexpr (DUAL) tma_load_3d(sTQ, &maps.tq, q_full, 0, m0, bh);
+      tma_load_4d(sQ, &maps.q, q_full, 0, m0, tma_h, tma_b);
+      if constexpr (DUAL) tma_load_4d(sTQ, &maps.tq, q_full, 0, m0, tma_h, tma_b);
       for (int s = 0; s < n_sub; ++s) {
         const int st = s % STAGES;
         const uint32_t ph = (s / STAGES) & 1;
@@ -133,11 +134,11 @@ fwd_tc5_sub32_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdSub32Map
         unsigned char* base = sKV + st * C::STAGE_BYTES;
         mbar_expect_tx(kv_full + st, C::STAGE_BYTES);
         const int n0 = s * BN;
-        tma_load_3d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, bh);
-        tma_load_3d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, bh);
+        tma_load_4d(base + C::SLOT_K * C::KV_BYTES, &maps.k, kv_full + st, 0, n0, tma_h, tma_b);
+        tma_load_4d(base + C::SLOT_V * C::KV_BYTES, &maps.v, kv_full + st, 0, n0, tma_h, tma_b);
         if constexpr (DUAL) {
-          tma_load_3d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, bh);
-          tma_load_3d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, bh);
+          tma_load_4d(base + C::SLOT_TK * C::KV_BYTES, &maps.tk, kv_full + st, 0, n0, tma_h, tma_b);
+          tma_load_4d(base + C::SLOT_TV * C::KV_BYTES, &maps.tv, kv_full + st, 0, n0, tma_h, tma_b);
         }
       }
     }
@@ -399,11 +400,11 @@ static int launch_fwd_sub32(const jvpfa_fwd_args& a, cudaStream_t stream) {
   FwdSub32Maps maps;
   const long long BH = (long long)a.B * a.H;
   const CUtensorMapDataType dt = Fmt<T>::kTma;
-  bool ok = encode_map(&maps.q, dt, a.q, 64, a.L, BH, C::BM) && encode_map(&maps.k, dt, a.k, 64, a.L, BH, C::BN) &&
-            encode_map(&maps.v, dt, a.v, 64, a.L, BH, C::BN);
+  bool ok = encode_map4d(&maps.q, dt, a.q, 64, a.L, a.H, a.B, a.in_stride, C::BM) && encode_map4d(&maps.k, dt, a.k, 64, a.L, a.H, a.B, a.in_stride, C::BN) &&
+            encode_map4d(&maps.v, dt, a.v, 64, a.L, a.H, a.B, a.in_stride, C::BN);
   if (DUAL)
-    ok = ok && encode_map(&maps.tq, dt, a.tq, 64, a.L, BH, C::BM) && encode_map(&maps.tk, dt, a.tk, 64, a.L, BH, C::BN) &&
-         encode_map(&maps.tv, dt, a.tv, 64, a.L, BH, C::BN);
+    ok = ok && encode_map4d(&maps.tq, dt, a.tq, 64, a.L, a.H, a.B, a.in_stride, C::BM) && encode_map4d(&maps.tk, dt, a.tk, 64, a.L, a.H, a.B, a.in_stride, C::BN) &&
+         encode_map4d(&maps.tv, dt, a.tv, 64, a.L, a.H, a.B, a.in_stride, C::BN);
   else
     maps.tq = maps.tk = maps.tv = maps.q;
   if (!ok) {

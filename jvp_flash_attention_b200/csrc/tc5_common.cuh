@@ -53,9 +53,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Host: (D, L, B*H) view of a contiguous (B, H, L, D) 16-bit tensor, box = 64 columns x box_rows
-// rows, 128-byte swizzle, out-of-range rows read as zero.  Defined in fwd_tc5.cu.
-bool encode_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, long long BH, int box_rows);
 // Read-only global loads and 16-bit unpacking used for user masks and bias.
 template <typename T>
 __device__ __forceinline__ float2 unpack2(uint32_t w);
@@ -86,9 +83,13 @@ __device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
 }
 
 // Host: (64, L, H, B) view of a 16-bit tensor whose batch / head / row strides (in elements) are given
-// (all zero: (B,H,L,64) row-major); same box, swizzle and fill.  Defined in fwd_tc5.cu.
+// (all zero: (B,H,L,64) row-major); box = 64 columns x box_rows rows, 128-byte swizzle, out-of-range
+// rows read as zero.  Defined in fwd_tc5.cu.
 bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* stride_bhl,
                  int box_rows);
+// The same for head dimension D (64-column boxes: a D = 128 tile is two loads).
+bool encode_map4d(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, int H, int B, const int64_t* stride_bhl,
+                  int box_rows);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -608,14 +608,15 @@ def test_reference_harness_grid_short_lengths(dt):
     assert not bad, bad
 
 
-@pytest.mark.parametrize("dt,kind", [("bf16", "causal"), ("fp16", "kvlen"), ("bf16", "none")])
-def test_strided_views_are_read_in_place(dt, kind):
+@pytest.mark.parametrize("dt,kind,D", [("bf16", "causal", 64), ("fp16", "kvlen", 64), ("bf16", "none", 64),
+                                        ("bf16", "causal", 128), ("fp16", "none", 128)])
+def test_strided_views_are_read_in_place(dt, kind, D):
     """q, k, v (and tangents) given as the (B,H,L,D) view of (B,L,H,D) tensors -- what a model's projection layer
-    produces before `.transpose(1, 2)` -- go to the D = 64 tcgen05 kernels with their strides (no copy; the
+    produces before `.transpose(1, 2)` -- go to the tcgen05 kernels with their strides (no copy; the
     reference always calls `.contiguous()`, jvp_attention.py:2733-2734).  Results must equal those from
     contiguous copies bit for bit, through the C ABI and through the public API with gradients."""
     dtype, dev = DT[dt], torch.device("cuda:0")
-    B, H, L, D = 3, 5, 200, 64
+    B, H, L = 3, 5, 200
     g = torch.Generator().manual_seed(11)
     base = [torch.randn(B, L, H, D, generator=g) for _ in range(8)]
     for i in (3, 4, 5):
@@ -657,6 +658,10 @@ def test_strided_views_are_read_in_place(dt, kind):
 
     for a, b in zip(api(q, k, v), api(q.contiguous(), k.contiguous(), v.contiguous())):
         assert torch.equal(a.contiguous(), b.contiguous())
+    # primal only (D = 64: the 32-key sub-tile kernel), views against copies
+    assert torch.equal(ja.JVPAttn.fwd(q, k, v, causal=causal, attn_mask=None if mask is None else mask.to(dev)),
+                       ja.JVPAttn.fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal=causal,
+                                      attn_mask=None if mask is None else mask.to(dev)))
     # a layout the kernels cannot read in place (fp32 goes to the register-tiled family) is still served
     o32 = ja.JVPAttn.fwd(q.float(), k.float(), v.float(), causal=causal)
     ro = orc.sdpa_primal(q.float().cpu(), k.float().cpu(), v.float().cpu(), causal=causal)
