@@ -55,7 +55,11 @@ struct BwdCfg {
   static constexpr int SLOT_Q = 0, SLOT_GO = 1, SLOT_TQ = 1 + (HAS_GO ? 1 : 0), SLOT_G = 2 + (HAS_GO ? 1 : 0);
 };
 
-template <typename T, int D, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+// MK: 0 = none / causal / key padding; 1 = uint8 mask; 2 = bias of the element type T.  For 1 and 2 the
+// elementwise threads fetch the 16 mask elements of each column chunk from global memory ahead of the
+// chunk's tcgen05.ld (own queries: one or two 16-byte loads of the thread's mask row; own keys: one element
+// of each of 16 query rows).  Key stride 1, 16-byte aligned rows and L % 16 == 0 are the host's responsibility.
+template <typename T, int D, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
 __global__ void __launch_bounds__(192, 1)
 bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int* status) {
   using C = BwdCfg<D, OWN_KEYS, HAS_GO, HAS_GT>;
@@ -307,6 +311,15 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
       }
     }
 
+    constexpr int MESZ = MK == 1 ? 1 : 2;  // bytes per mask element
+    const unsigned char* mbase = nullptr;
+    long long mpitch = 0;
+    if constexpr (MK != 0) {
+      mbase = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
+              ((long long)tma_b * a.mask.stride[0] + (long long)tma_h * a.mask.stride[1]) * MESZ;
+      mpitch = a.mask.stride[2] * MESZ;
+    }
+
     for (int it = 0; it < n_tiles; ++it) {
       const int st = it % STAGES;
       const int l0 = loop_begin + it * BL;
@@ -333,6 +346,31 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
       for (int c = 0; c < BL / 16; ++c) {
         uint32_t s[16], fp[16];
         uint32_t ts[HAS_GT ? 16 : 1], e[HAS_GT ? 16 : 1];
+        // MK != 0: the chunk's 16 mask / bias elements, one per column (indices clamped into the tensor;
+        // what lies outside is switched off by the index tests below)
+        uint32_t mraw[MK == 0 ? 1 : 16];
+        if constexpr (MK != 0) {
+          if constexpr (OWN_KEYS) {
+            const unsigned char* p = mbase + (long long)min(own_idx, L - 1) * MESZ;
+#pragma unroll
+            for (int x = 0; x < 16; ++x) {
+              const unsigned char* el = p + (long long)min(l0 + 16 * c + x, L - 1) * mpitch;
+              mraw[x] = MK == 1 ? ldg_nc_u8(el) : ldg_nc_u16(el);
+            }
+          } else {
+            const unsigned char* p = mbase + (long long)min(own_idx, L - 1) * mpitch + (size_t)(l0 + 16 * c) * MESZ;
+            uint32_t w[4 * MESZ];
+#pragma unroll
+            for (int j = 0; j < MESZ; ++j) {
+              uint4 r = make_uint4(0u, 0u, 0u, 0u);
+              if (l0 + 16 * c + (j + 1) * (16 / MESZ) <= L) r = ldg_nc_v4(p + 16 * j);
+              w[4 * j] = r.x, w[4 * j + 1] = r.y, w[4 * j + 2] = r.z, w[4 * j + 3] = r.w;
+            }
+#pragma unroll
+            for (int x = 0; x < 16; ++x)
+              mraw[x] = MK == 1 ? ((w[x >> 2] >> ((x & 3) * 8)) & 0xffu) : ((w[x >> 1] >> ((x & 1) * 16)) & 0xffffu);
+          }
+        }
         tmem_ld16(tbase + C::COL_S + 16 * c, s);
         tmem_ld16(tbase + C::COL_FP + 16 * c, fp);
         if constexpr (HAS_GT) {
@@ -357,7 +395,11 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
             i = own_idx;
             j = l0 + col;
           }
-          float p = fast_exp2(__uint_as_float(s[x]) * scale_log2 - lse);
+          float arg = __uint_as_float(s[x]) * scale_log2 - lse;
+          if constexpr (MK == 2) arg = fmaf(unpack1<T>(mraw[x]), kLog2e, arg);  // scores are in log2 units
+          float p = fast_exp2(arg);
+          if constexpr (MK == 1)
+            if (mraw[x] == 0u) p = 0.f;
           if (partial && (j >= n_valid || (causal && j > i))) p = 0.f;
           pv[x] = p;
           if constexpr (HAS_GT) {
@@ -447,8 +489,9 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-template <typename T, int D, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+template <typename T, int D, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status, bool overlap_previous) {
+  static_assert(MK >= 0 && MK <= 2, "mask mode");
   using C = BwdCfg<D, OWN_KEYS, HAS_GO, HAS_GT>;
   BwdMaps m;
   const long long BH = (long long)a.B * a.H;
@@ -467,7 +510,7 @@ static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(bwd)");
     return JVPFA_ERR_CUDA;
   }
-  auto kern = bwd_tc5_kernel<T, D, OWN_KEYS, HAS_GO, HAS_GT>;
+  auto kern = bwd_tc5_kernel<T, D, OWN_KEYS, HAS_GO, HAS_GT, MK>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(bwd_tc5)");
@@ -490,7 +533,7 @@ static int launch_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status
   return JVPFA_OK;
 }
 
-template <typename T, int D, bool HAS_GO, bool HAS_GT>
+template <typename T, int D, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_both(const jvpfa_bwd_args& a, cudaStream_t s) {
   int* status = tc5_status_device_ptr();
   if (!status) {
@@ -499,25 +542,26 @@ static int launch_both(const jvpfa_bwd_args& a, cudaStream_t s) {
   }
   int rc = JVPFA_OK;
   const bool both = !(a.impl & (JVPFA_IMPL_ONLY_DQ | JVPFA_IMPL_ONLY_DKDV));
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half<T, D, true, HAS_GO, HAS_GT>(a, s, status, false);
+  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half<T, D, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
   if (rc) return rc;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half<T, D, false, HAS_GO, HAS_GT>(a, s, status, both);
+  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half<T, D, false, HAS_GO, HAS_GT, MK>(a, s, status, both);
   return rc;
 }
 
-template <typename T, int D>
+template <typename T, int D, int MK>
 static int launch_d(const jvpfa_bwd_args& a, cudaStream_t s) {
   const bool go = a.go != nullptr, gt = a.gto != nullptr;
-  if (go && gt) return launch_both<T, D, true, true>(a, s);
-  if (gt) return launch_both<T, D, false, true>(a, s);
-  return launch_both<T, D, true, false>(a, s);
+  if (go && gt) return launch_both<T, D, true, true, MK>(a, s);
+  if (gt) return launch_both<T, D, false, true, MK>(a, s);
+  return launch_both<T, D, true, false, MK>(a, s);
 }
 
 template <typename T>
 static int launch_t(const jvpfa_bwd_args& a, cudaStream_t s) {
-  if (a.D == 64) return launch_d<T, 64>(a, s);
-  if (a.D == 128) return launch_d<T, 128>(a, s);
-  return JVPFA_ERR_UNSUPPORTED;
+  if (a.D != 128) return JVPFA_ERR_UNSUPPORTED;  // D = 64 has its own kernels (bwd_tc5_d64.cu)
+  if (a.mask.kind == JVPFA_MASK_BOOL) return launch_d<T, 128, 1>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BIAS) return launch_d<T, 128, 2>(a, s);
+  return launch_d<T, 128, 0>(a, s);
 }
 
 }  // namespace tc5
@@ -527,8 +571,8 @@ bool bwd_tc5_eligible(const jvpfa_bwd_args& a) {
   if (a.D != 64 && a.D != 128) return false;
   const int k = a.mask.kind;
   if (k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN) return true;
-  // Boolean masks and bias: the D = 64 kernel reads 16-byte pieces of mask rows (bwd_tc5_d64.cu)
-  if (a.D != 64 || (a.L & 15) != 0) return false;
+  // Boolean masks and bias: the elementwise threads read 16-byte pieces of mask rows
+  if ((a.L & 15) != 0) return false;
   if (k == JVPFA_MASK_BIAS && a.mask.bias_dtype != a.dtype) return false;
   const long long esz = k == JVPFA_MASK_BOOL ? 1 : 2;
   if (a.mask.stride[3] != 1 || (reinterpret_cast<uintptr_t>(a.mask.ptr) & 15u) != 0) return false;

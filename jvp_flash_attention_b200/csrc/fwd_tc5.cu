@@ -66,7 +66,10 @@ struct FwdMaps {
   CUtensorMap q, tq, k, tk, v, tv;
 };
 
-template <typename T, int D, bool DUAL>
+// MK: 0 = none / causal / key padding; 1 = uint8 mask; 2 = bias of the element type T (the softmax thread
+// of a query row reads its 64 mask elements of the tile with 16-byte loads before it waits for the scores;
+// key stride 1, 16-byte aligned rows and L % 16 == 0 are the host's responsibility).
+template <typename T, int D, bool DUAL, int MK>
 __global__ void __launch_bounds__(192, FwdCfg<D, DUAL>::MIN_CTAS)
 fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   using C = FwdCfg<D, DUAL>;
@@ -221,8 +224,25 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
     float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
     bool alive = true;
 
+    constexpr int MESZ = MK == 1 ? 1 : 2;          // bytes per mask element
+    constexpr int MW = MK == 0 ? 1 : 16 * MESZ;    // 32-bit words per row of a 64-key tile
+    const unsigned char* mrow = nullptr;
+    if constexpr (MK != 0)
+      mrow = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
+             ((long long)tma_b * a.mask.stride[0] + (long long)tma_h * a.mask.stride[1] +
+              (long long)min(i, L - 1) * a.mask.stride[2]) * MESZ;
+
     for (int it = 0; it < n_tiles; ++it) {
       const int n0 = it * BN;
+      uint32_t mw[MW];
+      if constexpr (MK != 0) {
+#pragma unroll
+        for (int j = 0; j < MW / 4; ++j) {
+          uint4 r = make_uint4(0u, 0u, 0u, 0u);
+          if (n0 + (j + 1) * (16 / MESZ) <= L) r = ldg_nc_v4(mrow + (size_t)n0 * MESZ + 16 * j);
+          mw[4 * j] = r.x, mw[4 * j + 1] = r.y, mw[4 * j + 2] = r.z, mw[4 * j + 3] = r.w;
+        }
+      }
       if (!mbar_wait(s_full, it & 1, ab, kAbortSFull)) {
         alive = false;
         break;
@@ -238,6 +258,14 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
       for (int c = 0; c < 32; ++c) {
         float v0 = __uint_as_float(x0[c]) * scale_log2;
         float v1 = __uint_as_float(x1[c]) * scale_log2;
+        if constexpr (MK == 1) {  // byte c and byte 32 + c of the row's 64
+          if (!((mw[c >> 2] >> ((c & 3) * 8)) & 0xffu)) v0 = -INFINITY;
+          if (!((mw[8 + (c >> 2)] >> ((c & 3) * 8)) & 0xffu)) v1 = -INFINITY;
+        }
+        if constexpr (MK == 2) {  // scores are in log2 units: bias * log2(e)
+          v0 = fmaf(unpack1<T>((mw[c >> 1] >> ((c & 1) * 16)) & 0xffffu), kLog2e, v0);
+          v1 = fmaf(unpack1<T>((mw[16 + (c >> 1)] >> ((c & 1) * 16)) & 0xffffu), kLog2e, v1);
+        }
         if (partial) {
           const int j0 = n0 + c, j1 = n0 + 32 + c;
           if (j0 >= n_valid || (causal && j0 > i)) v0 = -INFINITY;
@@ -442,7 +470,7 @@ bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L,
   return encode_map4d(m, dt, ptr, 64, L, H, B, st, box_rows);
 }
 
-template <typename T, int D, bool DUAL>
+template <typename T, int D, bool DUAL, int MK>
 static int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D, DUAL>;
   FwdMaps maps;
@@ -459,7 +487,7 @@ static int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
     return JVPFA_ERR_CUDA;
   }
-  auto kern = fwd_tc5_kernel<T, D, DUAL>;
+  auto kern = fwd_tc5_kernel<T, D, DUAL, MK>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(fwd_tc5)");
@@ -478,9 +506,11 @@ static int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
 template <typename T>
 static int launch_t(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
-  if (a.D == 64) return dual ? launch_one<T, 64, true>(a, s) : launch_one<T, 64, false>(a, s);
-  if (a.D == 128) return dual ? launch_one<T, 128, true>(a, s) : launch_one<T, 128, false>(a, s);
-  return JVPFA_ERR_UNSUPPORTED;
+  if (a.D == 64) return dual ? launch_one<T, 64, true, 0>(a, s) : launch_one<T, 64, false, 0>(a, s);
+  if (a.D != 128) return JVPFA_ERR_UNSUPPORTED;
+  if (a.mask.kind == JVPFA_MASK_BOOL) return dual ? launch_one<T, 128, true, 1>(a, s) : launch_one<T, 128, false, 1>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BIAS) return dual ? launch_one<T, 128, true, 2>(a, s) : launch_one<T, 128, false, 2>(a, s);
+  return dual ? launch_one<T, 128, true, 0>(a, s) : launch_one<T, 128, false, 0>(a, s);
 }
 
 }  // namespace tc5
@@ -490,8 +520,8 @@ bool fwd_tc5_eligible(const jvpfa_fwd_args& a) {
   if (a.D != 64 && a.D != 128) return false;
   const int k = a.mask.kind;
   if (k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN) return true;
-  // Boolean masks and bias: the D = 64 kernel reads 16-byte pieces of mask rows (fwd_tc5_d64.cu)
-  if (a.D != 64 || !(a.sm_scale > 0.f) || (a.L & 15) != 0) return false;
+  // Boolean masks and bias: the softmax threads read 16-byte pieces of mask rows
+  if ((a.D == 64 && !(a.sm_scale > 0.f)) || (a.L & 15) != 0) return false;
   if (k == JVPFA_MASK_BIAS && a.mask.bias_dtype != a.dtype) return false;
   const long long esz = k == JVPFA_MASK_BOOL ? 1 : 2;
   if (a.mask.stride[3] != 1 || (reinterpret_cast<uintptr_t>(a.mask.ptr) & 15u) != 0) return false;

@@ -65,6 +65,18 @@ __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
   return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
+// One 16-bit element (in the low half of h) as float.
+template <typename T>
+__device__ __forceinline__ float unpack1(uint32_t h);
+template <>
+__device__ __forceinline__ float unpack1<__nv_bfloat16>(uint32_t h) {
+  return __uint_as_float(h << 16);
+}
+template <>
+__device__ __forceinline__ float unpack1<__half>(uint32_t h) {
+  return __half2float(__ushort_as_half((unsigned short)h));
+}
+
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
   uint4 r;
   asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));

@@ -239,7 +239,8 @@ def test_tcgen05_backward_many_items_per_cta(cot, kind, dt, B, H, L):
 
 
 def test_tcgen05_dispatch_rules():
-    """AUTO takes the tcgen05 kernels exactly for 16-bit, D in {64,128}, none/causal/key-padding."""
+    """AUTO takes the tcgen05 kernels for 16-bit, D in {64,128}, none / causal / key padding, and boolean masks or bias
+    of the element type whose rows can be read as 16-byte pieces."""
     import ctypes as C
 
     lib = _lib.load()
@@ -279,6 +280,8 @@ def test_tcgen05_dispatch_rules():
     a.mask.bias_dtype = _lib.FP32
     assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
     a.mask.bias_dtype, a.D = _lib.FP16, 128
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 1
+    a.L = 72  # not a multiple of 16: rows cannot be read as 16-byte pieces
     assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
 
 
@@ -892,3 +895,34 @@ def test_reference_grid_largest_masked_case_on_tcgen05(mask_type):
                                                     attn_mask=sl(mask))
     for name, x, r in zip(("O", "tO", "dq", "dk", "dv"), (fast[0], fast[1], fast[4], fast[5], fast[6]), (ro, rto, rdq, rdk, rdv)):
         _close(x[b:b + 1, h:h + 1], r, torch.bfloat16, name)
+
+
+@pytest.mark.parametrize("cot,kind,dt,B,H,L", [
+    ("both", "none", "bf16", 2, 2, 192), ("gt", "causal", "fp16", 1, 3, 320), ("both", "bool", "bf16", 2, 2, 256),
+    ("gt", "bias", "fp16", 2, 2, 192), ("go", "bool_bcast", "bf16", 2, 2, 160), ("both", "bool_keys", "fp16", 3, 2, 224),
+    ("gt", "bias", "bf16", 1, 2, 48),
+])
+def test_tcgen05_head_dim_128_forward_and_backward(cot, kind, dt, B, H, L):
+    """The D = 128 tcgen05 kernels (forward with tangents, both backward launches) on every mask kind they take,
+    boolean masks and bias of the element type included, against the register-tiled family on all heads and the
+    float64 oracle on one."""
+    dtype = DT[dt]
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, 128, dtype, seed=B + L)
+    go = go if cot in ("go", "both") else None
+    gto = gto if cot in ("gt", "both") else None
+    mask, causal = _mask(kind, B, H, L, dtype, seed=L)
+    fast = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_TCGEN05)
+    assert _lib.device_status() == 0, "a bounded wait inside a tcgen05 kernel gave up"
+    slow = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC)
+    for name, x, y in zip(("O", "tO", "lse", "mu", "dq", "dk", "dv"), fast, slow):
+        assert torch.isfinite(x.float()).all(), name
+        if name in ("lse", "mu"):
+            assert orc.max_abs_err(x, y) < 2e-3, name
+        else:
+            _close(x, y.float(), dtype, name)
+    sl = lambda x: None if x is None else x[B - 1:, H - 1:]  # noqa: E731
+    msl = None if mask is None else mask[min(B, mask.shape[0]) - 1:, min(H, mask.shape[1]) - 1:]
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), sl(go), sl(gto),
+                                                    attn_mask=msl, causal=causal)
+    for name, x, r in zip(("O", "tO", "dq", "dk", "dv"), (fast[0], fast[1], fast[4], fast[5], fast[6]), (ro, rto, rdq, rdk, rdv)):
+        _close(x[B - 1:, H - 1:], r, dtype, name)
