@@ -289,6 +289,15 @@ class MaskSpec:
         return m
 
 
+def _launch(t: torch.Tensor, entry, args) -> int:
+    """Calls a library entry point with ``t``'s device current and its current stream.  Switching the device
+    through the context manager costs a few microseconds, so it is done only when another device is current."""
+    if t.device.index == torch.cuda.current_device():
+        return entry(C.byref(args), _stream(t))
+    with torch.cuda.device(t.device):
+        return entry(C.byref(args), _stream(t))
+
+
 def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -333,8 +342,7 @@ def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, im
     a.mask_tile_live = ptr(mask.tile_live)
     if in_stride is not None:
         a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
-    with torch.cuda.device(q.device):
-        rc = lib.jvpfa_fwd(C.byref(a), _stream(q))
+    rc = _launch(q, lib.jvpfa_fwd, a)
     if rc == ERR_UNSUPPORTED and in_stride is not None:
         raise Unsupported("jvpfa_fwd cannot read this layout in place")
     check(rc, "jvpfa_fwd")
@@ -353,8 +361,7 @@ def mask_check(mask: "MaskSpec", shape) -> tuple[bool, bool]:
     a.n_b, a.n_h, a.n_rows, a.L = n_b, n_h, n_rows, L
     a.mask = mask.to_c()
     a.out = out.data_ptr()
-    with torch.cuda.device(t.device):
-        check(lib.jvpfa_mask_check(C.byref(a), _stream(t)), "jvpfa_mask_check")
+    check(_launch(t, lib.jvpfa_mask_check, a), "jvpfa_mask_check")
     flags = out.tolist()
     return all(flags[1:]), bool(flags[0] & 1), bool(flags[0] & 2)
 
@@ -383,8 +390,7 @@ def mask_tiles(mask: "MaskSpec", L: int):
     a.tile_live = tile_live.data_ptr()
     a.head_live = head_live.data_ptr()
     a.tile_live_t = tile_live_t.data_ptr()
-    with torch.cuda.device(t.device):
-        rc = lib.jvpfa_mask_tiles(C.byref(a), _stream(t))
+    rc = _launch(t, lib.jvpfa_mask_tiles, a)
     if rc == ERR_UNSUPPORTED:
         raise Unsupported("jvpfa_mask_tiles cannot read this mask layout")
     check(rc, "jvpfa_mask_tiles")
@@ -401,8 +407,7 @@ def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
     a.B, a.H, a.L, a.D = B, H, L, D
     a.o, a.to, a.go, a.gto = ptr(o), ptr(to), ptr(go), ptr(gto)
     a.mu, a.delta, a.eps, a.cterm = ptr(mu), ptr(delta), ptr(eps), ptr(cterm)
-    with torch.cuda.device(o.device):
-        check(lib.jvpfa_bwd_preprocess(C.byref(a), _stream(o)), "jvpfa_bwd_preprocess")
+    check(_launch(o, lib.jvpfa_bwd_preprocess, a), "jvpfa_bwd_preprocess")
 
 
 def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, mask: MaskSpec,
@@ -427,8 +432,7 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
         a.mask_tile_live, a.mask_tile_live_t = ptr(mask.tile_live), ptr(mask.tile_live_t)
     if in_stride is not None:
         a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
-    with torch.cuda.device(q.device):
-        rc = lib.jvpfa_bwd(C.byref(a), _stream(q))
+    rc = _launch(q, lib.jvpfa_bwd, a)
     if rc == ERR_UNSUPPORTED and in_stride is not None:
         raise Unsupported("jvpfa_bwd cannot read this layout in place")
     check(rc, "jvpfa_bwd")
@@ -456,5 +460,4 @@ def bwd_noalloc(q, k, v, tq, tk, tv, o, to, go, gto, lse, mu, dq, dk, dv, mask: 
     a.lse, a.mu = ptr(lse), ptr(mu)
     a.dq, a.dk, a.dv = ptr(dq), ptr(dk), ptr(dv)
     a.mask = mask.to_c()
-    with torch.cuda.device(q.device):
-        check(lib.jvpfa_bwd_noalloc(C.byref(a), _stream(q)), "jvpfa_bwd_noalloc")
+    check(_launch(q, lib.jvpfa_bwd_noalloc, a), "jvpfa_bwd_noalloc")

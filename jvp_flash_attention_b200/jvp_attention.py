@@ -431,7 +431,7 @@ class JVPAttn(Function):
     ) -> Tensor:
         """Primal-only attention (upstream: jvp_attention.py:2701-2752).  Returns O."""
         out = JVPAttn.apply(q, k, v, None, None, None, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
-                            USE_TMA)
+                            USE_TMA, True)  # every positional argument given: the quick signature binding applies
         a, _ = out
         return a
 
@@ -457,7 +457,7 @@ class JVPAttn(Function):
         _, k_t = fwAD.unpack_dual(k)
         _, v_t = fwAD.unpack_dual(v)
         out = JVPAttn.apply(q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
-                            USE_TMA)
+                            USE_TMA, True)
         a, _ = out
         return a
 
