@@ -289,6 +289,47 @@ struct MaskView {
         return true;
     }
   }
+  // allowed() and bias() for the two neighbouring keys j, j + 1 (j even) of query i at once.  When the key
+  // stride is 1 and the address allows it, the two mask bytes / bias elements come from one load.
+  __device__ __forceinline__ void pair(int i, int j, bool ok[2], float b[2]) const {
+    b[0] = b[1] = 0.f;
+    if ((kind == JVPFA_MASK_BOOL || kind == JVPFA_MASK_BIAS) && sj == 1 && i < L && j + 1 < L) {
+      const long long off = i * si + j;
+      if (kind == JVPFA_MASK_BOOL) {
+        const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + off;
+        if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) {
+          const uint32_t w = *reinterpret_cast<const uint16_t*>(p);
+          ok[0] = (w & 0xffu) != 0, ok[1] = (w >> 8) != 0;
+          return;
+        }
+      } else if (bias_dtype == JVPFA_FP32) {
+        const float* p = reinterpret_cast<const float*>(base) + off;
+        if ((reinterpret_cast<uintptr_t>(p) & 7u) == 0) {
+          const float2 v = *reinterpret_cast<const float2*>(p);
+          ok[0] = ok[1] = true, b[0] = v.x, b[1] = v.y;
+          return;
+        }
+      } else {
+        const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + off;
+        if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+          const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+          ok[0] = ok[1] = true;
+          if (bias_dtype == JVPFA_BF16) {
+            b[0] = __uint_as_float(w << 16), b[1] = __uint_as_float(w & 0xffff0000u);
+          } else {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w));
+            b[0] = v.x, b[1] = v.y;
+          }
+          return;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      ok[e] = allowed(i, j + e);
+      if (ok[e]) b[e] = bias(i, j + e);
+    }
+  }
   // Additive bias in natural units (0 unless kind == BIAS).  Only call for in-range (i, j).
   __device__ __forceinline__ float bias(int i, int j) const {
     if (kind != JVPFA_MASK_BIAS) return 0.f;

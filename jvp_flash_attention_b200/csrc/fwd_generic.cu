@@ -149,20 +149,27 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const jvpfa_fwd_args a
 #pragma unroll
     for (int nt = 0; nt < NS; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = (e < 2) ? row_lo : row_hi;
-        const int j = n0 + nt * 8 + 2 * t + (e & 1);
-        float x = s[nt][e] * scale_log2;
-        if (!full_tile) {
-          if (mv.allowed(i, j)) {
-            x += mv.bias(i, j) * kLog2e;
-          } else {
-            x = -INFINITY;
-            if constexpr (DUAL) ts[nt][e] = 0.f;
+      for (int r = 0; r < 2; ++r) {  // accumulator elements 2r, 2r+1: row_lo / row_hi, keys j, j + 1
+        const int i = r == 0 ? row_lo : row_hi;
+        const int j = n0 + nt * 8 + 2 * t;
+        bool ok[2] = {true, true};
+        float bias[2] = {0.f, 0.f};
+        if (!full_tile) mv.pair(i, j, ok, bias);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int e = 2 * r + c;
+          float x = s[nt][e] * scale_log2;
+          if (!full_tile) {
+            if (ok[c]) {
+              x += bias[c] * kLog2e;
+            } else {
+              x = -INFINITY;
+              if constexpr (DUAL) ts[nt][e] = 0.f;
+            }
           }
+          s[nt][e] = x;
+          mx[r] = fmaxf(mx[r], x);
         }
-        s[nt][e] = x;
-        mx[e >> 1] = fmaxf(mx[e >> 1], x);
       }
     }
     float alpha[2], m_use[2];
