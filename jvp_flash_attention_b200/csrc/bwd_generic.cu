@@ -544,15 +544,17 @@ __global__ void __launch_bounds__(128) bwd_dq_kernel(const jvpfa_bwd_args a) {
 #pragma unroll
     for (int nt = 0; nt < NK; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = row[e >> 1];
-        const int j = n0 + nt * 8 + 2 * t + (e & 1);
-        float v = 0.f;
-        if (mv.allowed(i, j)) {
-          const float x = p[nt][e] * scale_log2 + mv.bias(i, j) * kLog2e;
-          v = exp2f(x - lse[e >> 1]);
+      for (int r = 0; r < 2; ++r) {  // accumulator elements 2r, 2r+1: one query row, keys j and j + 1
+        bool ok[2];
+        float bias[2];
+        mv.pair(row[r], n0 + nt * 8 + 2 * t, ok, bias);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int e = 2 * r + c;
+          float v = 0.f;
+          if (ok[c]) v = exp2f(p[nt][e] * scale_log2 + bias[c] * kLog2e - lse[r]);
+          p[nt][e] = v;
         }
-        p[nt][e] = v;
       }
     }
 

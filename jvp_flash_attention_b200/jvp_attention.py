@@ -101,18 +101,20 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
     if m.dtype == torch.bool:
         m8 = m.view(torch.uint8) if m.is_contiguous() or m.stride(-1) == 1 else m.contiguous().view(torch.uint8)
         spec = _lib.MaskSpec(_lib.MASK_BOOL, m8, bstrides(m8))
-        try:
-            # one pass: which 128 x 64 tiles have a True (the forward steps over the others) and which heads do
-            spec.tile_live, head_live, spec.tile_live_t = _lib.mask_tiles(spec, N)
-            every_head_live = True
-            if verify:
+        every_head_live = True
+        if verify:
+            # One pass answers upstream's check and says which 128 x 64 tiles have a True at all; forward and
+            # backward step over the others.  (Without verification the mask is not looked at beforehand, so
+            # there is no block skipping either: whether it would pay is known only from the pass's counts.)
+            try:
+                spec.tile_live, head_live, spec.tile_live_t = _lib.mask_tiles(spec, N)
                 *heads, n_live = head_live.tolist()  # the one read-back
                 every_head_live = all(heads)
                 n_entries = spec.tile_live.numel() // (((N + 63) // 64 + 63) // 64)
                 if n_live > 0.85 * n_entries * ((N + 63) // 64):
                     spec.tile_live = spec.tile_live_t = None  # (nearly) every tile is live: the plain loops are quicker
-        except _lib.Unsupported:  # layout not readable as 16-byte pieces: no skipping, element-wise check
-            every_head_live = _lib.mask_check(spec, m8.shape)[0] if verify else True
+            except _lib.Unsupported:  # layout not readable as 16-byte pieces: no skipping, element-wise check
+                every_head_live = _lib.mask_check(spec, m8.shape)[0]
         assert every_head_live, "The attention mask cannot be all False for any head."
         if mh == 1 and mi == 1:
             # Candidate key-padding mask: valid keys form a prefix of each row.
