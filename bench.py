@@ -348,7 +348,7 @@ def run_ours(args, rank, world, local):
         n_pairs = w.attended_pairs()
         mma = 2.0 * D * n_pairs  # flops of one L x L x D product over the attended pairs
         kernels = [
-            {"name": "fwd_tc5_d64_kernel (fwd_dual)", "ms": br["fwd_dual"], "mma_executed": 6, "mma_algorithmic": 6},
+            {"name": "fwd_tc5_pair64_kernel (fwd_dual)", "ms": br["fwd_dual"], "mma_executed": 6, "mma_algorithmic": 6},
             {"name": "bwd_tc5_d64_kernel<own keys> (dK,dV)", "ms": br["bwd_dkdv_only"], "mma_executed": 8,
              "mma_algorithmic": None},
             {"name": "bwd_tc5_d64_kernel<own queries> (dQ)", "ms": br["bwd_dq_only"], "mma_executed": 7,
@@ -376,7 +376,7 @@ def run_ours(args, rank, world, local):
                     "path": "torch.func.jvp(JVPAttn.fwd_dual) + autograd.grad; pinned host inputs, double-buffered H2D"},
             "gpu_launches": 4 * args.steps,
             "roofline": {"bound": "tensor",
-                         "kernel": "jvpfa_fwd (fwd_tc5_d64_kernel)" if dom == "fwd_dual" else
+                         "kernel": "jvpfa_fwd (fwd_tc5_pair64_kernel)" if dom == "fwd_dual" else
                          "jvpfa_bwd (bwd_tc5_d64_kernel own-keys + own-queries launches, timed as one call; "
                          "10 algorithmic MMAs, 15 executed because both launches recompute the score tiles)",
                          "achieved": ach, "peak": peaks["burst"],

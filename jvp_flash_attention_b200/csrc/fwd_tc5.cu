@@ -531,9 +531,9 @@ bool fwd_tc5_eligible(const jvpfa_fwd_args& a) {
 }
 
 int launch_fwd_tc5(const jvpfa_fwd_args& a, cudaStream_t s) {
-  // Pipelined two-issuer variant (fwd_tc5_d64.cu); it takes the row maximum before scaling and
-  // therefore needs a positive softmax scale.
-  if (a.D == 64 && a.sm_scale > 0.f) return launch_fwd_tc5_d64(a, s);
+  // Query-tile-pair kernel (fwd_tc5_pair64.cu); it takes the row maximum before scaling and therefore
+  // needs a positive softmax scale.
+  if (a.D == 64 && a.sm_scale > 0.f) return launch_fwd_tc5_pair64(a, s);
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);
 }
 
