@@ -17,6 +17,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libjvpfa.so"
 BF16, FP16, FP32 = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_KVLEN, MASK_BOOL, MASK_BIAS = 0, 1, 2, 3, 4
 IMPL_AUTO, IMPL_GENERIC, IMPL_TCGEN05 = 0, 1, 2
+INDEX_MASKS = (MASK_NONE, MASK_CAUSAL, MASK_KVLEN)  # masks applied by index comparison inside the kernels
 IMPL_ONLY_DKDV, IMPL_ONLY_DQ = 0x100, 0x200  # measurement aids for jvpfa_bwd
 
 DTYPE_ENUM = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32}
@@ -136,6 +137,7 @@ class BwdArgs(C.Structure):
         ("in_stride", C.c_int64 * 3),
         ("mask_tile_live", C.c_void_p),
         ("mask_tile_live_t", C.c_void_p),
+        ("dq_accum", C.c_void_p),
     ]
 
 
@@ -411,8 +413,10 @@ def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
 
 
 def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, mask: MaskSpec,
-        sm_scale: float, impl: int = IMPL_AUTO, in_stride: tuple[int, int, int] | None = None) -> None:
-    """Launches jvpfa_bwd (gradients of <go,O> + <gto,tO> w.r.t. q, k, v)."""
+        sm_scale: float, impl: int = IMPL_AUTO, in_stride: tuple[int, int, int] | None = None,
+        dq_accum: torch.Tensor | None = None) -> None:
+    """Launches jvpfa_bwd (gradients of <go,O> + <gto,tO> w.r.t. q, k, v).  ``dq_accum``: optional fp32 scratch of
+    q's shape; with it the library may run its single-pass backward (see jvpfa_bwd_args.dq_accum)."""
     lib = load()
     B, H, L, D = q.shape
     a = BwdArgs()
@@ -432,6 +436,7 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
         a.mask_tile_live, a.mask_tile_live_t = ptr(mask.tile_live), ptr(mask.tile_live_t)
     if in_stride is not None:
         a.in_stride[0], a.in_stride[1], a.in_stride[2] = in_stride
+    a.dq_accum = ptr(dq_accum)
     rc = _launch(q, lib.jvpfa_bwd, a)
     if rc == ERR_UNSUPPORTED and in_stride is not None:
         raise Unsupported("jvpfa_bwd cannot read this layout in place")

@@ -582,7 +582,11 @@ bool bwd_tc5_eligible(const jvpfa_bwd_args& a) {
 }
 
 int launch_bwd_tc5(const jvpfa_bwd_args& a, cudaStream_t s) {
-  if (a.D == 64) return launch_bwd_tc5_d64(a, s);  // pipelined variant (bwd_tc5_d64.cu)
+  if (a.D == 64) {
+    // one pass over the score tiles when the caller gave the dQ accumulation buffer (bwd_tc5_fused64.cu)
+    if (bwd_tc5_fused64_eligible(a) && !(a.impl & (JVPFA_IMPL_ONLY_DKDV | JVPFA_IMPL_ONLY_DQ))) return launch_bwd_tc5_fused64(a, s);
+    return launch_bwd_tc5_d64(a, s);  // two pipelined launches (bwd_tc5_d64.cu)
+  }
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);
 }
 

@@ -42,6 +42,11 @@ _UPSTREAM_HEAD_DIMS = {16, 32, 64, 128, 256}
 # Tests flip it to cross-check the two families against each other.
 KERNEL_IMPL = _lib.IMPL_AUTO
 
+# The backward of head-dimension-64 16-bit calls with no / causal / key-padding masks runs as one pass that sums dQ
+# with floating-point reductions (reproducible to rounding).  False: always the two-launch kernels, whose results
+# are bitwise reproducible from run to run.
+SINGLE_PASS_BACKWARD = True
+
 
 def _unwrap(x):
     """Strips functorch wrappers so that ``data_ptr()`` is available (cf. jvp_attention.py:2846-2855)."""
@@ -184,13 +189,18 @@ def _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec: _lib.MaskSpe
     delta, eps, cterm = stats[0], stats[1], stats[2]
     _lib.bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm)
     dq, dk, dv = (torch.empty(q.shape, device=q.device, dtype=q.dtype) for _ in range(3))
+    # fp32 scratch for dQ: with it the library forms every score tile once (head dimension 64, 16-bit, index masks)
+    acc = None
+    if SINGLE_PASS_BACKWARD and q.shape[-1] == 64 and q.dtype != torch.float32 and spec.kind in _lib.INDEX_MASKS:
+        acc = torch.empty(q.shape, device=q.device, dtype=torch.float32)
     if st is not None:
         try:
-            _lib.bwd(*ins, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL, in_stride=st)
+            _lib.bwd(*ins, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL, in_stride=st,
+                     dq_accum=acc)
             return dq, dk, dv
         except _lib.Unsupported:
             ins = [None if t is None else t.contiguous() for t in ins]
-    _lib.bwd(*ins, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL)
+    _lib.bwd(*ins, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, spec, sm_scale, KERNEL_IMPL, dq_accum=acc)
     return dq, dk, dv
 
 

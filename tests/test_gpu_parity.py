@@ -81,8 +81,9 @@ def _mask(kind, B, H, L, dtype, seed):
     raise ValueError(kind)
 
 
-def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC):
-    """fwd + preprocess + bwd through the C ABI on cuda:0.  Returns o, to, lse, mu, dq, dk, dv."""
+def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC, single_pass=False):
+    """fwd + preprocess + bwd through the C ABI on cuda:0.  Returns o, to, lse, mu, dq, dk, dv.
+    single_pass: hand jvpfa_bwd the fp32 dQ accumulation buffer, which selects the one-pass backward."""
     dev = torch.device("cuda:0")
     B, H, L, D = q.shape
     cu = lambda x: None if x is None else x.to(dev).contiguous()  # noqa: E731
@@ -100,8 +101,9 @@ def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENE
         use_t = gto is not None
         _lib.bwd_preprocess(o, to if use_t else None, go, gto, mu if use_t else None, stats[0], stats[1], stats[2])
         dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        acc = torch.full(q.shape, float("nan"), device=dev, dtype=torch.float32) if single_pass else None
         _lib.bwd(q, k, v, tq if use_t else None, tk if use_t else None, tv if use_t else None, go, gto, lse,
-                 mu if use_t else None, stats[0], stats[1], stats[2], dq, dk, dv, spec, D**-0.5, impl)
+                 mu if use_t else None, stats[0], stats[1], stats[2], dq, dk, dv, spec, D**-0.5, impl, dq_accum=acc)
     torch.cuda.synchronize()
     return o, to, lse, mu, dq, dk, dv
 
@@ -229,6 +231,38 @@ def test_tcgen05_backward_many_items_per_cta(cot, kind, dt, B, H, L):
         assert torch.isfinite(a.float()).all(), name
         _close(a, b.float(), dtype, name)
     # one (batch, head) slice against the float64 oracle
+    sl = lambda x: None if x is None else x[B - 1:, H - 1:]  # noqa: E731
+    msl = None if mask is None else mask[min(B, mask.shape[0]) - 1:, min(H, mask.shape[1]) - 1:]
+    _, _, rdq, rdk, rdv = orc.grads_through_both(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), sl(go), sl(gto),
+                                                 attn_mask=msl, causal=causal)
+    _close(dq[B - 1:, H - 1:], rdq, dtype, "dq")
+    _close(dk[B - 1:, H - 1:], rdk, dtype, "dk")
+    _close(dv[B - 1:, H - 1:], rdv, dtype, "dv")
+
+
+SINGLE_PASS_CASES = [c for c in PERSISTENT_CASES if c[1] in ("none", "causal", "kvlen")] + [
+    # ragged lengths (last key tile and last query sub-tile partly out of range), one sub-tile, odd sub-tile counts
+    ("gt", "causal", "bf16", 2, 3, 34), ("both", "none", "fp16", 3, 2, 200), ("go", "kvlen", "bf16", 2, 2, 328),
+    ("gt", "none", "bf16", 1, 1, 64), ("both", "causal", "bf16", 5, 31, 448), ("gt", "kvlen", "fp16", 9, 17, 576),
+]
+
+
+@pytest.mark.parametrize("cot,kind,dt,B,H,L", SINGLE_PASS_CASES)
+def test_single_pass_backward_against_two_launch_and_oracle(cot, kind, dt, B, H, L):
+    """The one-pass backward (every score tile formed once, dQ summed into the caller's fp32 buffer) against the
+    two-launch tcgen05 kernels on the same inputs, and one (batch, head) slice against the float64 oracle.  The
+    accumulation buffer is handed over full of NaN: the library must not rely on its contents."""
+    dtype = DT[dt]
+    q, k, v, tq, tk, tv, go, gto = _make(B, H, L, 64, dtype, seed=B + L)
+    go = go if cot in ("go", "both") else None
+    gto = gto if cot in ("gt", "both") else None
+    mask, causal = _mask(kind, B, H, L, dtype, seed=L)
+    *_, dq, dk, dv = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_TCGEN05, single_pass=True)
+    assert _lib.device_status() == 0, "a bounded wait inside the tcgen05 kernel gave up"
+    *_, dq2, dk2, dv2 = _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_TCGEN05)
+    for name, a, b in (("dq", dq, dq2), ("dk", dk, dk2), ("dv", dv, dv2)):
+        assert torch.isfinite(a.float()).all(), name
+        _close(a, b.float(), dtype, name)
     sl = lambda x: None if x is None else x[B - 1:, H - 1:]  # noqa: E731
     msl = None if mask is None else mask[min(B, mask.shape[0]) - 1:, min(H, mask.shape[1]) - 1:]
     _, _, rdq, rdk, rdv = orc.grads_through_both(sl(q), sl(k), sl(v), sl(tq), sl(tk), sl(tv), sl(go), sl(gto),
