@@ -97,6 +97,29 @@ def make_workload(name: str, B: int | None = None, H: int | None = None, L: int 
     return w
 
 
+def make_workload_on_device(name: str, heads: tuple[int, int], device) -> Workload:
+    """The (batch*head) units ``heads=(start, stop)`` of a configuration drawn on the GPU itself, one generator per
+    unit seeded ``seed*100003 + bh``: a rank produces its shard of the long-sequence configuration without a host
+    copy, and any other rank can reproduce one of those units bit for bit on a GPU of the same kind.  (The values
+    differ from ``make_workload(..., heads=...)``, which draws on the CPU.)  Tensors: q, k, v, tq, tk, tv, w1, w2 of
+    shape (1, stop-start, L, D)."""
+    dtype, b, h, l, d, causal, mask_kind, seed, tstd, loss = SPECS[name]
+    lo, hi = heads
+    w = Workload(name, dtype, 1, hi - lo, l, d, causal, mask_kind, seed, tstd, loss)
+    names = ["q", "k", "v", "tq", "tk", "tv", "w1", "w2"]
+    out = {n: torch.empty((1, hi - lo, l, d), device=device, dtype=dtype) for n in names}
+    g = torch.Generator(device=device)
+    for j, bh in enumerate(range(lo, hi)):
+        g.manual_seed(seed * 100003 + bh)
+        for n in names:
+            x = torch.randn((l, d), generator=g, device=device, dtype=torch.float32)
+            if n in ("tq", "tk", "tv"):
+                x = x * tstd
+            out[n][0, j] = x.to(dtype)
+    w.tensors = out
+    return w
+
+
 def shard_range(total: int, rank: int, world: int) -> tuple[int, int]:
     """Contiguous slice [start, stop) of ``total`` (batch*head) units owned by ``rank``.
 
