@@ -202,7 +202,9 @@ int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
  * given), which the row reductions read.  The scratch is a fixed device array of
  * 3 * JVPFA_NOALLOC_MAX_ROWS floats (6 MiB) that every GPU loading the library holds until
  * process exit.  Limits and rules:
- *   - B*H*L <= JVPFA_NOALLOC_MAX_ROWS, otherwise JVPFA_ERR_TOO_LARGE and nothing is launched;
+ *   - B*H*L <= JVPFA_NOALLOC_MAX_ROWS, otherwise JVPFA_ERR_TOO_LARGE; this and every argument check of
+ *     jvpfa_bwd_preprocess and jvpfa_bwd come before the first launch, so a refused call launches nothing and
+ *     leaves the array as it was;
  *   - all calls on one device share the array, so calls that can overlap on the GPU race:
  *     issue them on one stream (or otherwise serialise them);
  *   - the array keeps the last call's contents; no part of it needs to be zero beforehand;

@@ -28,9 +28,11 @@ FP32_TF32 = 3  # JVPFA_FP32_TF32: fp32 tensors, products as one TF32 MMA
 FP32_PRECISION = "3xtf32"
 
 
-def compute_enum(t: torch.Tensor) -> int:
-    """jvpfa_dtype for the arithmetic on tensors like ``t``."""
-    if t.dtype == torch.float32 and FP32_PRECISION == "tf32":
+def compute_enum(t: torch.Tensor, fp32_mode: str | None = None) -> int:
+    """jvpfa_dtype for the arithmetic on tensors like ``t``.  ``fp32_mode``: the precision recorded when the call's
+    forward ran (so that a backward recomputes the scores exactly as the forward formed them); None = the current
+    process-wide setting."""
+    if t.dtype == torch.float32 and (fp32_mode or FP32_PRECISION) == "tf32":
         return FP32_TF32
     return DTYPE_ENUM[t.dtype]
 
@@ -266,7 +268,7 @@ class MaskSpec:
     bias, or int32 kv_len) and ``strides`` are the broadcast element strides of a (B,H,L,L) view.
     """
 
-    __slots__ = ("kind", "tensor", "strides", "bias_dtype", "tile_live", "tile_live_t")
+    __slots__ = ("kind", "tensor", "strides", "bias_dtype", "tile_live", "tile_live_t", "fp32_mode")
 
     def __init__(self, kind=MASK_NONE, tensor=None, strides=(0, 0, 0, 0), bias_dtype=FP32):
         self.kind = kind
@@ -275,6 +277,7 @@ class MaskSpec:
         self.bias_dtype = bias_dtype
         self.tile_live = None  # MASK_BOOL: bitmap from mask_tiles(), lets the forward step over dead tiles
         self.tile_live_t = None  # ... and its transpose (per 128-key tile), for the backward launch that owns keys
+        self.fp32_mode = None  # fp32 precision the forward of this call ran under ("3xtf32" / "tf32"); None = current
 
     def to_c(self) -> Mask:
         m = Mask()
@@ -333,7 +336,7 @@ def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, mask: MaskSpec, sm_scale: float, im
     B, H, L, D = q.shape
     a = FwdArgs()
     a.struct_size = C.sizeof(FwdArgs)
-    a.dtype = compute_enum(q)
+    a.dtype = compute_enum(q, mask.fp32_mode)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.impl = impl
     a.sm_scale = sm_scale
@@ -399,13 +402,13 @@ def mask_tiles(mask: "MaskSpec", L: int):
     return tile_live, head_live, tile_live_t
 
 
-def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm) -> None:
+def bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm, fp32_mode: str | None = None) -> None:
     """Launches jvpfa_bwd_preprocess (row reductions delta / eps / cterm)."""
     lib = load()
     B, H, L, D = o.shape
     a = PreArgs()
     a.struct_size = C.sizeof(PreArgs)
-    a.dtype = compute_enum(o)
+    a.dtype = compute_enum(o, fp32_mode)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.o, a.to, a.go, a.gto = ptr(o), ptr(to), ptr(go), ptr(gto)
     a.mu, a.delta, a.eps, a.cterm = ptr(mu), ptr(delta), ptr(eps), ptr(cterm)
@@ -421,7 +424,7 @@ def bwd(q, k, v, tq, tk, tv, go, gto, lse, mu, delta, eps, cterm, dq, dk, dv, ma
     B, H, L, D = q.shape
     a = BwdArgs()
     a.struct_size = C.sizeof(BwdArgs)
-    a.dtype = compute_enum(q)
+    a.dtype = compute_enum(q, mask.fp32_mode)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.impl = impl
     a.sm_scale = sm_scale
@@ -455,7 +458,7 @@ def bwd_noalloc(q, k, v, tq, tk, tv, o, to, go, gto, lse, mu, dq, dk, dv, mask: 
     B, H, L, D = q.shape
     a = BwdNoAllocArgs()
     a.struct_size = C.sizeof(BwdNoAllocArgs)
-    a.dtype = compute_enum(q)
+    a.dtype = compute_enum(q, mask.fp32_mode)
     a.B, a.H, a.L, a.D = B, H, L, D
     a.impl = impl
     a.sm_scale = sm_scale

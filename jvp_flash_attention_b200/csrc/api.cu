@@ -106,6 +106,7 @@ static int validate_bwd(const jvpfa_bwd_args* a) {
   const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->go, a->gto, a->dq, a->dk, a->dv};
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
+  if (a->dq_accum && !aligned16(a->dq_accum)) return JVPFA_ERR_ALIGN;
   if (impl_family(a->impl) > JVPFA_IMPL_TCGEN05 || (a->impl & ~0x3ff) != 0) return JVPFA_ERR_UNSUPPORTED;
   rc = check_strides(a->in_stride);
   if (rc) return rc;
@@ -123,6 +124,25 @@ static int validate_pre(const jvpfa_pre_args* a) {
   const void* ptrs[] = {a->o, a->to, a->go, a->gto};
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
+  return JVPFA_OK;
+}
+
+// Everything jvpfa_bwd_preprocess / jvpfa_bwd check before they launch, without launching: used by callers inside
+// the library that issue several launches and must not have run any of them when a later one is refused.
+int check_pre_request(const jvpfa_pre_args* a) {
+  const int rc = validate_pre(a);
+  return rc ? rc : check_arch();
+}
+
+int check_bwd_request(const jvpfa_bwd_args* a) {
+  int rc = validate_bwd(a);
+  if (rc) return rc;
+  rc = check_arch();
+  if (rc) return rc;
+  const bool tc5 = bwd_tc5_eligible(*a);
+  const int fam = impl_family(a->impl);
+  if (fam == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
+  if (has_strides(a->in_stride) && !(tc5 && fam != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
   return JVPFA_OK;
 }
 
@@ -159,23 +179,17 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
 }
 
 int jvpfa_bwd_preprocess(const jvpfa_pre_args* a, void* stream) {
-  int rc = validate_pre(a);
-  if (rc) return rc;
-  rc = check_arch();
+  const int rc = check_pre_request(a);
   if (rc) return rc;
   return launch_pre(*a, static_cast<cudaStream_t>(stream));
 }
 
 int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
-  int rc = validate_bwd(a);
-  if (rc) return rc;
-  rc = check_arch();
+  const int rc = check_bwd_request(a);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc5 = bwd_tc5_eligible(*a);
   const int fam = impl_family(a->impl);
-  if (fam == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
-  if (has_strides(a->in_stride) && !(tc5 && fam != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
   if (tc5 && fam != JVPFA_IMPL_GENERIC) return launch_bwd_tc5(*a, s);
   return launch_bwd_generic(*a, s);
 }

@@ -86,8 +86,6 @@ extern "C" int jvpfa_bwd_noalloc(const jvpfa_bwd_noalloc_args* a, void* stream) 
   p.go = a->go, p.gto = a->gto;
   p.mu = a->gto ? a->mu : nullptr;
   p.delta = delta, p.eps = eps, p.cterm = cterm;
-  rc = jvpfa_bwd_preprocess(&p, stream);
-  if (rc) return rc;
 
   jvpfa_bwd_args g{};
   g.struct_size = (int32_t)sizeof(g);
@@ -102,5 +100,12 @@ extern "C" int jvpfa_bwd_noalloc(const jvpfa_bwd_noalloc_args* a, void* stream) 
   g.delta = delta, g.eps = eps, g.cterm = cterm;
   g.dq = a->dq, g.dk = a->dk, g.dv = a->dv;
   g.mask = a->mask;
+  // Both requests are checked in full before the first launch: a refused call leaves the shared array untouched.
+  rc = check_pre_request(&p);
+  if (rc) return rc;
+  rc = check_bwd_request(&g);
+  if (rc) return rc;
+  rc = jvpfa_bwd_preprocess(&p, stream);
+  if (rc) return rc;
   return jvpfa_bwd(&g, stream);
 }

@@ -71,7 +71,7 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
   // The own-queries launch that follows reads nothing this kernel writes: it is launched with programmatic
   // stream serialization and fills the SMs as this kernel's last CTAs leave them.
   if constexpr (OWN_KEYS) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (*(volatile int*)status != 0) return;
+  const bool dead_on_entry = *(volatile int*)status != 0;  // an earlier bounded wait gave up
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -116,6 +116,24 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
     n_tiles = (n_end + BL - 1) / BL;
   }
   const size_t stat_off = (size_t)bh * L;
+
+  // NaN into this CTA's output rows: the results of this launch are not to be trusted
+  auto poison = [&]() {
+    if (tid < OWN && own0 + tid < L) {
+      if constexpr (OWN_KEYS) {
+        poison_row<T>(a.dk, stat_off + own0 + tid, D);
+        poison_row<T>(a.dv, stat_off + own0 + tid, D);
+      } else {
+        poison_row<T>(a.dq, stat_off + own0 + tid, D);
+      }
+    }
+  };
+  if (dead_on_entry) {
+    poison();
+    // the stream's next kernel must still be ordered after the launch this one overlaps
+    if constexpr (!OWN_KEYS) asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(own_full, 1);
@@ -473,8 +491,13 @@ bwd_tc5_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdMaps maps, int
     }
   }
 
+  // The own-queries launch may have started while the own-keys launch before it was still running (programmatic
+  // stream serialization).  Whatever follows on the stream is ordered after THIS grid only, so this grid must not
+  // complete before that one has: wait for it here, after the work.
+  if constexpr (!OWN_KEYS) asm volatile("griddepcontrol.wait;" ::: "memory");
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag != 0) poison();
   if (warp == 0) {
     if (*abort_flag != 0) {
       const long long t0 = clock64();

@@ -95,30 +95,6 @@ struct Bwd64Cfg {
 
 __device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
 
-#ifdef JVPFA_TC5_PROFILE
-// Event trace of CTA 0 (experiment flag): clock64 at fixed points of sub-tiles [G0, G0 + W).
-#ifndef JVPFA_TRACE_G0
-#define JVPFA_TRACE_G0 16
-#endif
-constexpr int kTraceG0 = JVPFA_TRACE_G0, kTraceW = 24, kTraceEv = 20;
-__device__ long long g_bwd_trace[2][kTraceW * kTraceEv];
-#define TRACE(g, ev)                                                                 \
-  do {                                                                               \
-    if (blockIdx.x == 0 && (g) >= kTraceG0 && (g) < kTraceG0 + kTraceW)              \
-      g_bwd_trace[OWN_KEYS ? 0 : 1][((g) - kTraceG0) * kTraceEv + (ev)] = clock64(); \
-  } while (0)
-// Per-item time line of three CTAs: [0] kernel start, [1 + 2k] item k's first s_full seen, [2 + 2k] item k stored.
-__device__ long long g_bwd_items[2][3][24];
-#define ITEM_TRACE(idx)                                                                           \
-  do {                                                                                            \
-    const int slot_ = blockIdx.x == 0 ? 0 : (blockIdx.x == 73 ? 1 : (blockIdx.x == 147 ? 2 : -1)); \
-    if (slot_ >= 0 && (idx) < 24) g_bwd_items[OWN_KEYS ? 0 : 1][slot_][(idx)] = clock64();        \
-  } while (0)
-#else
-#define TRACE(g, ev)
-#define ITEM_TRACE(idx)
-#endif
-
 // One work item of the persistent loop.
 struct BwdItem {
   int bh, b, h, own0, loop_begin, n_sub;
@@ -166,7 +142,7 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
   // launched with programmatic stream serialization and may take over each SM as soon as this
   // kernel's CTA there has exited (both need a whole SM): the tails of the two launches overlap.
   if constexpr (OWN_KEYS) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (*(volatile int*)status != 0) return;
+  const bool dead_on_entry = *(volatile int*)status != 0;  // an earlier bounded wait gave up
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -283,8 +259,30 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     return n_valid;
   };
 
+  // NaN into the output rows that this CTA's items own: this launch's results are not to be trusted
+  auto poison = [&]() {
+    BwdItem it;
+    for (int k = 0; k < k_max; ++k) {
+      if (!get_item(k, it)) continue;
+      const int i = it.own0 + tid;
+      if (tid < OWN && i < L) {
+        if constexpr (OWN_KEYS) {
+          poison_row<T>(a.dk, (size_t)it.bh * L + i, D);
+          poison_row<T>(a.dv, (size_t)it.bh * L + i, D);
+        } else {
+          poison_row<T>(a.dq, (size_t)it.bh * L + i, D);
+        }
+      }
+    }
+  };
+  if (dead_on_entry) {
+    poison();
+    // the stream's next kernel must still be ordered after the launch this one overlaps
+    if constexpr (!OWN_KEYS) asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
+
   if (tid == 0) {
-    ITEM_TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(loop_full + s, 1);
       mbar_init(stat_full + s, 1);
@@ -409,7 +407,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             continue;
           }
           const int l0 = sub_l0<BL>(it, s);
-          if (lane == 0) TRACE(g, 18);
           if (lane == 0) {
             unsigned char* base = sLoop + st * C::STAGE_BYTES;
             mbar_expect_tx(loop_full + st, C::STAGE_BYTES);
@@ -527,13 +524,11 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             }
             cf.advance(2);
           }
-          if (!part_b) TRACE(g, 17);
           if (!mbar_wait_u32(bar_loop_full + cs.st_bar, cs.st_par, ab, kAbortBwdLoopFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          TRACE(g, r * 4 + (part_b ? 2 : 0));
           const uint32_t lp = ring_lo + cs.st_tile;  // tile slot 0 of the stage
           const uint32_t acc = tmem + cs.buf_col;
           if (!part_b) {
@@ -571,7 +566,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             }
           }
           tc_commit_u32(bar_s_full + cs.sf_bar);
-          TRACE(g, r * 4 + (part_b ? 3 : 1));
           cs.advance(2);
         }
         if (!ok) break;
@@ -610,7 +604,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             break;
           }
           tc_fence_after();
-          TRACE(g, second ? 10 : 8);
           const uint32_t lp = ring_lo + co.st_tile;
           const uint32_t opnd = tmem + co.buf_col;
           const uint32_t acc = s > 0;
@@ -630,7 +623,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             if constexpr (HAS_GT) outer(oc, opnd + C::OFF_E, lp + C::SLOT_TK * LOOP16, 1);              // dQ += gtS tK
           }
           tc_commit_u32(bar_loop_empty + co.st_bar);
-          TRACE(g, second ? 11 : 9);
           co.advance(1);
         }
         if (ok) tc_commit(done + kact % C::N_OUT_BUF);
@@ -775,8 +767,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           break;
         }
         tc_fence_after();
-        if (row == 0) TRACE(g, 12);
-        if (tid == 128 && (g & 7) == 0) ITEM_TRACE(1 + g / 8);
         // Masking by index comparison; columns outside [col_lo, col_hi) get p = 0.
         //   own keys   : (key j = own_idx, query i = l0 + col) is dead if j >= n_valid, or causal and j > i
         //   own queries: (query i = own_idx, key j = l0 + col) is dead if j >= n_valid, or causal and j > i
@@ -822,7 +812,6 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
             tmem_ld16(tbuf + C::OFF_E + 16 * c, ev);
           }
           tmem_wait_ld();
-          if (row == 0 && c == 0) TRACE(g, 13);
           const int lo_c = col_lo - 16 * c, hi_c = col_hi - 16 * c;  // live columns of this half: [lo_c, hi_c)
           const uint32_t live_c = live >> (16 * c);
           uint32_t pk_gs[8], pk_gt[8], pk_av[8], pk_p[8];
@@ -873,11 +862,9 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
           }
           if constexpr (OWN_KEYS && HAS_GO) tmem_st8(tbuf + C::OFF_S + 8 * c, pk_p);
         }
-        if (row == 0) TRACE(g, 14);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full + buf);
-        if (row == 0) TRACE(g, 15);
         if (pend_kact >= 0 && !epilogue()) break;
       }
       if (!alive) break;
@@ -891,8 +878,13 @@ bwd_tc5_d64_kernel(const jvpfa_bwd_args a, const __grid_constant__ Bwd64Maps map
     if (alive && pend_kact >= 0) epilogue();
   }
 
+  // The own-queries launch may have started while the own-keys launch before it was still running (programmatic
+  // stream serialization).  Whatever follows on the stream is ordered after THIS grid only, so this grid must not
+  // complete before that one has: wait for it here, after the work, where the tails of the two launches still overlap.
+  if constexpr (!OWN_KEYS) asm volatile("griddepcontrol.wait;" ::: "memory");
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag != 0) poison();
   if (warp == 0) {
     if (*abort_flag != 0) {
       const long long t0 = clock64();
@@ -1002,16 +994,6 @@ static int launch_t64(const jvpfa_bwd_args& a, cudaStream_t s) {
 }
 
 }  // namespace tc5
-
-#ifdef JVPFA_TC5_PROFILE
-extern "C" int jvpfa_debug_read_items(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, tc5::g_bwd_items, sizeof(long long) * 2 * 3 * 24);
-}
-extern "C" int jvpfa_debug_read_trace(long long* out, int which) {
-  return (int)cudaMemcpyFromSymbol(out, tc5::g_bwd_trace, sizeof(long long) * tc5::kTraceW * tc5::kTraceEv,
-                                   sizeof(long long) * tc5::kTraceW * tc5::kTraceEv * which);
-}
-#endif
 
 int launch_bwd_tc5_d64(const jvpfa_bwd_args& a, cudaStream_t s) {
   return a.dtype == JVPFA_BF16 ? tc5::launch_t64<__nv_bfloat16>(a, s) : tc5::launch_t64<__half>(a, s);

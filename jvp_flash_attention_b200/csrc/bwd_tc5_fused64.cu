@@ -97,7 +97,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
   using C = BwdFCfg<HAS_GO, HAS_GT>;
   constexpr int D = 64, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES;
 
-  if (*(volatile int*)status != 0) return;
+  const bool dead_on_entry = *(volatile int*)status != 0;  // an earlier bounded wait gave up
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -160,6 +160,25 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     }
     return n_valid;
   };
+
+  // NaN into the rows of dK, dV and of the dQ accumulator that this CTA's items own: this launch's results are
+  // not to be trusted
+  auto poison = [&]() {
+    FItem it;
+    for (int k = 0; k < k_max; ++k) {
+      if (!get_item(k, it)) continue;
+      const int i = it.own0 + tid;
+      if (tid < OWN && i < L) {
+        poison_row<T>(a.dk, (size_t)it.bh * L + i, D);
+        poison_row<T>(a.dv, (size_t)it.bh * L + i, D);
+        dq_acc[((size_t)it.bh * L + i) * D] = poison_f32();
+      }
+    }
+  };
+  if (dead_on_entry) {
+    poison();
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(own_full, 1);
@@ -611,6 +630,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
 
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag != 0) poison();
   if (warp == 0) {
     if (*abort_flag != 0) {
       // Something gave up: give copies and MMAs that may still be in flight time to land before the TMEM

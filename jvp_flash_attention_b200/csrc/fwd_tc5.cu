@@ -78,7 +78,7 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   constexpr int KSTEPS_N = BN / 16;  // contraction steps over the keys of a tile
   constexpr int HALVES = D / 64;     // 64-column TMA boxes per row
 
-  if (*(volatile int*)&g_tc5_status != 0) return;  // an earlier CTA gave up: do nothing
+  const bool dead_on_entry = *(volatile int*)&g_tc5_status != 0;  // an earlier bounded wait gave up
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -112,6 +112,15 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   int n_end = n_valid;
   if (causal) n_end = min(n_end, m0 + BM);
   const int n_tiles = (n_end + BN - 1) / BN;
+
+  // lse = NaN for this CTA's rows: the results of this launch are not to be trusted
+  auto poison = [&]() {
+    if (tid < BM && m0 + tid < L) a.lse[(size_t)bh * L + m0 + tid] = poison_f32();
+  };
+  if (dead_on_entry) {
+    poison();
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(q_full, 1);
@@ -414,6 +423,7 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   // ---- teardown: every thread arrives here, with or without an abort ----
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag != 0) poison();
   if (warp == 0) {
     if (*abort_flag != 0) {
       // Something gave up: give copies and MMAs that may still be in flight time to land before

@@ -144,7 +144,7 @@ fwd_tc5_pair64_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPairMap
   using C = FwdPairCfg<DUAL>;
   constexpr int D = 64, BM = C::BM, BN = C::BN, STAGES = C::STAGES;
 
-  if (*(volatile int*)status != 0) return;
+  const bool dead_on_entry = *(volatile int*)status != 0;  // an earlier bounded wait gave up
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -229,6 +229,20 @@ fwd_tc5_pair64_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPairMap
     it.n_load = max(it.nt0, it.nt1);
     return true;
   };
+
+  // lse = NaN for every row of this CTA's items: the results of this launch are not to be trusted
+  auto poison = [&]() {
+    PairItem it;
+    for (int k = 0; k < k_max; ++k) {
+      if (!get_item(k, it)) continue;
+      const int i = it.m0 + tid;
+      if (tid < 2 * BM && i < L) a.lse[(size_t)it.bh * L + i] = poison_f32();
+    }
+  };
+  if (dead_on_entry) {
+    poison();
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(q_full, 1);
@@ -747,6 +761,7 @@ fwd_tc5_pair64_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPairMap
   }
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag != 0) poison();
   if (warp == 0) {
     if (*abort_flag != 0) {
       // Something gave up: give copies and MMAs that may still be in flight time to land before the TMEM

@@ -356,6 +356,17 @@ __device__ __forceinline__ void umma_ts_lo_dyn(uint32_t d_tmem, uint32_t a_tmem,
       : "memory");
 }
 
+// Outputs of a launch that ran after a bounded wait gave up (or of the launch that gave up) are undefined.  To make
+// that visible without a synchronisation, such a CTA stamps NaN into the statistics / leading elements of the rows
+// it owns: every later reduction over the outputs, and every backward that reads lse, then carries NaN.
+__device__ __forceinline__ float poison_f32() { return __uint_as_float(0x7fc00000u); }
+template <typename T>
+__device__ __forceinline__ void poison_row(void* base, size_t row, int D) {  // first 16 bytes of a (.., D) row
+  uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<T*>(base) + row * D);
+  *p = sizeof(T) == 2 ? make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu)
+                      : make_uint4(0x7fc00000u, 0x7fc00000u, 0x7fc00000u, 0x7fc00000u);
+}
+
 template <int I>
 struct IntC {
   static constexpr int value = I;

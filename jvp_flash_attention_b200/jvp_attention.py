@@ -48,6 +48,35 @@ KERNEL_IMPL = _lib.IMPL_AUTO
 SINGLE_PASS_BACKWARD = True
 
 
+def is_hip() -> bool:
+    """Upstream's backend probe (jvp_attention.py:54-59).  This build has one target, NVIDIA sm_100a."""
+    return False
+
+
+def is_cuda() -> bool:
+    """True when a CUDA device is present (upstream: jvp_attention.py:62-67)."""
+    return torch.cuda.is_available()
+
+
+def is_blackwell() -> bool:
+    """True on a compute-capability-10 device, the only kind these kernels run on (upstream: jvp_attention.py:86-91)."""
+    try:
+        return is_cuda() and torch.cuda.get_device_capability()[0] == 10
+    except Exception:  # noqa: BLE001
+        return False
+
+
+def supports_host_descriptor() -> bool:
+    """Upstream asks this before building host-side TMA descriptors (jvp_attention.py:70-75); here every tcgen05 kernel
+    takes host-encoded tensor maps, so the answer is that of is_blackwell()."""
+    return is_blackwell()
+
+
+def supports_tma() -> bool:
+    """See supports_host_descriptor (upstream: jvp_attention.py:78-83)."""
+    return is_blackwell()
+
+
 def _unwrap(x):
     """Strips functorch wrappers so that ``data_ptr()`` is available (cf. jvp_attention.py:2846-2855)."""
     fc = torch._C._functorch
@@ -71,7 +100,8 @@ def set_fp32_precision(mode: str) -> str:
     ``"3xtf32"`` (default): every product as three TF32 MMAs on a hi/lo split, about 1e-6 relative error.
     ``"tf32"``: one TF32 MMA per product, about 5e-4 -- what upstream's fp32 path computes (its ``tl.dot`` calls
     run on TF32 tensor cores, jvp_attention.py:233-236; its fp32 tolerance is 2.35e-2), about 2.5x faster.
-    Forward and backward of one call must run under the same mode."""
+    A call's backward (and double backward) runs at the precision its forward ran at: the mode is recorded with the
+    call, so changing it in between affects later forwards only."""
     if mode not in ("3xtf32", "tf32"):
         raise ValueError("fp32 precision is '3xtf32' or 'tf32'")
     prev, _lib.FP32_PRECISION = _lib.FP32_PRECISION, mode
@@ -187,7 +217,7 @@ def _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec: _lib.MaskSpe
     Z, H, N, _ = q.shape
     stats = torch.empty((3, Z, H, N), device=q.device, dtype=torch.float32)
     delta, eps, cterm = stats[0], stats[1], stats[2]
-    _lib.bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm)
+    _lib.bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm, spec.fp32_mode)
     dq, dk, dv = (torch.empty(q.shape, device=q.device, dtype=q.dtype) for _ in range(3))
     # fp32 scratch for dQ: with it the library forms every score tile once (head dimension 64, 16-bit, index masks)
     acc = None
@@ -402,6 +432,9 @@ class JVPAttn(Function):
         tq, tk, tv = (None if t is None else t.to(q.dtype) for t in tangents)
 
         spec, MASK_TYPE, mask_tensor = classify_mask(attn_mask, causal, Z, H, N_CTX, q.dtype, verify_attn_mask)
+        # the backward of this call recomputes the scores at the precision they had here, whatever the process-wide
+        # setting is by then
+        spec.fp32_mode = _lib.FP32_PRECISION
         o, o_t, M, mu = _launch_fwd(qc, kc, vc, tq, tk, tv, spec, sm_scale)
         grid = JVPAttn.Grid((N_CTX + 63) // 64, Z * H, 1)
         return JVPAttn.FwdOut(
@@ -482,6 +515,11 @@ class JVPAttn(Function):
             raise RuntimeError(
                 "JVPAttn.jvp needs tangents at forward time: call JVPAttn.fwd_dual (or pass q_t, k_t, v_t to apply)"
             )
+        # Nobody can ask for a gradient of the tangent when no input takes part in a graph: hand the kernel's tangent
+        # over as it is and skip the bridging node.  (Looked up on the unwrapped tensors: inside torch.func.jvp the
+        # wrappers do not say.)
+        if not any(x is not None and _unwrap(x).requires_grad for x in (q, k, v, q_t, k_t, v_t, gq, gk, gv)):
+            return JVPAttn.JVPOut(o_t, None)
         tq = gq if gq is not None else (q_t if q_t is not None else torch.zeros_like(q))
         tk = gk if gk is not None else (k_t if k_t is not None else torch.zeros_like(k))
         tv = gv if gv is not None else (v_t if v_t is not None else torch.zeros_like(v))

@@ -491,7 +491,7 @@ def test_config2_full_size_sampled_heads_and_linearity():
     loss = ((to.float() - t["target"].float()) ** 2).mean()
     g = torch.autograd.grad(loss, a)
     n = to.numel()
-    for (b, h) in ((0, 0), (3, 15)):
+    for (b, h) in ((0, 0), (0, 9), (1, 3), (1, 14), (2, 0), (2, 7), (3, 5), (3, 15)):
         sl = lambda x: x[b:b + 1, h:h + 1]  # noqa: E731
         cpu = {k_: sl(v_) for k_, v_ in w.tensors.items()}
         ro, rto = orc.sdpa_jvp(cpu["q"], cpu["k"], cpu["v"], cpu["tq"], cpu["tk"], cpu["tv"], causal=True)
@@ -509,6 +509,23 @@ def test_config2_full_size_sampled_heads_and_linearity():
                              tuple(x.detach() for x in a), (2 * t["tq"], 2 * t["tk"], 2 * t["tv"]))
     assert torch.equal(o2, o.detach())
     assert (to2.float() - 2 * to.detach().float()).abs().max().item() <= 2e-2
+    # Every one of the 64 heads, all five results: the tcgen05 kernels of the benchmark shape (whose persistent work
+    # lists depend on the shape) against the register-tiled family, through the C ABI, with the cotangent of the loss.
+    gto = (2.0 * (to.detach().float() - t["target"].float()) / n).to(torch.bfloat16)
+    c = w.tensors
+    res = {}
+    for impl, single in ((_lib.IMPL_TCGEN05, True), (_lib.IMPL_TCGEN05, False), (_lib.IMPL_GENERIC, False)):
+        res[(impl, single)] = _run_kernels(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], None, gto.cpu(), None, True,
+                                           impl=impl, single_pass=single)
+        assert _lib.device_status() == 0
+    ref = res[(_lib.IMPL_GENERIC, False)]
+    for key in ((_lib.IMPL_TCGEN05, True), (_lib.IMPL_TCGEN05, False)):
+        got = res[key]
+        for idx, nme in ((0, "O"), (1, "tO")):
+            _close(got[idx], ref[idx].float(), torch.bfloat16, nme)
+        for idx, nme in ((4, "dq"), (5, "dk"), (6, "dv")):
+            e = orc.rel_err(got[idx], ref[idx].float())
+            assert e < 3e-2, f"{nme} all heads, tcgen05 {key} vs register-tiled: rel {e:.3e}"
 
 
 def test_config3_full_size_keypad_sampled_heads():
@@ -622,12 +639,13 @@ def test_config5_shard_long_sequence_sampled_head():
     o, to = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a), (t["tq"], t["tk"], t["tv"]))
     g = torch.autograd.grad((o.float() * t["w1"].float()).sum() + (to.float() * t["w2"].float()).sum(), a)
     assert _lib.device_status() == 0
-    c = {k_: v_[:, :1] for k_, v_ in w.tensors.items()}
-    ro, rto, rdq, rdk, rdv = orc.grads_through_both(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], c["w1"], c["w2"])
-    _close(o[:, :1], ro, torch.bfloat16, "O")
-    _close(to[:, :1], rto, torch.bfloat16, "tO")
-    for x, r_, nme in zip(g, (rdq, rdk, rdv), ("dq", "dk", "dv")):
-        _close(x[:, :1], r_, torch.bfloat16, nme)
+    for hd in (0, 3):
+        c = {k_: v_[:, hd:hd + 1] for k_, v_ in w.tensors.items()}
+        ro, rto, rdq, rdk, rdv = orc.grads_through_both(c["q"], c["k"], c["v"], c["tq"], c["tk"], c["tv"], c["w1"], c["w2"])
+        _close(o[:, hd:hd + 1], ro, torch.bfloat16, "O")
+        _close(to[:, hd:hd + 1], rto, torch.bfloat16, "tO")
+        for x, r_, nme in zip(g, (rdq, rdk, rdv), ("dq", "dk", "dv")):
+            _close(x[:, hd:hd + 1], r_, torch.bfloat16, nme)
     o2, to2 = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(x.detach() for x in a), (2 * t["tq"], 2 * t["tk"], 2 * t["tv"]))
     assert torch.equal(o2, o.detach())
     assert (to2.float() - 2 * to.detach().float()).abs().max().item() <= 2e-2
