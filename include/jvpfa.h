@@ -66,11 +66,7 @@ typedef enum {
 typedef enum {
   JVPFA_IMPL_AUTO = 0,
   JVPFA_IMPL_GENERIC = 1, /* force the register-tiled mma.sync kernels                    */
-  JVPFA_IMPL_TCGEN05 = 2, /* force the TMA + tcgen05/TMEM kernels; error if not eligible  */
-  /* Measurement aids, OR-ed into the family value, honoured by jvpfa_bwd only: run just one of
-   * its two launches (the other output tensors are then left untouched). */
-  JVPFA_IMPL_ONLY_DKDV = 0x100,
-  JVPFA_IMPL_ONLY_DQ = 0x200
+  JVPFA_IMPL_TCGEN05 = 2  /* force the TMA + tcgen05/TMEM kernels; error if not eligible  */
 } jvpfa_impl;
 
 /* Mask / bias description shared by forward and backward.

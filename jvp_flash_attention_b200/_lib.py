@@ -18,7 +18,6 @@ BF16, FP16, FP32 = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_KVLEN, MASK_BOOL, MASK_BIAS = 0, 1, 2, 3, 4
 IMPL_AUTO, IMPL_GENERIC, IMPL_TCGEN05 = 0, 1, 2
 INDEX_MASKS = (MASK_NONE, MASK_CAUSAL, MASK_KVLEN)  # masks applied by index comparison inside the kernels
-IMPL_ONLY_DKDV, IMPL_ONLY_DQ = 0x100, 0x200  # measurement aids for jvpfa_bwd
 
 DTYPE_ENUM = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32}
 FP32_TF32 = 3  # JVPFA_FP32_TF32: fp32 tensors, products as one TF32 MMA

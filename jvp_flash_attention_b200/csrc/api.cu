@@ -93,7 +93,7 @@ static int validate_fwd(const jvpfa_fwd_args* a) {
   return check_mask(a->mask);
 }
 
-static int impl_family(int impl) { return impl & 0xff; }
+static int impl_family(int impl) { return impl; }
 
 static int validate_bwd(const jvpfa_bwd_args* a) {
   if (!a) return JVPFA_ERR_NULL;
@@ -107,7 +107,7 @@ static int validate_bwd(const jvpfa_bwd_args* a) {
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return JVPFA_ERR_ALIGN;
   if (a->dq_accum && !aligned16(a->dq_accum)) return JVPFA_ERR_ALIGN;
-  if (impl_family(a->impl) > JVPFA_IMPL_TCGEN05 || (a->impl & ~0x3ff) != 0) return JVPFA_ERR_UNSUPPORTED;
+  if (a->impl < JVPFA_IMPL_AUTO || a->impl > JVPFA_IMPL_TCGEN05) return JVPFA_ERR_UNSUPPORTED;
   rc = check_strides(a->in_stride);
   if (rc) return rc;
   return check_mask(a->mask);

@@ -620,8 +620,8 @@ static int launch_bwd_one(const jvpfa_bwd_args& a, cudaStream_t stream) {
     return JVPFA_ERR_CUDA;
   }
   dim3 grid((a.L + C::OWN - 1) / C::OWN, a.B * a.H);
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) k1<<<grid, C::NTHREADS, smem_kv, stream>>>(a);
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) k2<<<grid, C::NTHREADS, smem_q, stream>>>(a);
+  k1<<<grid, C::NTHREADS, smem_kv, stream>>>(a);
+  k2<<<grid, C::NTHREADS, smem_q, stream>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "launch bwd_generic");

@@ -564,10 +564,9 @@ static int launch_both(const jvpfa_bwd_args& a, cudaStream_t s) {
     return JVPFA_ERR_CUDA;
   }
   int rc = JVPFA_OK;
-  const bool both = !(a.impl & (JVPFA_IMPL_ONLY_DQ | JVPFA_IMPL_ONLY_DKDV));
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half<T, D, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
+  rc = launch_half<T, D, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
   if (rc) return rc;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half<T, D, false, HAS_GO, HAS_GT, MK>(a, s, status, both);
+  rc = launch_half<T, D, false, HAS_GO, HAS_GT, MK>(a, s, status, true);
   return rc;
 }
 
@@ -607,7 +606,7 @@ bool bwd_tc5_eligible(const jvpfa_bwd_args& a) {
 int launch_bwd_tc5(const jvpfa_bwd_args& a, cudaStream_t s) {
   if (a.D == 64) {
     // one pass over the score tiles when the caller gave the dQ accumulation buffer (bwd_tc5_fused64.cu)
-    if (bwd_tc5_fused64_eligible(a) && !(a.impl & (JVPFA_IMPL_ONLY_DKDV | JVPFA_IMPL_ONLY_DQ))) return launch_bwd_tc5_fused64(a, s);
+    if (bwd_tc5_fused64_eligible(a)) return launch_bwd_tc5_fused64(a, s);
     return launch_bwd_tc5_d64(a, s);  // two pipelined launches (bwd_tc5_d64.cu)
   }
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);

@@ -970,10 +970,9 @@ static int launch_both64(const jvpfa_bwd_args& a, cudaStream_t s) {
     return JVPFA_ERR_CUDA;
   }
   int rc = JVPFA_OK;
-  const bool both = !(a.impl & (JVPFA_IMPL_ONLY_DQ | JVPFA_IMPL_ONLY_DKDV));
-  if (!(a.impl & JVPFA_IMPL_ONLY_DQ)) rc = launch_half64<T, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
+  rc = launch_half64<T, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
   if (rc) return rc;
-  if (!(a.impl & JVPFA_IMPL_ONLY_DKDV)) rc = launch_half64<T, false, HAS_GO, HAS_GT, MK>(a, s, status, both);
+  rc = launch_half64<T, false, HAS_GO, HAS_GT, MK>(a, s, status, true);
   return rc;
 }
 

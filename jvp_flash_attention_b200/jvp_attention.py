@@ -134,6 +134,18 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
         return tuple(0 if t.shape[d] == 1 else t.stride(d) for d in range(4))
 
     if m.dtype == torch.bool:
+        if mh == 1 and mi == 1:
+            # Candidate key-padding mask: valid keys form a prefix of each row.  Lengths, the prefix test and
+            # upstream's "no head all False" check come back in one read-back.
+            rows = m.reshape(mz, N)
+            lens = rows.sum(dim=-1, dtype=torch.int32)
+            prefix = torch.arange(N, device=m.device).unsqueeze(0) < lens.unsqueeze(1)
+            is_prefix, min_len = torch.stack(((prefix == rows).all().to(torch.int32), lens.min())).tolist()
+            if is_prefix:
+                if verify:
+                    assert min_len > 0, "The attention mask cannot be all False for any head."
+                kv_len = lens.expand(Z).contiguous() if mz == 1 else lens.contiguous()
+                return _lib.MaskSpec(_lib.MASK_KVLEN, kv_len), 1, attn_mask
         m8 = m.view(torch.uint8) if m.is_contiguous() or m.stride(-1) == 1 else m.contiguous().view(torch.uint8)
         spec = _lib.MaskSpec(_lib.MASK_BOOL, m8, bstrides(m8))
         every_head_live = True
@@ -151,14 +163,6 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
             except _lib.Unsupported:  # layout not readable as 16-byte pieces: no skipping, element-wise check
                 every_head_live = _lib.mask_check(spec, m8.shape)[0]
         assert every_head_live, "The attention mask cannot be all False for any head."
-        if mh == 1 and mi == 1:
-            # Candidate key-padding mask: valid keys form a prefix of each row.
-            rows = m.reshape(mz, N)
-            lens = rows.sum(dim=-1, dtype=torch.int32)
-            prefix = torch.arange(N, device=m.device).unsqueeze(0) < lens.unsqueeze(1)
-            if bool((prefix == rows).all()):
-                kv_len = lens.expand(Z).contiguous() if mz == 1 else lens.contiguous()
-                return _lib.MaskSpec(_lib.MASK_KVLEN, kv_len), 1, attn_mask
         return spec, 1, attn_mask
 
     if m.dtype not in _lib.DTYPE_ENUM:
@@ -308,6 +312,58 @@ class _TangentBridge(Function):
         return gq, gk, gv, gtq, gtk, gtv, None, None, None, None, None, None
 
 
+def _forward_impl(q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, verify_attn_mask):
+    """Checks, mask classification and the launch of the fused forward, shared by JVPAttn.forward and its lean twin
+    (JVPAttn's nested types are looked up when it is called).
+    Returns (o, o_t, M, mu, mask_spec, MASK_TYPE, mask_tensor, sm_scale, HEAD_DIM_K, grid)."""
+    if dropout_p != 0.0:
+        raise NotImplementedError("Dropout is not currently supported in JVP attention.")
+
+    Z, H, N_CTX, HEAD_DIM_Q = q.shape
+    HEAD_DIM_K = k.shape[-1]
+    HEAD_DIM_V = v.shape[-1]
+    assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V, (
+        "JVP attention requires HEAD_DIM_Q == HEAD_DIM_K == HEAD_DIM_V"
+        f" but got HEAD_DIM_Q={HEAD_DIM_Q}, HEAD_DIM_K={HEAD_DIM_K}, HEAD_DIM_V={HEAD_DIM_V}"
+    )
+    assert HEAD_DIM_K in _UPSTREAM_HEAD_DIMS, (
+        "JVP attention only supports HEAD_DIM_K in {16, 32, 64, 128, 256},"
+        f" but got HEAD_DIM_K={HEAD_DIM_K}"
+    )
+    if HEAD_DIM_K not in _SUPPORTED_HEAD_DIMS:
+        raise NotImplementedError(
+            f"HEAD_DIM_K={HEAD_DIM_K} has no sm_100a kernel in this build (supported: {_SUPPORTED_HEAD_DIMS})"
+        )
+    assert N_CTX % 2 == 0 and N_CTX >= MIN_SEQUENCE_LENGTH, (
+        "JVP attention requires N_CTX to be a multiple of 2 and >= 32,"
+        f" but got N_CTX={N_CTX}"
+    )
+    assert k.shape == q.shape and v.shape == q.shape, "q, k, v must share one (Z, H, N_CTX, HEAD_DIM) shape"
+    if causal and attn_mask is not None:
+        raise ValueError("Causal attention does not support an attention mask.")
+    if q.dtype not in _lib.DTYPE_ENUM:
+        raise TypeError(f"unsupported dtype {q.dtype}; expected bfloat16, float16 or float32")
+    _require_cuda(q, k, v, q_t, k_t, v_t, attn_mask)
+
+    if sm_scale is None:
+        sm_scale = HEAD_DIM_K**-0.5
+
+    tangents = [q_t, k_t, v_t]
+    if any(t is not None for t in tangents):
+        tangents = [torch.zeros_like(q) if t is None else t for t in tangents]
+    qc, kc, vc = q, k, v  # strided views are read in place where the kernels can (_launch_fwd)
+    tq, tk, tv = (None if t is None else t.to(q.dtype) for t in tangents)
+
+    spec, MASK_TYPE, mask_tensor = classify_mask(attn_mask, causal, Z, H, N_CTX, q.dtype, verify_attn_mask)
+    # the backward of this call recomputes the scores at the precision they had here, whatever the process-wide
+    # setting is by then
+    spec.fp32_mode = _lib.FP32_PRECISION
+    o, o_t, M, mu = _launch_fwd(qc, kc, vc, tq, tk, tv, spec, sm_scale)
+    grid = JVPAttn.Grid((N_CTX + 63) // 64, Z * H, 1)
+    return o, o_t, M, mu, spec, MASK_TYPE, mask_tensor, sm_scale, HEAD_DIM_K, grid
+
+
+
 class JVPAttn(Function):
     """JVP (Jacobian-Vector Product) for Attention Mechanism (same interface as upstream's JVPAttn)."""
 
@@ -393,50 +449,8 @@ class JVPAttn(Function):
         ``warp_specialize`` and ``USE_TMA`` are accepted for signature compatibility and ignored:
         there is one sm_100a code path.
         """
-        if dropout_p != 0.0:
-            raise NotImplementedError("Dropout is not currently supported in JVP attention.")
-
-        Z, H, N_CTX, HEAD_DIM_Q = q.shape
-        HEAD_DIM_K = k.shape[-1]
-        HEAD_DIM_V = v.shape[-1]
-        assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V, (
-            "JVP attention requires HEAD_DIM_Q == HEAD_DIM_K == HEAD_DIM_V"
-            f" but got HEAD_DIM_Q={HEAD_DIM_Q}, HEAD_DIM_K={HEAD_DIM_K}, HEAD_DIM_V={HEAD_DIM_V}"
-        )
-        assert HEAD_DIM_K in _UPSTREAM_HEAD_DIMS, (
-            "JVP attention only supports HEAD_DIM_K in {16, 32, 64, 128, 256},"
-            f" but got HEAD_DIM_K={HEAD_DIM_K}"
-        )
-        if HEAD_DIM_K not in _SUPPORTED_HEAD_DIMS:
-            raise NotImplementedError(
-                f"HEAD_DIM_K={HEAD_DIM_K} has no sm_100a kernel in this build (supported: {_SUPPORTED_HEAD_DIMS})"
-            )
-        assert N_CTX % 2 == 0 and N_CTX >= MIN_SEQUENCE_LENGTH, (
-            "JVP attention requires N_CTX to be a multiple of 2 and >= 32,"
-            f" but got N_CTX={N_CTX}"
-        )
-        assert k.shape == q.shape and v.shape == q.shape, "q, k, v must share one (Z, H, N_CTX, HEAD_DIM) shape"
-        if causal and attn_mask is not None:
-            raise ValueError("Causal attention does not support an attention mask.")
-        if q.dtype not in _lib.DTYPE_ENUM:
-            raise TypeError(f"unsupported dtype {q.dtype}; expected bfloat16, float16 or float32")
-        _require_cuda(q, k, v, q_t, k_t, v_t, attn_mask)
-
-        if sm_scale is None:
-            sm_scale = HEAD_DIM_K**-0.5
-
-        tangents = [q_t, k_t, v_t]
-        if any(t is not None for t in tangents):
-            tangents = [torch.zeros_like(q) if t is None else t for t in tangents]
-        qc, kc, vc = q, k, v  # strided views are read in place where the kernels can (_launch_fwd)
-        tq, tk, tv = (None if t is None else t.to(q.dtype) for t in tangents)
-
-        spec, MASK_TYPE, mask_tensor = classify_mask(attn_mask, causal, Z, H, N_CTX, q.dtype, verify_attn_mask)
-        # the backward of this call recomputes the scores at the precision they had here, whatever the process-wide
-        # setting is by then
-        spec.fp32_mode = _lib.FP32_PRECISION
-        o, o_t, M, mu = _launch_fwd(qc, kc, vc, tq, tk, tv, spec, sm_scale)
-        grid = JVPAttn.Grid((N_CTX + 63) // 64, Z * H, 1)
+        o, o_t, M, mu, spec, MASK_TYPE, mask_tensor, sm_scale, HEAD_DIM_K, grid = _forward_impl(
+            q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, verify_attn_mask)
         return JVPAttn.FwdOut(
             o,
             JVPAttn.FwdOutCtxContrib(o_t, M, grid, HEAD_DIM_K, sm_scale, mask_tensor, MASK_TYPE, dropout_p, 0,
@@ -475,10 +489,10 @@ class JVPAttn(Function):
         USE_TMA: bool = True,
     ) -> Tensor:
         """Primal-only attention (upstream: jvp_attention.py:2701-2752).  Returns O."""
-        out = JVPAttn.apply(q, k, v, None, None, None, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
-                            USE_TMA, True)  # every positional argument given: the quick signature binding applies
-        a, _ = out
-        return a
+        if dropout_p != 0.0:
+            raise NotImplementedError("Dropout is not currently supported in JVP attention.")
+        # every positional argument given: the quick signature binding applies
+        return _Attn.apply(q, k, v, None, None, None, attn_mask, causal, sm_scale, True)[0]
 
     @staticmethod
     def fwd_dual(
@@ -501,43 +515,95 @@ class JVPAttn(Function):
         _, q_t = fwAD.unpack_dual(q)
         _, k_t = fwAD.unpack_dual(k)
         _, v_t = fwAD.unpack_dual(v)
-        out = JVPAttn.apply(q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, warp_specialize,
-                            USE_TMA, True)
-        a, _ = out
-        return a
+        if dropout_p != 0.0:
+            raise NotImplementedError("Dropout is not currently supported in JVP attention.")
+        return _Attn.apply(q, k, v, q_t, k_t, v_t, attn_mask, causal, sm_scale, True)[0]
 
     @staticmethod
     def jvp(ctx: "JVPAttn.FnCtx", gq: Tensor, gk: Tensor, gv: Tensor, *_) -> "JVPAttn.JVPOut":
         """Returns the tangent computed by the fused forward (upstream: jvp_attention.py:2816-2828),
         routed through ``_TangentBridge`` so that it carries a gradient."""
-        o_t, q, k, v, q_t, k_t, v_t, o, M, mu = ctx.saved_for_forward
-        if o_t is None:
-            raise RuntimeError(
-                "JVPAttn.jvp needs tangents at forward time: call JVPAttn.fwd_dual (or pass q_t, k_t, v_t to apply)"
-            )
-        # Nobody can ask for a gradient of the tangent when no input takes part in a graph: hand the kernel's tangent
-        # over as it is and skip the bridging node.  (Looked up on the unwrapped tensors: inside torch.func.jvp the
-        # wrappers do not say.)
-        if not any(x is not None and _unwrap(x).requires_grad for x in (q, k, v, q_t, k_t, v_t, gq, gk, gv)):
-            return JVPAttn.JVPOut(o_t, None)
-        tq = gq if gq is not None else (q_t if q_t is not None else torch.zeros_like(q))
-        tk = gk if gk is not None else (k_t if k_t is not None else torch.zeros_like(k))
-        tv = gv if gv is not None else (v_t if v_t is not None else torch.zeros_like(v))
-        t = _TangentBridge.apply(q, k, v, tq, tk, tv, o_t, o, M, mu, ctx.mask_spec, ctx.sm_scale)
-        return JVPAttn.JVPOut(t, None)
+        return JVPAttn.JVPOut(_jvp_impl(ctx, gq, gk, gv), None)
 
     @staticmethod
     def backward(ctx, do, _) -> "JVPAttn.BwdOut":
         """Gradient of <do, O> w.r.t. q, k, v (upstream: jvp_attention.py:2831-2978)."""
         if do is None:
             return JVPAttn.BwdOut(*([None] * 13))
-        # Inside fwAD.dual_level() the saved q, k, v are still dual; only their primal parts (which
-        # keep the backward graph needed for double backward) may enter the next Function.
-        q, k, v, o, M = (fwAD.unpack_dual(x).primal for x in ctx.saved_tensors)
-        _check_bwd_layout(q, k, v, o)
-        dq, dk, dv = _AttnBwd.apply(q, k, v, o.detach(), M, fwAD.unpack_dual(do).primal, ctx.mask_spec,
-                                    ctx.sm_scale)
+        dq, dk, dv = _backward_impl(ctx, do)
         return JVPAttn.BwdOut(dq, dk, dv, None, None, None, None, None, None, None, None, None, None)
+
+
+def _jvp_impl(ctx, gq, gk, gv):
+    """The tangent output of a call whose forward has run: the kernel's tangent, behind ``_TangentBridge`` when a
+    gradient of it can be asked for."""
+    o_t, q, k, v, q_t, k_t, v_t, o, M, mu = ctx.saved_for_forward
+    if o_t is None:
+        raise RuntimeError(
+            "JVPAttn.jvp needs tangents at forward time: call JVPAttn.fwd_dual (or pass q_t, k_t, v_t to apply)"
+        )
+    # Nobody can ask for a gradient of the tangent when no input takes part in a graph: hand the kernel's tangent
+    # over as it is and skip the bridging node.  (Looked up on the unwrapped tensors: inside torch.func.jvp the
+    # wrappers do not say.)
+    if not any(x is not None and _unwrap(x).requires_grad for x in (q, k, v, q_t, k_t, v_t, gq, gk, gv)):
+        return o_t
+    tq = gq if gq is not None else (q_t if q_t is not None else torch.zeros_like(q))
+    tk = gk if gk is not None else (k_t if k_t is not None else torch.zeros_like(k))
+    tv = gv if gv is not None else (v_t if v_t is not None else torch.zeros_like(v))
+    return _TangentBridge.apply(q, k, v, tq, tk, tv, o_t, o, M, mu, ctx.mask_spec, ctx.sm_scale)
+
+
+def _backward_impl(ctx, do):
+    """(dq, dk, dv) of <do, O>, as a node that can be differentiated once more."""
+    # Inside fwAD.dual_level() the saved q, k, v are still dual; only their primal parts (which
+    # keep the backward graph needed for double backward) may enter the next Function.
+    q, k, v, o, M = (fwAD.unpack_dual(x).primal for x in ctx.saved_tensors)
+    _check_bwd_layout(q, k, v, o)
+    return _AttnBwd.apply(q, k, v, o.detach(), M, fwAD.unpack_dual(do).primal, ctx.mask_spec, ctx.sm_scale)
+
+
+class _Box:
+    """One-slot holder that passes through ``Function.apply`` and the pytree handling of torch.func transforms as
+    a single opaque leaf."""
+
+    __slots__ = ("value",)
+
+    def __init__(self, value=None):
+        self.value = value
+
+
+class _Attn(Function):
+    """What ``JVPAttn.fwd`` and ``JVPAttn.fwd_dual`` call: the same forward, jvp and backward as ``JVPAttn``, whose
+    second output is one opaque holder of (o_t, M, mu, mask description, scale) instead of upstream's nested
+    NamedTuples.  Under ``torch.func.jvp`` every output of a custom Function is wrapped and unwrapped as a pytree once
+    per transform level; the NamedTuples (some twenty leaves) made that the larger part of a call's host time.
+    ``JVPAttn.apply`` keeps upstream's output structure for callers that use it directly."""
+
+    @staticmethod
+    def forward(q, k, v, q_t, k_t, v_t, attn_mask, causal, sm_scale, verify_attn_mask):
+        o, o_t, M, mu, spec, _, _, sm_scale, _, _ = _forward_impl(q, k, v, q_t, k_t, v_t, attn_mask, 0.0, causal, sm_scale,
+                                                                 verify_attn_mask)
+        return o, _Box((o_t, M, mu, spec, sm_scale))
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        q, k, v, q_t, k_t, v_t, *_ = inputs
+        o, aux = outputs
+        o_t, M, mu, ctx.mask_spec, ctx.sm_scale = aux.value
+        ctx.save_for_forward(o_t, q, k, v, q_t, k_t, v_t, o, M, mu)
+        ctx.save_for_backward(q, k, v, o, M)
+        ctx.set_materialize_grads(False)
+
+    @staticmethod
+    def jvp(ctx, gq, gk, gv, *_):
+        return _jvp_impl(ctx, gq, gk, gv), None
+
+    @staticmethod
+    def backward(ctx, do, _):
+        if do is None:
+            return (None,) * 10
+        dq, dk, dv = _backward_impl(ctx, do)
+        return (dq, dk, dv) + (None,) * 7
 
 
 attention = JVPAttn.fwd
@@ -564,7 +630,7 @@ class _ForwardSignature(inspect.Signature):
         return super().bind(*args, **kwargs)
 
 
-for _fn in (JVPAttn, _TangentBridge, _AttnBwd):
+for _fn in (JVPAttn, _Attn, _TangentBridge, _AttnBwd):
     _sig = inspect.signature(_fn.forward)
     _fn.forward.__signature__ = _ForwardSignature(list(_sig.parameters.values()), return_annotation=_sig.return_annotation)
 del _fn, _sig
