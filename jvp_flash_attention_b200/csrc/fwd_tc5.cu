@@ -517,10 +517,7 @@ template <typename T>
 static int launch_t(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
   if (a.D == 64) return dual ? launch_one<T, 64, true, 0>(a, s) : launch_one<T, 64, false, 0>(a, s);
-  if (a.D != 128) return JVPFA_ERR_UNSUPPORTED;
-  if (a.mask.kind == JVPFA_MASK_BOOL) return dual ? launch_one<T, 128, true, 1>(a, s) : launch_one<T, 128, false, 1>(a, s);
-  if (a.mask.kind == JVPFA_MASK_BIAS) return dual ? launch_one<T, 128, true, 2>(a, s) : launch_one<T, 128, false, 2>(a, s);
-  return dual ? launch_one<T, 128, true, 0>(a, s) : launch_one<T, 128, false, 0>(a, s);
+  return JVPFA_ERR_UNSUPPORTED;  // head dimension 128 has its own kernel
 }
 
 }  // namespace tc5
@@ -544,6 +541,8 @@ int launch_fwd_tc5(const jvpfa_fwd_args& a, cudaStream_t s) {
   // Query-tile-pair kernel (fwd_tc5_pair64.cu); it takes the row maximum before scaling and therefore
   // needs a positive softmax scale.
   if (a.D == 64 && a.sm_scale > 0.f) return launch_fwd_tc5_pair64(a, s);
+  // Head dimension 128: score products of the next key tile under the softmax of this one (fwd_tc5_pipe128.cu).
+  if (a.D == 128) return launch_fwd_tc5_pipe128(a, s);
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);
 }
 

@@ -53,6 +53,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Two accumulator words as a packed pair of fp32 values, and the three-input maximum.
+__device__ __forceinline__ float2 pf2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // Read-only global loads and 16-bit unpacking used for user masks and bias.
 template <typename T>
 __device__ __forceinline__ float2 unpack2(uint32_t w);
