@@ -609,6 +609,8 @@ int launch_bwd_tc5(const jvpfa_bwd_args& a, cudaStream_t s) {
     if (bwd_tc5_fused64_eligible(a)) return launch_bwd_tc5_fused64(a, s);
     return launch_bwd_tc5_d64(a, s);  // two pipelined launches (bwd_tc5_d64.cu)
   }
+  // Head dimension 128 without a user mask or bias: the pipelined kernels of bwd_tc5_pipe128.cu
+  if (bwd_tc5_pipe128_eligible(a)) return launch_bwd_tc5_pipe128(a, s);
   return a.dtype == JVPFA_BF16 ? tc5::launch_t<__nv_bfloat16>(a, s) : tc5::launch_t<__half>(a, s);
 }
 

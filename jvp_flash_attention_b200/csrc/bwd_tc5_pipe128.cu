@@ -1,0 +1,568 @@
+// Backward of <gO, O> + <gtO, tO> for head dimension 128, bf16 / fp16, without a user mask or bias, on the Blackwell
+// tensor cores, with the score products of the next tile running under the elementwise work of the current one.
+//
+// Same split as the register-tiled backward (bwd_generic.cu; upstream jvp_attention.py:2008-2233): one launch owns
+// 128-key tiles and loops over queries (dK, dV), one owns 128-query tiles and loops over keys (dQ).  Both are
+// instances of one template:
+//   "own" side  : 128 rows, one per TMEM lane; four operand tiles resident in smem
+//                 own keys: K, tK, V, tV        own queries: Q, tQ, G, gO        (G = cotangent of tO)
+//   "loop" side : 32-row tiles streamed through a three-stage TMA ring, the four tensors of a stage adjacent
+//                 own keys: Q, tQ, G, gO        own queries: K, tK, V, tV
+// TMEM: two buffers of four 128x32 fp32 score accumulators [S | TS | E | FP], then the outputs (dK | dV, or dQ).
+// Per loop tile the MMA warp forms
+//     [S | TS] = own0 [loop0 | loop1]^T ,  TS += own1 loop0^T     (scores and tangent scores)
+//     [E | FP] = own2 [loop2 | loop3]^T ,  FP += own3 loop2^T     (own keys: E = V G^T, FP = V gO^T + tV G^T)
+// where products that share the 128-row operand are one instruction over the adjacent loop tiles.  The elementwise
+// threads (two warpgroups, 16 of the 32 columns each) read the four accumulators and write the 16-bit operands
+//     P, A = P*(tS-mu), gtS = P*(E-eps), gS = P*((E-eps)*(tS-mu) + FP - delta - cterm - eps*mu)
+// back over the columns they have just read: warpgroup h puts its 16 columns of gS and gtS over its half of S and
+// its A and P over its half of TS, so that neither group can overwrite what the other still has to read.  A second
+// group of MMAs (A operand from TMEM, one contraction step per 16-column piece; B = the streamed tiles used
+// MN-major) accumulates
+//     dK += gS Q + gtS tQ ,  dV += A G + P gO      or      dQ += gS K + gtS tK.
+// The issuer's order is  scores(0), scores(1), out(0), scores(2), out(1), ...: the tensor pipe executes in issue
+// order, so scores(t+2) overwrites buffer t & 1 only after out(t) has read its operands from it.
+// Formulas: see bwd_generic.cu.  All waits are bounded (tc5_common.cuh); after one that gave up the CTA's output
+// rows carry NaN.
+#include "tc5_common.cuh"
+
+namespace jvpfa {
+namespace tc5 {
+
+struct BwdPipeMaps {
+  CUtensorMap k, v, tk, tv;   // key-side tensors
+  CUtensorMap q, go, tq, g;   // query-side tensors (g = cotangent of tO)
+};
+
+template <bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+struct BwdPipeCfg {
+  static constexpr int D = 128;
+  static constexpr int OWN = 128;
+  static constexpr int BL = 32;
+  static constexpr int STAGES = 3;
+  static constexpr int NTHREADS = 320;  // producer, issuer, two elementwise warpgroups
+  static constexpr int OWN_BYTES = OWN * D * 2;      // 32 KiB: two 64-column halves of 16 KiB
+  static constexpr int OWN_HALF = OWN * 128;
+  static constexpr int LQ_BYTES = BL * 128;          // 4 KiB: one loop tensor, one 64-column half
+  static constexpr int LOOP_HALF = 4 * LQ_BYTES;     // [loop0 | loop1 | loop2 | loop3] of one half
+  static constexpr int STAGE_BYTES = 2 * LOOP_HALF;  // 32 KiB
+  static constexpr int OFF_LOOP = 4 * OWN_BYTES;
+  static constexpr int TILE_BYTES = OFF_LOOP + STAGES * STAGE_BYTES;  // 224 KiB
+  static constexpr int STAT_BYTES = OWN_KEYS ? STAGES * BL * 16 : 0;
+  static constexpr int SMEM_BYTES = TILE_BYTES + STAT_BYTES + 256 + 1024;
+  // tensors actually loaded
+  static constexpr int N_KEY = HAS_GT ? 4 : 2;                               // K, V (+ tK, tV)
+  static constexpr int N_QRY = 1 + (HAS_GO ? 1 : 0) + (HAS_GT ? 2 : 0);      // Q (+ gO) (+ tQ, G)
+  static constexpr int N_OWN = OWN_KEYS ? N_KEY : N_QRY;
+  static constexpr int N_LOOP = OWN_KEYS ? N_QRY : N_KEY;
+  // TMEM columns
+  static constexpr int SC_COLS = 4 * BL;  // one buffer: S | TS | E | FP
+  static constexpr int COL_S = 0, COL_TS = BL, COL_E = 2 * BL, COL_FP = 3 * BL;
+  // Packed operands: piece h (columns 16h .. 16h+15 of the tile) of gS at COL_S + 16h, of gtS 8 columns on;
+  // of A at COL_TS + 16h, of P 8 columns on.
+  static constexpr int COL_OUT0 = 2 * SC_COLS;
+  static constexpr int COL_OUT1 = COL_OUT0 + D;
+  static constexpr int COLS_ALLOC = 512;
+};
+static_assert(BwdPipeCfg<true, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+__global__ void __launch_bounds__(320, 1)
+bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMaps maps, int* status) {
+  using C = BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>;
+  constexpr int D = C::D, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES;
+
+  // The own-queries launch that follows reads nothing this kernel writes: it is launched with programmatic
+  // stream serialization and fills the SMs as this kernel's last CTAs leave them.
+  if constexpr (OWN_KEYS) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const bool dead_on_entry = *(volatile int*)status != 0;  // an earlier bounded wait gave up
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* sOwn = smem;
+  unsigned char* sLoop = smem + C::OFF_LOOP;
+  float4* sStat = reinterpret_cast<float4*>(smem + C::TILE_BYTES);  // OWN_KEYS: [STAGES][BL] {lse, mu, eps, sub}
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::TILE_BYTES + C::STAT_BYTES);
+  uint64_t* own_full = bars + 0;
+  uint64_t* loop_full = bars + 1;   // [3]
+  uint64_t* loop_empty = bars + 4;  // [3]
+  uint64_t* s_full = bars + 7;      // [2]
+  uint64_t* p_full = bars + 9;      // [2]
+  uint64_t* done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int L = a.L;
+  const int bh = blockIdx.y;
+  const int tma_b = bh / a.H, tma_h = bh - tma_b * a.H;  // coordinates in the (D, L, H, B) tensor maps
+  const bool causal = a.mask.kind == JVPFA_MASK_CAUSAL;
+  int n_valid = L;
+  if (a.mask.kind == JVPFA_MASK_KVLEN) {
+    const int n = a.mask.kv_len[tma_b];
+    n_valid = n < 0 ? 0 : (n > L ? L : n);
+  }
+  // Tile ranges.  Own keys: heaviest (lowest) key tiles come first by construction; own queries: reversed so that
+  // the heaviest (highest) query tiles start first.
+  int own0, loop_begin, n_tiles;
+  if constexpr (OWN_KEYS) {
+    own0 = blockIdx.x * OWN;
+    loop_begin = causal ? own0 : 0;
+    n_tiles = (L - loop_begin + BL - 1) / BL;
+    if (own0 >= n_valid) n_tiles = 0;
+  } else {
+    own0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * OWN;
+    loop_begin = 0;
+    int n_end = n_valid;
+    if (causal) n_end = min(n_end, own0 + OWN);
+    n_tiles = (n_end + BL - 1) / BL;
+  }
+  const size_t stat_off = (size_t)bh * L;
+
+  // NaN into this CTA's output rows: the results of this launch are not to be trusted
+  auto poison = [&]() {
+    if (tid < OWN && own0 + tid < L) {
+      if constexpr (OWN_KEYS) {
+        poison_row<T>(a.dk, stat_off + own0 + tid, D);
+        poison_row<T>(a.dv, stat_off + own0 + tid, D);
+      } else {
+        poison_row<T>(a.dq, stat_off + own0 + tid, D);
+      }
+    }
+  };
+  if (dead_on_entry) {
+    poison();
+    // the stream's next kernel must still be ordered after the launch this one overlaps
+    if constexpr (!OWN_KEYS) asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(own_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(loop_full + s, OWN_KEYS ? 2 : 1);  // TMA bytes (+ the row statistics, own keys)
+      mbar_init(loop_empty + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(s_full + s, 1);
+      mbar_init(p_full + s, 256);
+    }
+    mbar_init(done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::COLS_ALLOC);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const AbortState ab{abort_flag, status};
+
+  // Tensor map of own slot s / loop slot s (nullptr: the slot is not used by this instance).
+  auto own_map = [&](int s) -> const CUtensorMap* {
+    if constexpr (OWN_KEYS) {
+      if (s == 0) return &maps.k;
+      if (s == 2) return &maps.v;
+      if (!HAS_GT) return nullptr;
+      return s == 1 ? &maps.tk : &maps.tv;
+    } else {
+      if (s == 0) return &maps.q;
+      if (s == 3) return HAS_GO ? &maps.go : nullptr;
+      if (!HAS_GT) return nullptr;
+      return s == 1 ? &maps.tq : &maps.g;
+    }
+  };
+  auto loop_map = [&](int s) -> const CUtensorMap* {
+    if constexpr (OWN_KEYS) {
+      if (s == 0) return &maps.q;
+      if (s == 3) return HAS_GO ? &maps.go : nullptr;
+      if (!HAS_GT) return nullptr;
+      return s == 1 ? &maps.tq : &maps.g;
+    } else {
+      if (s == 0) return &maps.k;
+      if (s == 2) return &maps.v;
+      if (!HAS_GT) return nullptr;
+      return s == 1 ? &maps.tk : &maps.tv;
+    }
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (+ stats)
+    if (n_tiles > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(own_full, C::N_OWN * C::OWN_BYTES);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const CUtensorMap* m = own_map(s);
+          if (m == nullptr) continue;
+          for (int hf = 0; hf < 2; ++hf)
+            tma_load_4d(sOwn + s * C::OWN_BYTES + hf * C::OWN_HALF, m, own_full, hf * 64, own0, tma_h, tma_b);
+        }
+      }
+      for (int t = 0; t < n_tiles; ++t) {
+        const int st = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        if (!mbar_wait(loop_empty + st, ph ^ 1, ab, kAbortBwdLoopEmpty)) break;
+        const int l0 = loop_begin + t * BL;
+        if (lane == 0) {
+          unsigned char* base = sLoop + st * C::STAGE_BYTES;
+          mbar_expect_tx(loop_full + st, C::N_LOOP * 2 * C::LQ_BYTES);
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const CUtensorMap* m = loop_map(s);
+            if (m == nullptr) continue;
+            for (int hf = 0; hf < 2; ++hf)
+              tma_load_4d(base + hf * C::LOOP_HALF + s * C::LQ_BYTES, m, loop_full + st, hf * 64, l0, tma_h, tma_b);
+          }
+        }
+        if constexpr (OWN_KEYS) {
+          // per-query statistics of this tile, combined once for all 128 key rows; fetched after the tile
+          // loads have been issued, so that the two latencies overlap
+          {
+            const int i = l0 + lane;
+            float4 s4 = make_float4(INFINITY, 0.f, 0.f, 0.f);
+            if (i < L) {
+              s4.x = a.lse[stat_off + i];
+              s4.w = a.delta[stat_off + i];
+              if constexpr (HAS_GT) {
+                s4.y = a.mu[stat_off + i];
+                s4.z = a.eps[stat_off + i];
+                s4.w += a.cterm[stat_off + i] + s4.z * s4.y;
+              }
+            }
+            sStat[st * BL + lane] = s4;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(loop_full + st);  // second arrival: the statistics are in place
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_n32 = make_idesc(Fmt<T>::kIdesc, OWN, BL, 0, 0);      // 128 x 32 scores
+      constexpr uint32_t idesc_n64 = make_idesc(Fmt<T>::kIdesc, OWN, 2 * BL, 0, 0);  // two adjacent accumulators
+      constexpr uint32_t idesc_out = make_idesc(Fmt<T>::kIdesc, OWN, D, 0, 1);       // 128 x 128 outputs
+      const uint32_t own_base = smem_u32(sOwn);
+      // K-major operands, contraction step ks over the head dimension
+      auto adesc = [&](int slot, int ks) {
+        return make_smem_desc(own_base + slot * C::OWN_BYTES + (ks >> 2) * C::OWN_HALF + (ks & 3) * 32, 16, 1024);
+      };
+      auto bdesc = [](uint32_t stage, int slot, int ks) {
+        return make_smem_desc(stage + (ks >> 2) * C::LOOP_HALF + slot * C::LQ_BYTES + (ks & 3) * 32, 16, 1024);
+      };
+      // MN-major loop tiles as the B operand of the outputs, contraction step kk (16 rows) counted from `slot`
+      auto mndesc = [](uint32_t stage, int slot, int kk) {
+        return make_smem_desc(stage + slot * C::LQ_BYTES + kk * 2048, C::LOOP_HALF, 1024);
+      };
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % STAGES;
+        if (!mbar_wait(loop_full + st, (t / STAGES) & 1, ab, kAbortBwdLoopFull)) return false;
+        tc_fence_after();
+        const uint32_t lp = smem_u32(sLoop + st * C::STAGE_BYTES);
+        const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
+        if constexpr (HAS_GT) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) umma_ss(sc + C::COL_S, adesc(0, ks), bdesc(lp, 0, ks), idesc_n64, ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) umma_ss(sc + C::COL_TS, adesc(1, ks), bdesc(lp, 0, ks), idesc_n32, 1);
+          constexpr bool wide = !OWN_KEYS || HAS_GO;  // [E | FP] in one instruction
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ss(sc + C::COL_E, adesc(2, ks), bdesc(lp, 2, ks), wide ? idesc_n64 : idesc_n32, ks > 0);
+          if constexpr (OWN_KEYS || HAS_GO) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              umma_ss(sc + C::COL_FP, adesc(3, ks), bdesc(lp, 2, ks), idesc_n32, wide ? 1u : (uint32_t)(ks > 0));
+          }
+        } else {
+          // S = own0 loop0^T ; FP = V gO^T (own keys: own2 loop3^T) or gO V^T (own queries: own3 loop2^T)
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) umma_ss(sc + C::COL_S, adesc(0, ks), bdesc(lp, 0, ks), idesc_n32, ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ss(sc + C::COL_FP, adesc(OWN_KEYS ? 2 : 3, ks), bdesc(lp, OWN_KEYS ? 3 : 2, ks), idesc_n32, ks > 0);
+        }
+        tc_commit(s_full + (t & 1));
+        return true;
+      };
+      bool ok = mbar_wait(own_full, 0, ab, kAbortBwdOwn);
+      if (ok) ok = issue_scores(0);
+      for (int t = 0; ok && t < n_tiles; ++t) {
+        if (t + 1 < n_tiles && !issue_scores(t + 1)) break;
+        if (!mbar_wait(p_full + (t & 1), (t >> 1) & 1, ab, kAbortBwdPFull)) break;
+        tc_fence_after();
+        const int st = t % STAGES;
+        const uint32_t lp = smem_u32(sLoop + st * C::STAGE_BYTES);
+        const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
+        const uint32_t acc = t > 0;
+        // Contraction step kk = 2 * term + piece: rows 16 * piece .. of loop tile (slot + term), operand piece at
+        // column 16 * piece + 8 * term of the accumulator it was written over.
+        // dK or dQ += gS loop0 + gtS loop1
+#pragma unroll
+        for (int kk = 0; kk < (HAS_GT ? 4 : 2); ++kk)
+          umma_ts(tmem + C::COL_OUT0, sc + C::COL_S + 16 * (kk & 1) + 8 * (kk >> 1), mndesc(lp, 0, kk), idesc_out,
+                  acc | (uint32_t)(kk > 0));
+        if constexpr (OWN_KEYS) {
+          if constexpr (HAS_GT) {
+            // dV += A G + P gO
+#pragma unroll
+            for (int kk = 0; kk < (HAS_GO ? 4 : 2); ++kk)
+              umma_ts(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * (kk & 1) + 8 * (kk >> 1), mndesc(lp, 2, kk), idesc_out,
+                      acc | (uint32_t)(kk > 0));
+          } else {
+            // dV += P gO
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)
+              umma_ts(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * kk + 8, mndesc(lp, 3, kk), idesc_out,
+                      acc | (uint32_t)(kk > 0));
+          }
+        }
+        tc_commit(loop_empty + st);
+      }
+      tc_commit(done);
+    }
+  } else {
+    // ------------------------------------------------------------------ elementwise + epilogue
+    const int quarter = warp & 3;       // TMEM lane quarter this warp may access
+    const int piece = (warp - 2) >> 2;  // warpgroup: columns 16 * piece .. 16 * piece + 15 of every loop tile
+    const int row = quarter * 32 + lane;
+    const int own_idx = own0 + row;  // key index (OWN_KEYS) or query index
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tbase = tmem + lane_off;
+    const float scale_log2 = a.sm_scale * kLog2e;
+    bool alive = true;
+
+    // own-queries variant: this thread's row statistics
+    float r_lse = INFINITY, r_mu = 0.f, r_eps = 0.f, r_sub = 0.f;
+    if constexpr (!OWN_KEYS) {
+      if (own_idx < L) {
+        r_lse = a.lse[stat_off + own_idx];
+        r_sub = a.delta[stat_off + own_idx];
+        if constexpr (HAS_GT) {
+          r_mu = a.mu[stat_off + own_idx];
+          r_eps = a.eps[stat_off + own_idx];
+          r_sub += a.cterm[stat_off + own_idx] + r_eps * r_mu;
+        }
+      }
+    }
+
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t % STAGES;
+      const int l0 = loop_begin + t * BL;
+      if constexpr (OWN_KEYS) {
+        if (!mbar_wait(loop_full + st, (t / STAGES) & 1, ab, kAbortBwdLoopFull)) {
+          alive = false;
+          break;
+        }
+      }
+      if (!mbar_wait(s_full + (t & 1), (t >> 1) & 1, ab, kAbortBwdSFull)) {
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t sc = tbase + (t & 1) * C::SC_COLS + 16 * piece;
+      uint32_t s[16], fp[16];
+      uint32_t ts[HAS_GT ? 16 : 1], e[HAS_GT ? 16 : 1];
+      tmem_ld16(sc + C::COL_S, s);
+      tmem_ld16(sc + C::COL_FP, fp);
+      if constexpr (HAS_GT) {
+        tmem_ld16(sc + C::COL_TS, ts);
+        tmem_ld16(sc + C::COL_E, e);
+      }
+      tmem_wait_ld();
+      // does any element of this tile need the mask test?
+      bool partial;
+      if constexpr (OWN_KEYS) {
+        partial = (own0 + OWN > n_valid) || (causal && own0 + OWN - 1 > l0);
+      } else {
+        partial = (l0 + BL > n_valid) || (causal && l0 + BL - 1 > own0);
+      }
+      const float4* stat = sStat + st * BL + 16 * piece;
+      uint32_t pk_gs[8], pk_gt[HAS_GT ? 8 : 1], pk_av[(HAS_GT && OWN_KEYS) ? 8 : 1], pk_p[OWN_KEYS ? 8 : 1];
+#pragma unroll
+      for (int x2 = 0; x2 < 8; ++x2) {
+        float pv[2], gs[2], av[2], gt[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int col = 2 * x2 + h;
+          float lse, mu, eps, sub;
+          int i, j;
+          if constexpr (OWN_KEYS) {
+            const float4 s4 = stat[col];
+            lse = s4.x, mu = s4.y, eps = s4.z, sub = s4.w;
+            i = l0 + 16 * piece + col;
+            j = own_idx;
+          } else {
+            lse = r_lse, mu = r_mu, eps = r_eps, sub = r_sub;
+            i = own_idx;
+            j = l0 + 16 * piece + col;
+          }
+          float p = fast_exp2(fmaf(__uint_as_float(s[col]), scale_log2, -lse));
+          if (partial && (j >= n_valid || (causal && j > i))) p = 0.f;
+          pv[h] = p;
+          if constexpr (HAS_GT) {
+            const float tm = fmaf(__uint_as_float(ts[col]), a.sm_scale, -mu);
+            const float eb = __uint_as_float(e[col]) - eps;
+            av[h] = p * tm;
+            gt[h] = p * eb;
+            gs[h] = p * fmaf(eb, tm, __uint_as_float(fp[col]) - sub);
+          } else {
+            gs[h] = p * (__uint_as_float(fp[col]) - sub);
+          }
+        }
+        pk_gs[x2] = Elem<T>::pack(gs[0], gs[1]);
+        if constexpr (HAS_GT) pk_gt[x2] = Elem<T>::pack(gt[0], gt[1]);
+        if constexpr (HAS_GT && OWN_KEYS) pk_av[x2] = Elem<T>::pack(av[0], av[1]);
+        if constexpr (OWN_KEYS) pk_p[x2] = Elem<T>::pack(pv[0], pv[1]);
+      }
+      // over this thread's own 16 columns of S and TS, all of which are in registers
+      tmem_st8(sc + C::COL_S, pk_gs);
+      if constexpr (HAS_GT) tmem_st8(sc + C::COL_S + 8, pk_gt);
+      if constexpr (HAS_GT && OWN_KEYS) tmem_st8(sc + C::COL_TS, pk_av);
+      if constexpr (OWN_KEYS && (HAS_GO || !HAS_GT)) tmem_st8(sc + C::COL_TS + 8, pk_p);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full + (t & 1));
+    }
+
+    // ---- epilogue: warpgroup `piece` stores columns 64 * piece .. 64 * piece + 63 of every output row ----
+    if (alive && n_tiles > 0) alive = mbar_wait(done, 0, ab, kAbortBwdDone);
+    if (alive) {
+      tc_fence_after();
+      const bool in_range = own_idx < L;
+      auto store_rows = [&](void* gptr, uint32_t col0, float mul) {
+        T* g = reinterpret_cast<T*>(gptr) + ((size_t)bh * L + own_idx) * D + 64 * piece;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32], pk[16];
+          if (n_tiles > 0) {
+            tmem_ld32(tbase + col0 + 64 * piece + 32 * c, r);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) r[x] = 0u;
+          }
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            pk[x] = Elem<T>::pack(__uint_as_float(r[2 * x]) * mul, __uint_as_float(r[2 * x + 1]) * mul);
+          if (in_range) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+              reinterpret_cast<uint4*>(g + 32 * c)[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+          }
+        }
+      };
+      if constexpr (OWN_KEYS) {
+        store_rows(a.dk, C::COL_OUT0, a.sm_scale);
+        store_rows(a.dv, C::COL_OUT1, 1.f);
+      } else {
+        store_rows(a.dq, C::COL_OUT0, a.sm_scale);
+      }
+    }
+  }
+
+  // The own-queries launch may have started while the own-keys launch before it was still running (programmatic
+  // stream serialization).  Whatever follows on the stream is ordered after THIS grid only, so this grid must not
+  // complete before that one has: wait for it here, after the work.
+  if constexpr (!OWN_KEYS) asm volatile("griddepcontrol.wait;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) poison();
+  if (warp == 0) {
+    if (*abort_flag != 0) {
+      const long long t0 = clock64();
+      while (clock64() - t0 < (1ll << 22)) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem, C::COLS_ALLOC);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+static int launch_pipe_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status, bool overlap_previous) {
+  using C = BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>;
+  BwdPipeMaps m;
+  const CUtensorMapDataType dt = Fmt<T>::kTma;
+  const int key_rows = OWN_KEYS ? C::OWN : C::BL;
+  const int qry_rows = OWN_KEYS ? C::BL : C::OWN;
+  auto enc = [&](CUtensorMap* map, const void* p, const int64_t* st, int rows) {
+    return encode_map4d(map, dt, p, C::D, a.L, a.H, a.B, st, rows);
+  };
+  bool ok = enc(&m.k, a.k, a.in_stride, key_rows) && enc(&m.v, a.v, a.in_stride, key_rows) &&
+            enc(&m.q, a.q, a.in_stride, qry_rows);
+  m.tk = m.tv = m.k;
+  m.go = m.tq = m.g = m.q;
+  if (HAS_GO) ok = ok && enc(&m.go, a.go, nullptr, qry_rows);
+  if (HAS_GT)
+    ok = ok && enc(&m.tk, a.tk, a.in_stride, key_rows) && enc(&m.tv, a.tv, a.in_stride, key_rows) &&
+         enc(&m.tq, a.tq, a.in_stride, qry_rows) && enc(&m.g, a.gto, nullptr, qry_rows);
+  if (!ok) {
+    set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(bwd)");
+    return JVPFA_ERR_CUDA;
+  }
+  auto kern = bwd_tc5_pipe128_kernel<T, OWN_KEYS, HAS_GO, HAS_GT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "cudaFuncSetAttribute(bwd_tc5_pipe128)");
+    return JVPFA_ERR_CUDA;
+  }
+  dim3 grid((a.L + C::OWN - 1) / C::OWN, a.B * a.H);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = dim3(C::NTHREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = overlap_previous ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, a, m, status);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "launch bwd_tc5_pipe128");
+    return JVPFA_ERR_CUDA;
+  }
+  return JVPFA_OK;
+}
+
+template <typename T, bool HAS_GO, bool HAS_GT>
+static int launch_pipe_both(const jvpfa_bwd_args& a, cudaStream_t s) {
+  int* status = tc5_status_device_ptr();
+  if (!status) {
+    set_last_cuda_error(cudaErrorUnknown, "status word address");
+    return JVPFA_ERR_CUDA;
+  }
+  int rc = launch_pipe_half<T, true, HAS_GO, HAS_GT>(a, s, status, false);
+  if (rc) return rc;
+  return launch_pipe_half<T, false, HAS_GO, HAS_GT>(a, s, status, true);
+}
+
+template <typename T>
+static int launch_pipe_t(const jvpfa_bwd_args& a, cudaStream_t s) {
+  const bool go = a.go != nullptr, gt = a.gto != nullptr;
+  if (go && gt) return launch_pipe_both<T, true, true>(a, s);
+  if (gt) return launch_pipe_both<T, false, true>(a, s);
+  return launch_pipe_both<T, true, false>(a, s);
+}
+
+}  // namespace tc5
+
+bool bwd_tc5_pipe128_eligible(const jvpfa_bwd_args& a) {
+  if (a.dtype != JVPFA_BF16 && a.dtype != JVPFA_FP16) return false;
+  if (a.D != 128) return false;
+  const int k = a.mask.kind;
+  return k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN;
+}
+
+int launch_bwd_tc5_pipe128(const jvpfa_bwd_args& a, cudaStream_t s) {
+  return a.dtype == JVPFA_BF16 ? tc5::launch_pipe_t<__nv_bfloat16>(a, s) : tc5::launch_pipe_t<__half>(a, s);
+}
+
+}  // namespace jvpfa

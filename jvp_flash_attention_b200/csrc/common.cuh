@@ -390,6 +390,8 @@ int launch_bwd_tc5_fused64(const jvpfa_bwd_args& a, cudaStream_t stream);
 bool bwd_tc5_fused64_eligible(const jvpfa_bwd_args& a);
 int launch_fwd_tc5_pair64(const jvpfa_fwd_args& a, cudaStream_t stream);
 int launch_fwd_tc5_pipe128(const jvpfa_fwd_args& a, cudaStream_t stream);
+bool bwd_tc5_pipe128_eligible(const jvpfa_bwd_args& a);
+int launch_bwd_tc5_pipe128(const jvpfa_bwd_args& a, cudaStream_t stream);
 bool bwd_tc5_eligible(const jvpfa_bwd_args& a);
 void set_last_cuda_error(cudaError_t e, const char* where);
 int check_pre_request(const jvpfa_pre_args* a);

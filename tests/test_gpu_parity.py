@@ -953,6 +953,10 @@ def test_reference_grid_largest_masked_case_on_tcgen05(mask_type):
     ("both", "none", "bf16", 2, 2, 192), ("gt", "causal", "fp16", 1, 3, 320), ("both", "bool", "bf16", 2, 2, 256),
     ("gt", "bias", "fp16", 2, 2, 192), ("go", "bool_bcast", "bf16", 2, 2, 160), ("both", "bool_keys", "fp16", 3, 2, 224),
     ("gt", "bias", "bf16", 1, 2, 48),
+    # the pipelined kernels (no user mask): ragged lengths, every cotangent combination, more than one ring lap
+    ("go", "none", "fp16", 1, 2, 200), ("both", "kvlen", "bf16", 2, 2, 512), ("gt", "none", "bf16", 1, 2, 96),
+    ("go", "causal", "bf16", 1, 2, 333), ("both", "causal", "bf16", 1, 2, 1024), ("gt", "kvlen", "fp16", 2, 1, 160),
+    ("both", "none", "fp16", 1, 1, 31),
 ])
 def test_tcgen05_head_dim_128_forward_and_backward(cot, kind, dt, B, H, L):
     """The D = 128 tcgen05 kernels (forward with tangents, both backward launches) on every mask kind they take,
