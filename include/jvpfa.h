@@ -290,11 +290,13 @@ int jvpfa_version(void);
 const char* jvpfa_last_cuda_error(void);
 
 /* Reads the device-side status word of the tcgen05 kernels on the current device into *status:
- * 0 = every bounded wait completed; otherwise the code of the first wait that gave up (the
- * kernels then drained and exited early, and their outputs are undefined).  clear != 0 resets
- * the word.  This call synchronises with the device (it is a cudaMemcpyFromSymbol); it is meant
- * for tests and post-mortems, not for the hot path.  No upstream counterpart: Triton kernels
- * have no such waits. */
+ * 0 = every bounded wait completed; otherwise the code of the first wait that gave up.  The
+ * kernels then drained and exited early, the output rows of the affected CTAs (lse in the
+ * forward; dq / dk / dv rows in the backward) hold NaN, and while the word stays non-zero every
+ * later tcgen05 launch on the device writes NaN and returns at once.  clear != 0 resets the
+ * word.  This call synchronises with the device (it is a cudaMemcpyFromSymbol): poll it where
+ * the caller synchronises anyway, not per launch.  No upstream counterpart: Triton kernels have
+ * no such waits. */
 int jvpfa_device_status(int* status, int clear);
 
 /* 1 if jvpfa_fwd / jvpfa_bwd with impl == JVPFA_IMPL_AUTO would take the
