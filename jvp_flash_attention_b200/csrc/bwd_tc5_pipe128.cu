@@ -6,14 +6,16 @@
 // instances of one template:
 //   "own" side  : 128 rows, one per TMEM lane; four operand tiles resident in smem
 //                 own keys: K, tK, V, tV        own queries: Q, tQ, G, gO        (G = cotangent of tO)
-//   "loop" side : 32-row tiles streamed through a three-stage TMA ring, the four tensors of a stage adjacent
-//                 own keys: Q, tQ, G, gO        own queries: K, tK, V, tV
-// TMEM: two buffers of four 128x32 fp32 score accumulators [S | TS | E | FP], then the outputs (dK | dV, or dQ).
+//   "loop" side : tiles of BL rows (32 with own keys, 48 with own queries) streamed by TMA, the tensors of a stage
+//                 adjacent.  Own keys: Q, tQ, G, gO in one three-stage ring.  Own queries: K, tK in a three-stage
+//                 ring (the output products read them again), V, tV in a one-stage ring that comes free as soon
+//                 as the tile's scores exist.
+// TMEM: two buffers of four 128 x BL fp32 score accumulators [S | TS | E | FP], then the outputs (dK | dV, or dQ).
 // Per loop tile the MMA warp forms
 //     [S | TS] = own0 [loop0 | loop1]^T ,  TS += own1 loop0^T     (scores and tangent scores)
 //     [E | FP] = own2 [loop2 | loop3]^T ,  FP += own3 loop2^T     (own keys: E = V G^T, FP = V gO^T + tV G^T)
 // where products that share the 128-row operand are one instruction over the adjacent loop tiles.  The elementwise
-// threads (two warpgroups, 16 of the 32 columns each) read the four accumulators and write the 16-bit operands
+// threads (BL / 16 warpgroups, 16 columns each) read the four accumulators and write the 16-bit operands
 //     P, A = P*(tS-mu), gtS = P*(E-eps), gS = P*((E-eps)*(tS-mu) + FP - delta - cterm - eps*mu)
 // back over the columns they have just read: warpgroup h puts its 16 columns of gS and gtS over its half of S and
 // its A and P over its half of TS, so that neither group can overwrite what the other still has to read.  A second
@@ -38,23 +40,35 @@ template <bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
 struct BwdPipeCfg {
   static constexpr int D = 128;
   static constexpr int OWN = 128;
-  static constexpr int BL = 32;
-  static constexpr int STAGES = 3;
-  static constexpr int NTHREADS = 320;  // producer, issuer, two elementwise warpgroups
-  static constexpr int OWN_BYTES = OWN * D * 2;      // 32 KiB: two 64-column halves of 16 KiB
+  // Rows of a loop tile.  An MMA instruction costs about 58 cycles whatever its N up to 64, so wider tiles mean fewer
+  // instructions per column.  Own keys: dK | dV take 256 TMEM columns, which leaves two score buffers of 4 x 32; own
+  // queries: dQ takes 128, which leaves two buffers of 4 x 48.
+  static constexpr int BL = OWN_KEYS ? 32 : 48;
+  static constexpr int NP = BL / 16;                // 16-column pieces = elementwise warpgroups
+  static constexpr int NTHREADS = 64 + 128 * NP;    // producer, issuer, NP elementwise warpgroups
+  static constexpr int OWN_BYTES = OWN * D * 2;     // 32 KiB: two 64-column halves of 16 KiB
   static constexpr int OWN_HALF = OWN * 128;
-  static constexpr int LQ_BYTES = BL * 128;          // 4 KiB: one loop tensor, one 64-column half
-  static constexpr int LOOP_HALF = 4 * LQ_BYTES;     // [loop0 | loop1 | loop2 | loop3] of one half
-  static constexpr int STAGE_BYTES = 2 * LOOP_HALF;  // 32 KiB
-  static constexpr int OFF_LOOP = 4 * OWN_BYTES;
-  static constexpr int TILE_BYTES = OFF_LOOP + STAGES * STAGE_BYTES;  // 224 KiB
-  static constexpr int STAT_BYTES = OWN_KEYS ? STAGES * BL * 16 : 0;
+  static constexpr int LQ_BYTES = BL * 128;         // one loop tensor, one 64-column half
+  // Ring X holds the loop tensors that the output products read again (they stay until the tile's outputs are done);
+  // ring Y those that only the score products read (free as soon as the scores exist).  Own keys: all four in X.
+  static constexpr int NX = OWN_KEYS ? 4 : 2;
+  static constexpr int NY = 4 - NX;
+  static constexpr int XSTAGES = 3;
+  static constexpr int X_HALF = NX * LQ_BYTES;      // [x0 | x1 (| x2 | x3)] of one half
+  static constexpr int X_STAGE = 2 * X_HALF;
+  static constexpr int Y_HALF = NY * LQ_BYTES;
+  static constexpr int Y_STAGE = 2 * Y_HALF;        // one stage
+  static constexpr int OFF_X = 4 * OWN_BYTES;
+  static constexpr int OFF_Y = OFF_X + XSTAGES * X_STAGE;
+  static constexpr int TILE_BYTES = OFF_Y + Y_STAGE;  // 224 KiB
+  static constexpr int STAT_BYTES = OWN_KEYS ? XSTAGES * BL * 16 : 0;
   static constexpr int SMEM_BYTES = TILE_BYTES + STAT_BYTES + 256 + 1024;
   // tensors actually loaded
   static constexpr int N_KEY = HAS_GT ? 4 : 2;                               // K, V (+ tK, tV)
   static constexpr int N_QRY = 1 + (HAS_GO ? 1 : 0) + (HAS_GT ? 2 : 0);      // Q (+ gO) (+ tQ, G)
   static constexpr int N_OWN = OWN_KEYS ? N_KEY : N_QRY;
-  static constexpr int N_LOOP = OWN_KEYS ? N_QRY : N_KEY;
+  static constexpr int N_X = OWN_KEYS ? N_QRY : (HAS_GT ? 2 : 1);            // own queries: K (+ tK)
+  static constexpr int N_Y = OWN_KEYS ? 0 : (HAS_GT ? 2 : 1);                // own queries: V (+ tV)
   // TMEM columns
   static constexpr int SC_COLS = 4 * BL;  // one buffer: S | TS | E | FP
   static constexpr int COL_S = 0, COL_TS = BL, COL_E = 2 * BL, COL_FP = 3 * BL;
@@ -63,14 +77,16 @@ struct BwdPipeCfg {
   static constexpr int COL_OUT0 = 2 * SC_COLS;
   static constexpr int COL_OUT1 = COL_OUT0 + D;
   static constexpr int COLS_ALLOC = 512;
+  static_assert(COL_OUT0 + (OWN_KEYS ? 2 : 1) * D <= 512, "TMEM budget");
 };
 static_assert(BwdPipeCfg<true, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(BwdPipeCfg<false, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>::NTHREADS, 1)
 bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMaps maps, int* status) {
   using C = BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>;
-  constexpr int D = C::D, OWN = C::OWN, BL = C::BL, STAGES = C::STAGES;
+  constexpr int D = C::D, OWN = C::OWN, BL = C::BL, STAGES = C::XSTAGES, NP = C::NP;
 
   // The own-queries launch that follows reads nothing this kernel writes: it is launched with programmatic
   // stream serialization and fills the SMs as this kernel's last CTAs leave them.
@@ -81,7 +97,8 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   unsigned char* sOwn = smem;
-  unsigned char* sLoop = smem + C::OFF_LOOP;
+  unsigned char* sX = smem + C::OFF_X;
+  unsigned char* sY = smem + C::OFF_Y;
   float4* sStat = reinterpret_cast<float4*>(smem + C::TILE_BYTES);  // OWN_KEYS: [STAGES][BL] {lse, mu, eps, sub}
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::TILE_BYTES + C::STAT_BYTES);
   uint64_t* own_full = bars + 0;
@@ -90,7 +107,9 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
   uint64_t* s_full = bars + 7;      // [2]
   uint64_t* p_full = bars + 9;      // [2]
   uint64_t* done = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* y_full = bars + 12;   // ring Y (one stage)
+  uint64_t* y_empty = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -146,9 +165,11 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(s_full + s, 1);
-      mbar_init(p_full + s, 256);
+      mbar_init(p_full + s, 128 * NP);
     }
     mbar_init(done, 1);
+    mbar_init(y_full, 1);
+    mbar_init(y_empty, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -176,18 +197,22 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
       return s == 1 ? &maps.tq : &maps.g;
     }
   };
-  auto loop_map = [&](int s) -> const CUtensorMap* {
-    if constexpr (OWN_KEYS) {
+  // Tensor map of slot s of ring X / ring Y (nullptr: not used by this instance).
+  auto x_map = [&](int s) -> const CUtensorMap* {
+    if constexpr (OWN_KEYS) {  // Q, tQ, G, gO
       if (s == 0) return &maps.q;
       if (s == 3) return HAS_GO ? &maps.go : nullptr;
       if (!HAS_GT) return nullptr;
       return s == 1 ? &maps.tq : &maps.g;
-    } else {
+    } else {  // K, tK
       if (s == 0) return &maps.k;
-      if (s == 2) return &maps.v;
-      if (!HAS_GT) return nullptr;
-      return s == 1 ? &maps.tk : &maps.tv;
+      return (s == 1 && HAS_GT) ? &maps.tk : nullptr;
     }
+  };
+  auto y_map = [&](int s) -> const CUtensorMap* {  // own queries: V, tV
+    if (OWN_KEYS) return nullptr;
+    if (s == 0) return &maps.v;
+    return (s == 1 && HAS_GT) ? &maps.tv : nullptr;
   };
 
   if (warp == 0) {
@@ -209,14 +234,28 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
         if (!mbar_wait(loop_empty + st, ph ^ 1, ab, kAbortBwdLoopEmpty)) break;
         const int l0 = loop_begin + t * BL;
         if (lane == 0) {
-          unsigned char* base = sLoop + st * C::STAGE_BYTES;
-          mbar_expect_tx(loop_full + st, C::N_LOOP * 2 * C::LQ_BYTES);
+          unsigned char* base = sX + st * C::X_STAGE;
+          mbar_expect_tx(loop_full + st, C::N_X * 2 * C::LQ_BYTES);
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            const CUtensorMap* m = loop_map(s);
+          for (int s = 0; s < C::NX; ++s) {
+            const CUtensorMap* m = x_map(s);
             if (m == nullptr) continue;
             for (int hf = 0; hf < 2; ++hf)
-              tma_load_4d(base + hf * C::LOOP_HALF + s * C::LQ_BYTES, m, loop_full + st, hf * 64, l0, tma_h, tma_b);
+              tma_load_4d(base + hf * C::X_HALF + s * C::LQ_BYTES, m, loop_full + st, hf * 64, l0, tma_h, tma_b);
+          }
+        }
+        if constexpr (C::NY > 0) {
+          // ring Y comes free (scores of the previous tile) after the X stage did (outputs of three tiles ago)
+          if (!mbar_wait(y_empty, (t & 1) ^ 1, ab, kAbortBwdLoopEmpty)) break;
+          if (lane == 0) {
+            mbar_expect_tx(y_full, C::N_Y * 2 * C::LQ_BYTES);
+#pragma unroll
+            for (int s = 0; s < C::NY; ++s) {
+              const CUtensorMap* m = y_map(s);
+              if (m == nullptr) continue;
+              for (int hf = 0; hf < 2; ++hf)
+                tma_load_4d(sY + hf * C::Y_HALF + s * C::LQ_BYTES, m, y_full, hf * 64, l0, tma_h, tma_b);
+            }
           }
         }
         if constexpr (OWN_KEYS) {
@@ -244,49 +283,70 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_tiles > 0) {
-      constexpr uint32_t idesc_n32 = make_idesc(Fmt<T>::kIdesc, OWN, BL, 0, 0);      // 128 x 32 scores
-      constexpr uint32_t idesc_n64 = make_idesc(Fmt<T>::kIdesc, OWN, 2 * BL, 0, 0);  // two adjacent accumulators
-      constexpr uint32_t idesc_out = make_idesc(Fmt<T>::kIdesc, OWN, D, 0, 1);       // 128 x 128 outputs
-      const uint32_t own_base = smem_u32(sOwn);
-      // K-major operands, contraction step ks over the head dimension
-      auto adesc = [&](int slot, int ks) {
-        return make_smem_desc(own_base + slot * C::OWN_BYTES + (ks >> 2) * C::OWN_HALF + (ks & 3) * 32, 16, 1024);
+      constexpr uint32_t idesc_n1 = make_idesc(Fmt<T>::kIdesc, OWN, BL, 0, 0);      // one 128 x BL accumulator
+      constexpr uint32_t idesc_n2 = make_idesc(Fmt<T>::kIdesc, OWN, 2 * BL, 0, 0);  // two adjacent accumulators
+      constexpr uint32_t idesc_out = make_idesc(Fmt<T>::kIdesc, OWN, D, 0, 1);      // 128 x 128 outputs
+      // Shared-memory descriptors as low words (tc5_common.cuh): the high word is the same for every tile used here,
+      // and stepping through a tile is an integer add.  K-major operands: contraction step ks over the head dimension
+      // = 32 bytes inside a 64-column half, the halves OWN_HALF / X_HALF / Y_HALF apart.  MN-major ring-X tiles (B of the
+      // outputs): contraction step kk = 16 rows = 2048 bytes, leading offset = distance of the two 64-column halves.
+      const uint32_t a_lo0 = kDescLo | (smem_u32(sOwn) >> 4);
+      constexpr uint32_t kMnLo = (uint32_t)(C::X_HALF >> 4) << 16;
+      auto a_off = [](int slot, int ks) -> uint32_t {
+        return (uint32_t)(slot * C::OWN_BYTES + (ks >> 2) * C::OWN_HALF + (ks & 3) * 32) >> 4;
       };
-      auto bdesc = [](uint32_t stage, int slot, int ks) {
-        return make_smem_desc(stage + (ks >> 2) * C::LOOP_HALF + slot * C::LQ_BYTES + (ks & 3) * 32, 16, 1024);
-      };
-      // MN-major loop tiles as the B operand of the outputs, contraction step kk (16 rows) counted from `slot`
-      auto mndesc = [](uint32_t stage, int slot, int kk) {
-        return make_smem_desc(stage + slot * C::LQ_BYTES + kk * 2048, C::LOOP_HALF, 1024);
+      auto b_off = [](uint32_t half, int slot, int ks) -> uint32_t {
+        return (uint32_t)((ks >> 2) * half + slot * C::LQ_BYTES + (ks & 3) * 32) >> 4;
       };
       auto issue_scores = [&](int t) -> bool {
         const int st = t % STAGES;
         if (!mbar_wait(loop_full + st, (t / STAGES) & 1, ab, kAbortBwdLoopFull)) return false;
         tc_fence_after();
-        const uint32_t lp = smem_u32(sLoop + st * C::STAGE_BYTES);
+        const uint32_t lx = kDescLo | (smem_u32(sX + st * C::X_STAGE) >> 4);
+        // loop tensors 2 and 3: slots 2, 3 of the X stage (own keys) or slots 0, 1 of ring Y (own queries)
+        const uint32_t l2 = OWN_KEYS ? lx + ((2 * C::LQ_BYTES) >> 4) : (kDescLo | (smem_u32(sY) >> 4));
+        constexpr uint32_t h2 = OWN_KEYS ? C::X_HALF : C::Y_HALF;
         const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
         if constexpr (HAS_GT) {
+          umma_ss_lo<false>(sc + C::COL_S, a_lo0 + a_off(0, 0), lx + b_off(C::X_HALF, 0, 0), idesc_n2);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) umma_ss(sc + C::COL_S, adesc(0, ks), bdesc(lp, 0, ks), idesc_n64, ks > 0);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) umma_ss(sc + C::COL_TS, adesc(1, ks), bdesc(lp, 0, ks), idesc_n32, 1);
-          constexpr bool wide = !OWN_KEYS || HAS_GO;  // [E | FP] in one instruction
+          for (int ks = 1; ks < 8; ++ks)
+            umma_ss_lo<true>(sc + C::COL_S, a_lo0 + a_off(0, ks), lx + b_off(C::X_HALF, 0, ks), idesc_n2);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_ss(sc + C::COL_E, adesc(2, ks), bdesc(lp, 2, ks), wide ? idesc_n64 : idesc_n32, ks > 0);
-          if constexpr (OWN_KEYS || HAS_GO) {
+            umma_ss_lo<true>(sc + C::COL_TS, a_lo0 + a_off(1, ks), lx + b_off(C::X_HALF, 0, ks), idesc_n1);
+          if constexpr (C::NY > 0) {
+            if (!mbar_wait(y_full, t & 1, ab, kAbortBwdLoopFull)) return false;
+            tc_fence_after();
+          }
+          constexpr bool wide = !OWN_KEYS || HAS_GO;  // [E | FP] in one instruction
+          umma_ss_lo<false>(sc + C::COL_E, a_lo0 + a_off(2, 0), l2 + b_off(h2, 0, 0), wide ? idesc_n2 : idesc_n1);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              umma_ss(sc + C::COL_FP, adesc(3, ks), bdesc(lp, 2, ks), idesc_n32, wide ? 1u : (uint32_t)(ks > 0));
+          for (int ks = 1; ks < 8; ++ks)
+            umma_ss_lo<true>(sc + C::COL_E, a_lo0 + a_off(2, ks), l2 + b_off(h2, 0, ks), wide ? idesc_n2 : idesc_n1);
+          if constexpr (OWN_KEYS || HAS_GO) {
+            umma_ss_lo<wide>(sc + C::COL_FP, a_lo0 + a_off(3, 0), l2 + b_off(h2, 0, 0), idesc_n1);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks)
+              umma_ss_lo<true>(sc + C::COL_FP, a_lo0 + a_off(3, ks), l2 + b_off(h2, 0, ks), idesc_n1);
           }
         } else {
           // S = own0 loop0^T ; FP = V gO^T (own keys: own2 loop3^T) or gO V^T (own queries: own3 loop2^T)
+          umma_ss_lo<false>(sc + C::COL_S, a_lo0 + a_off(0, 0), lx + b_off(C::X_HALF, 0, 0), idesc_n1);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) umma_ss(sc + C::COL_S, adesc(0, ks), bdesc(lp, 0, ks), idesc_n32, ks > 0);
+          for (int ks = 1; ks < 8; ++ks)
+            umma_ss_lo<true>(sc + C::COL_S, a_lo0 + a_off(0, ks), lx + b_off(C::X_HALF, 0, ks), idesc_n1);
+          if constexpr (C::NY > 0) {
+            if (!mbar_wait(y_full, t & 1, ab, kAbortBwdLoopFull)) return false;
+            tc_fence_after();
+          }
+          constexpr int fa = OWN_KEYS ? 2 : 3, fb = OWN_KEYS ? 1 : 0;
+          umma_ss_lo<false>(sc + C::COL_FP, a_lo0 + a_off(fa, 0), l2 + b_off(h2, fb, 0), idesc_n1);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_ss(sc + C::COL_FP, adesc(OWN_KEYS ? 2 : 3, ks), bdesc(lp, OWN_KEYS ? 3 : 2, ks), idesc_n32, ks > 0);
+          for (int ks = 1; ks < 8; ++ks)
+            umma_ss_lo<true>(sc + C::COL_FP, a_lo0 + a_off(fa, ks), l2 + b_off(h2, fb, ks), idesc_n1);
         }
+        if constexpr (C::NY > 0) tc_commit(y_empty);
         tc_commit(s_full + (t & 1));
         return true;
       };
@@ -297,29 +357,31 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
         if (!mbar_wait(p_full + (t & 1), (t >> 1) & 1, ab, kAbortBwdPFull)) break;
         tc_fence_after();
         const int st = t % STAGES;
-        const uint32_t lp = smem_u32(sLoop + st * C::STAGE_BYTES);
+        const uint32_t mx = kMnLo | (smem_u32(sX + st * C::X_STAGE) >> 4);
         const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
         const uint32_t acc = t > 0;
-        // Contraction step kk = 2 * term + piece: rows 16 * piece .. of loop tile (slot + term), operand piece at
+        // Contraction step kk = NP * term + piece: rows 16 * piece .. of X tile (slot + term), operand piece at
         // column 16 * piece + 8 * term of the accumulator it was written over.
-        // dK or dQ += gS loop0 + gtS loop1
+        // dK or dQ += gS x0 + gtS x1
+        umma_ts_lo_dyn(tmem + C::COL_OUT0, sc + C::COL_S, mx, idesc_out, acc);
 #pragma unroll
-        for (int kk = 0; kk < (HAS_GT ? 4 : 2); ++kk)
-          umma_ts(tmem + C::COL_OUT0, sc + C::COL_S + 16 * (kk & 1) + 8 * (kk >> 1), mndesc(lp, 0, kk), idesc_out,
-                  acc | (uint32_t)(kk > 0));
+        for (int kk = 1; kk < (HAS_GT ? 2 : 1) * NP; ++kk)
+          umma_ts_lo<true>(tmem + C::COL_OUT0, sc + C::COL_S + 16 * (kk % NP) + 8 * (kk / NP), mx + kk * 128, idesc_out);
         if constexpr (OWN_KEYS) {
           if constexpr (HAS_GT) {
-            // dV += A G + P gO
+            // dV += A G + P gO   (X slots 2, 3)
+            constexpr uint32_t o2 = (2 * C::LQ_BYTES) >> 4;
+            umma_ts_lo_dyn(tmem + C::COL_OUT1, sc + C::COL_TS, mx + o2, idesc_out, acc);
 #pragma unroll
-            for (int kk = 0; kk < (HAS_GO ? 4 : 2); ++kk)
-              umma_ts(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * (kk & 1) + 8 * (kk >> 1), mndesc(lp, 2, kk), idesc_out,
-                      acc | (uint32_t)(kk > 0));
+            for (int kk = 1; kk < (HAS_GO ? 2 : 1) * NP; ++kk)
+              umma_ts_lo<true>(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * (kk % NP) + 8 * (kk / NP), mx + o2 + kk * 128, idesc_out);
           } else {
-            // dV += P gO
+            // dV += P gO   (X slot 3)
+            constexpr uint32_t o3 = (3 * C::LQ_BYTES) >> 4;
+            umma_ts_lo_dyn(tmem + C::COL_OUT1, sc + C::COL_TS + 8, mx + o3, idesc_out, acc);
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk)
-              umma_ts(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * kk + 8, mndesc(lp, 3, kk), idesc_out,
-                      acc | (uint32_t)(kk > 0));
+            for (int kk = 1; kk < NP; ++kk)
+              umma_ts_lo<true>(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * kk + 8, mx + o3 + kk * 128, idesc_out);
           }
         }
         tc_commit(loop_empty + st);
@@ -430,18 +492,17 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
       mbar_arrive(p_full + (t & 1));
     }
 
-    // ---- epilogue: warpgroup `piece` stores columns 64 * piece .. 64 * piece + 63 of every output row ----
+    // ---- epilogue ----
     if (alive && n_tiles > 0) alive = mbar_wait(done, 0, ab, kAbortBwdDone);
     if (alive) {
       tc_fence_after();
       const bool in_range = own_idx < L;
       auto store_rows = [&](void* gptr, uint32_t col0, float mul) {
-        T* g = reinterpret_cast<T*>(gptr) + ((size_t)bh * L + own_idx) * D + 64 * piece;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        T* g = reinterpret_cast<T*>(gptr) + ((size_t)bh * L + own_idx) * D;
+        for (int c = piece; c < D / 32; c += NP) {  // 32-column chunks dealt round the warpgroups
           uint32_t r[32], pk[16];
           if (n_tiles > 0) {
-            tmem_ld32(tbase + col0 + 64 * piece + 32 * c, r);
+            tmem_ld32(tbase + col0 + 32 * c, r);
             tmem_wait_ld();
           } else {
 #pragma unroll

@@ -121,16 +121,6 @@ struct TileUse {
   }
 };
 
-// D[tmem] (+)= A[smem] * B[smem] with descriptor low words (see umma_ss_lo) and a run-time accumulate flag
-__device__ __forceinline__ void umma_ss_lo_dyn(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
-      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 template <typename T, bool DUAL, int MK>
 __global__ void __launch_bounds__(384, 1)
 fwd_tc5_pair64_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPairMaps maps, int* status) {

@@ -183,26 +183,28 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
       constexpr uint32_t idesc_s2 = make_idesc(Fmt<T>::kIdesc, BM, 2 * BN, 0, 0);  // 128 x 128: [S | Q tK^T]
       constexpr uint32_t idesc_o1 = make_idesc(Fmt<T>::kIdesc, BM, D, 0, 1);       // 128 x 128, B MN-major
       constexpr uint32_t idesc_o2 = make_idesc(Fmt<T>::kIdesc, BM, 2 * D, 0, 1);   // 128 x 256: [O | tO']
-      const uint32_t aQ = smem_u32(sQ), aTQ = smem_u32(sTQ);
-      // K-major operand, contraction step ks over D; `half` = bytes between the two 64-column halves
-      auto kdesc = [](uint32_t base, uint32_t half, int ks) {
-        return make_smem_desc(base + (ks >> 2) * half + (ks & 3) * 32, 16, 1024);
-      };
-      // MN-major [V | tV], contraction step kk over the keys; 64-column chunks are HALF_BYTES apart
-      auto vdesc = [](uint32_t base, int kk) { return make_smem_desc(base + kk * 2048, C::HALF_BYTES, 1024); };
+      // Shared-memory descriptors as low words (tc5_common.cuh): the high word is the same for every tile used here and
+      // stepping through a tile is an integer add, which keeps the issuing thread's own instruction count small.
+      // K-major operands: contraction step ks over D = 32 bytes inside a 64-column half.  MN-major [V | tV]: contraction
+      // step kk over the keys = 2048 bytes; the 64-column chunks are HALF_BYTES apart (the leading offset).
+      const uint32_t q_lo = kDescLo | (smem_u32(sQ) >> 4), tq_lo = kDescLo | (smem_u32(sTQ) >> 4);
+      constexpr uint32_t kVLo = (uint32_t)(C::HALF_BYTES >> 4) << 16;
+      auto k_off = [](uint32_t half, int ks) -> uint32_t { return (uint32_t)((ks >> 2) * half + (ks & 3) * 32) >> 4; };
+      constexpr uint32_t QH = BM * 128, KH = C::N_T * C::HALF_BYTES;
       auto issue_s = [&](int t) -> bool {
         const int st = t & 1;
         if (!mbar_wait(k_full + st, (t >> 1) & 1, ab, kAbortKvFull)) return false;
         tc_fence_after();
-        const uint32_t aK = smem_u32(sK + st * C::K_STAGE);
+        const uint32_t k_lo = kDescLo | (smem_u32(sK + st * C::K_STAGE) >> 4);
         const uint32_t sc = tmem + st * C::SC_COLS;
+        umma_ss_lo<false>(sc, q_lo, k_lo, DUAL ? idesc_s2 : idesc_s1);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(sc, kdesc(aQ, BM * 128, ks), kdesc(aK, C::N_T * C::HALF_BYTES, ks), DUAL ? idesc_s2 : idesc_s1, ks > 0);
+        for (int ks = 1; ks < 8; ++ks)
+          umma_ss_lo<true>(sc, q_lo + k_off(QH, ks), k_lo + k_off(KH, ks), DUAL ? idesc_s2 : idesc_s1);
         if constexpr (DUAL) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_ss(sc + BN, kdesc(aTQ, BM * 128, ks), kdesc(aK, C::N_T * C::HALF_BYTES, ks), idesc_s1, 1);
+            umma_ss_lo<true>(sc + BN, tq_lo + k_off(QH, ks), k_lo + k_off(KH, ks), idesc_s1);
         }
         tc_commit(s_full + st);
         tc_commit(k_empty + st);
@@ -217,14 +219,15 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
         if (!mbar_wait(p_full + st, ph, ab, kAbortPFull)) break;
         if (!mbar_wait(v_full + st, ph, ab, kAbortKvFull)) break;
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + st * C::V_STAGE);
+        const uint32_t v_lo = kVLo | (smem_u32(sV + st * C::V_STAGE) >> 4);
         const uint32_t sc = tmem + st * C::SC_COLS;
+        umma_ts_lo_dyn(tmem + C::COL_O, sc, v_lo, DUAL ? idesc_o2 : idesc_o1, t > 0);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + C::COL_O, sc + kk * 8, vdesc(aV, kk), DUAL ? idesc_o2 : idesc_o1, (t > 0 || kk > 0));
+        for (int kk = 1; kk < 4; ++kk)
+          umma_ts_lo<true>(tmem + C::COL_O, sc + kk * 8, v_lo + kk * 128, DUAL ? idesc_o2 : idesc_o1);
         if constexpr (DUAL) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_ts(tmem + C::COL_TO, sc + BN + kk * 8, vdesc(aV, kk), idesc_o1, 1);
+          for (int kk = 0; kk < 4; ++kk) umma_ts_lo<true>(tmem + C::COL_TO, sc + BN + kk * 8, v_lo + kk * 128, idesc_o1);
         }
         tc_commit(v_empty + st);
         tc_commit(pv_done);
