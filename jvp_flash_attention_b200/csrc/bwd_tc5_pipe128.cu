@@ -1,5 +1,5 @@
-// Backward of <gO, O> + <gtO, tO> for head dimension 128, bf16 / fp16, without a user mask or bias, on the Blackwell
-// tensor cores, with the score products of the next tile running under the elementwise work of the current one.
+// Backward of <gO, O> + <gtO, tO> for head dimension 128, bf16 / fp16, on the Blackwell tensor cores, with the score
+// products of the next tile running under the elementwise work of the current one.
 //
 // Same split as the register-tiled backward (bwd_generic.cu; upstream jvp_attention.py:2008-2233): one launch owns
 // 128-key tiles and loops over queries (dK, dV), one owns 128-query tiles and loops over keys (dQ).  Both are
@@ -82,7 +82,12 @@ struct BwdPipeCfg {
 static_assert(BwdPipeCfg<true, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(BwdPipeCfg<false, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
-template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+// MK: 0 = none / causal / key padding; 1 = uint8 mask; 2 = bias of the element type T.  For 1 and 2 every elementwise
+// thread fetches the 16 mask elements of its piece of the tile from global memory before it waits for the scores (own
+// queries: one or two 16-byte loads of the thread's mask row; own keys: one element of each of 16 query rows, the lanes
+// of a warp reading neighbouring keys).  Key stride 1, 16-byte aligned rows and L % 16 == 0 are the host's
+// responsibility.
+template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
 __global__ void __launch_bounds__(BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>::NTHREADS, 1)
 bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMaps maps, int* status) {
   using C = BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>;
@@ -413,9 +418,44 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
       }
     }
 
+    constexpr int MESZ = MK == 1 ? 1 : 2;  // bytes per mask element
+    const unsigned char* mbase = nullptr;
+    long long mpitch = 0;
+    if constexpr (MK != 0) {
+      mbase = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
+              ((long long)tma_b * a.mask.stride[0] + (long long)tma_h * a.mask.stride[1]) * MESZ;
+      mpitch = a.mask.stride[2] * MESZ;
+    }
+
     for (int t = 0; t < n_tiles; ++t) {
       const int st = t % STAGES;
       const int l0 = loop_begin + t * BL;
+      // MK != 0: the piece's 16 mask / bias elements, one per column (indices clamped into the tensor; what lies
+      // outside is switched off by the index tests below)
+      uint32_t mraw[MK == 0 ? 1 : 16];
+      if constexpr (MK != 0) {
+        const int c0 = l0 + 16 * piece;  // first loop-side index of this thread's columns
+        if constexpr (OWN_KEYS) {
+          const unsigned char* pm = mbase + (long long)min(own_idx, L - 1) * MESZ;
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const unsigned char* el = pm + (long long)min(c0 + x, L - 1) * mpitch;
+            mraw[x] = MK == 1 ? ldg_nc_u8(el) : ldg_nc_u16(el);
+          }
+        } else {
+          const unsigned char* pm = mbase + (long long)min(own_idx, L - 1) * mpitch + (size_t)c0 * MESZ;
+          uint32_t w[4 * MESZ];
+#pragma unroll
+          for (int j = 0; j < MESZ; ++j) {
+            uint4 r = make_uint4(0u, 0u, 0u, 0u);
+            if (c0 + (j + 1) * (16 / MESZ) <= L) r = ldg_nc_v4(pm + 16 * j);
+            w[4 * j] = r.x, w[4 * j + 1] = r.y, w[4 * j + 2] = r.z, w[4 * j + 3] = r.w;
+          }
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            mraw[x] = MK == 1 ? ((w[x >> 2] >> ((x & 3) * 8)) & 0xffu) : ((w[x >> 1] >> ((x & 1) * 16)) & 0xffffu);
+        }
+      }
       if constexpr (OWN_KEYS) {
         if (!mbar_wait(loop_full + st, (t / STAGES) & 1, ab, kAbortBwdLoopFull)) {
           alive = false;
@@ -464,7 +504,11 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
             i = own_idx;
             j = l0 + 16 * piece + col;
           }
-          float p = fast_exp2(fmaf(__uint_as_float(s[col]), scale_log2, -lse));
+          float arg = fmaf(__uint_as_float(s[col]), scale_log2, -lse);
+          if constexpr (MK == 2) arg = fmaf(unpack1<T>(mraw[col]), kLog2e, arg);  // scores are in log2 units
+          float p = fast_exp2(arg);
+          if constexpr (MK == 1)
+            if (mraw[col] == 0u) p = 0.f;
           if (partial && (j >= n_valid || (causal && j > i))) p = 0.f;
           pv[h] = p;
           if constexpr (HAS_GT) {
@@ -548,7 +592,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT>
+template <typename T, bool OWN_KEYS, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_pipe_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* status, bool overlap_previous) {
   using C = BwdPipeCfg<OWN_KEYS, HAS_GO, HAS_GT>;
   BwdPipeMaps m;
@@ -570,7 +614,7 @@ static int launch_pipe_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* s
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(bwd)");
     return JVPFA_ERR_CUDA;
   }
-  auto kern = bwd_tc5_pipe128_kernel<T, OWN_KEYS, HAS_GO, HAS_GT>;
+  auto kern = bwd_tc5_pipe128_kernel<T, OWN_KEYS, HAS_GO, HAS_GT, MK>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(bwd_tc5_pipe128)");
@@ -593,33 +637,38 @@ static int launch_pipe_half(const jvpfa_bwd_args& a, cudaStream_t stream, int* s
   return JVPFA_OK;
 }
 
-template <typename T, bool HAS_GO, bool HAS_GT>
+template <typename T, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_pipe_both(const jvpfa_bwd_args& a, cudaStream_t s) {
   int* status = tc5_status_device_ptr();
   if (!status) {
     set_last_cuda_error(cudaErrorUnknown, "status word address");
     return JVPFA_ERR_CUDA;
   }
-  int rc = launch_pipe_half<T, true, HAS_GO, HAS_GT>(a, s, status, false);
+  int rc = launch_pipe_half<T, true, HAS_GO, HAS_GT, MK>(a, s, status, false);
   if (rc) return rc;
-  return launch_pipe_half<T, false, HAS_GO, HAS_GT>(a, s, status, true);
+  return launch_pipe_half<T, false, HAS_GO, HAS_GT, MK>(a, s, status, true);
+}
+
+template <typename T, int MK>
+static int launch_pipe_m(const jvpfa_bwd_args& a, cudaStream_t s) {
+  const bool go = a.go != nullptr, gt = a.gto != nullptr;
+  if (go && gt) return launch_pipe_both<T, true, true, MK>(a, s);
+  if (gt) return launch_pipe_both<T, false, true, MK>(a, s);
+  return launch_pipe_both<T, true, false, MK>(a, s);
 }
 
 template <typename T>
 static int launch_pipe_t(const jvpfa_bwd_args& a, cudaStream_t s) {
-  const bool go = a.go != nullptr, gt = a.gto != nullptr;
-  if (go && gt) return launch_pipe_both<T, true, true>(a, s);
-  if (gt) return launch_pipe_both<T, false, true>(a, s);
-  return launch_pipe_both<T, true, false>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BOOL) return launch_pipe_m<T, 1>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BIAS) return launch_pipe_m<T, 2>(a, s);
+  return launch_pipe_m<T, 0>(a, s);
 }
 
 }  // namespace tc5
 
+// Every request that bwd_tc5_eligible() accepts with head dimension 128 (it checks the mask layout).
 bool bwd_tc5_pipe128_eligible(const jvpfa_bwd_args& a) {
-  if (a.dtype != JVPFA_BF16 && a.dtype != JVPFA_FP16) return false;
-  if (a.D != 128) return false;
-  const int k = a.mask.kind;
-  return k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN;
+  return (a.dtype == JVPFA_BF16 || a.dtype == JVPFA_FP16) && a.D == 128;
 }
 
 int launch_bwd_tc5_pipe128(const jvpfa_bwd_args& a, cudaStream_t s) {
