@@ -45,7 +45,8 @@ struct BwdPipeCfg {
   // queries: dQ takes 128, which leaves two buffers of 4 x 48.
   static constexpr int BL = OWN_KEYS ? 32 : 48;
   static constexpr int NP = BL / 16;                // 16-column pieces = elementwise warpgroups
-  static constexpr int NTHREADS = 64 + 128 * NP;    // producer, issuer, NP elementwise warpgroups
+  static constexpr int NTHREADS = 64 + 128 * NP + 32;  // producer, issuer, NP elementwise warpgroups, second issuer
+  static constexpr int WARP_ISSUER2 = 2 + 4 * NP;
   static constexpr int OWN_BYTES = OWN * D * 2;     // 32 KiB: two 64-column halves of 16 KiB
   static constexpr int OWN_HALF = OWN * 128;
   static constexpr int LQ_BYTES = BL * 128;         // one loop tensor, one 64-column half
@@ -166,10 +167,10 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
     mbar_init(own_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(loop_full + s, OWN_KEYS ? 2 : 1);  // TMA bytes (+ the row statistics, own keys)
-      mbar_init(loop_empty + s, 1);
+      mbar_init(loop_empty + s, OWN_KEYS ? 2 : 1);  // own keys: both issuing threads read the stage
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(s_full + s, 1);
+      mbar_init(s_full + s, 2);  // one commit per issuing thread
       mbar_init(p_full + s, 128 * NP);
     }
     mbar_init(done, 1);
@@ -285,9 +286,16 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == C::WARP_ISSUER2) {
+    // ------------------------------------------------------------------ MMA issuers
+    // One thread cannot issue an MMA more often than about every 58 cycles, whatever its shape; two threads together
+    // can.  The first issuer forms [S | TS] and, after the elementwise threads, the outputs; the second forms [E | FP].
+    // Everything that reads what the elementwise threads write (they write over S and TS only) is issued by the first
+    // thread, after that thread's own scores into the same buffer two tiles earlier and before its next ones: the
+    // tensor pipe keeps one thread's instructions in order, so no barrier between the two issuers is needed.  The
+    // second thread waits for p_full(t) only to know that E and FP of tile t have been read before it overwrites them.
     if (lane == 0 && n_tiles > 0) {
+      const bool second = warp != 1;
       constexpr uint32_t idesc_n1 = make_idesc(Fmt<T>::kIdesc, OWN, BL, 0, 0);      // one 128 x BL accumulator
       constexpr uint32_t idesc_n2 = make_idesc(Fmt<T>::kIdesc, OWN, 2 * BL, 0, 0);  // two adjacent accumulators
       constexpr uint32_t idesc_out = make_idesc(Fmt<T>::kIdesc, OWN, D, 0, 1);      // 128 x 128 outputs
@@ -303,27 +311,42 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
       auto b_off = [](uint32_t half, int slot, int ks) -> uint32_t {
         return (uint32_t)((ks >> 2) * half + slot * C::LQ_BYTES + (ks & 3) * 32) >> 4;
       };
-      auto issue_scores = [&](int t) -> bool {
+      // first issuer: [S | TS] = own0 [loop0 | loop1]^T, TS += own1 loop0^T
+      auto issue_s = [&](int t) -> bool {
         const int st = t % STAGES;
         if (!mbar_wait(loop_full + st, (t / STAGES) & 1, ab, kAbortBwdLoopFull)) return false;
         tc_fence_after();
         const uint32_t lx = kDescLo | (smem_u32(sX + st * C::X_STAGE) >> 4);
-        // loop tensors 2 and 3: slots 2, 3 of the X stage (own keys) or slots 0, 1 of ring Y (own queries)
-        const uint32_t l2 = OWN_KEYS ? lx + ((2 * C::LQ_BYTES) >> 4) : (kDescLo | (smem_u32(sY) >> 4));
-        constexpr uint32_t h2 = OWN_KEYS ? C::X_HALF : C::Y_HALF;
         const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
-        if constexpr (HAS_GT) {
-          umma_ss_lo<false>(sc + C::COL_S, a_lo0 + a_off(0, 0), lx + b_off(C::X_HALF, 0, 0), idesc_n2);
+        constexpr uint32_t id = HAS_GT ? idesc_n2 : idesc_n1;
+        umma_ss_lo<false>(sc + C::COL_S, a_lo0 + a_off(0, 0), lx + b_off(C::X_HALF, 0, 0), id);
 #pragma unroll
-          for (int ks = 1; ks < 8; ++ks)
-            umma_ss_lo<true>(sc + C::COL_S, a_lo0 + a_off(0, ks), lx + b_off(C::X_HALF, 0, ks), idesc_n2);
+        for (int ks = 1; ks < 8; ++ks)
+          umma_ss_lo<true>(sc + C::COL_S, a_lo0 + a_off(0, ks), lx + b_off(C::X_HALF, 0, ks), id);
+        if constexpr (HAS_GT) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_ss_lo<true>(sc + C::COL_TS, a_lo0 + a_off(1, ks), lx + b_off(C::X_HALF, 0, ks), idesc_n1);
-          if constexpr (C::NY > 0) {
-            if (!mbar_wait(y_full, t & 1, ab, kAbortBwdLoopFull)) return false;
-            tc_fence_after();
-          }
+        }
+        tc_commit(s_full + (t & 1));
+        return true;
+      };
+      // second issuer: [E | FP] = own2 [loop2 | loop3]^T, FP += own3 loop2^T; loop tensors 2 and 3 are slots 2, 3 of the
+      // X stage (own keys) or slots 0, 1 of ring Y (own queries)
+      auto issue_e = [&](int t) -> bool {
+        uint32_t l2;
+        if constexpr (OWN_KEYS) {
+          const int st = t % STAGES;
+          if (!mbar_wait(loop_full + st, (t / STAGES) & 1, ab, kAbortBwdLoopFull)) return false;
+          l2 = (kDescLo | (smem_u32(sX + st * C::X_STAGE) >> 4)) + ((2 * C::LQ_BYTES) >> 4);
+        } else {
+          if (!mbar_wait(y_full, t & 1, ab, kAbortBwdLoopFull)) return false;
+          l2 = kDescLo | (smem_u32(sY) >> 4);
+        }
+        tc_fence_after();
+        constexpr uint32_t h2 = OWN_KEYS ? C::X_HALF : C::Y_HALF;
+        const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
+        if constexpr (HAS_GT) {
           constexpr bool wide = !OWN_KEYS || HAS_GO;  // [E | FP] in one instruction
           umma_ss_lo<false>(sc + C::COL_E, a_lo0 + a_off(2, 0), l2 + b_off(h2, 0, 0), wide ? idesc_n2 : idesc_n1);
 #pragma unroll
@@ -336,62 +359,62 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
               umma_ss_lo<true>(sc + C::COL_FP, a_lo0 + a_off(3, ks), l2 + b_off(h2, 0, ks), idesc_n1);
           }
         } else {
-          // S = own0 loop0^T ; FP = V gO^T (own keys: own2 loop3^T) or gO V^T (own queries: own3 loop2^T)
-          umma_ss_lo<false>(sc + C::COL_S, a_lo0 + a_off(0, 0), lx + b_off(C::X_HALF, 0, 0), idesc_n1);
-#pragma unroll
-          for (int ks = 1; ks < 8; ++ks)
-            umma_ss_lo<true>(sc + C::COL_S, a_lo0 + a_off(0, ks), lx + b_off(C::X_HALF, 0, ks), idesc_n1);
-          if constexpr (C::NY > 0) {
-            if (!mbar_wait(y_full, t & 1, ab, kAbortBwdLoopFull)) return false;
-            tc_fence_after();
-          }
+          // FP = V gO^T (own keys: own2 loop3^T) or gO V^T (own queries: own3 loop2^T)
           constexpr int fa = OWN_KEYS ? 2 : 3, fb = OWN_KEYS ? 1 : 0;
           umma_ss_lo<false>(sc + C::COL_FP, a_lo0 + a_off(fa, 0), l2 + b_off(h2, fb, 0), idesc_n1);
 #pragma unroll
           for (int ks = 1; ks < 8; ++ks)
             umma_ss_lo<true>(sc + C::COL_FP, a_lo0 + a_off(fa, ks), l2 + b_off(h2, fb, ks), idesc_n1);
         }
-        if constexpr (C::NY > 0) tc_commit(y_empty);
+        if constexpr (OWN_KEYS) tc_commit(loop_empty + (t % STAGES)); else tc_commit(y_empty);
         tc_commit(s_full + (t & 1));
         return true;
       };
       bool ok = mbar_wait(own_full, 0, ab, kAbortBwdOwn);
-      if (ok) ok = issue_scores(0);
-      for (int t = 0; ok && t < n_tiles; ++t) {
-        if (t + 1 < n_tiles && !issue_scores(t + 1)) break;
-        if (!mbar_wait(p_full + (t & 1), (t >> 1) & 1, ab, kAbortBwdPFull)) break;
-        tc_fence_after();
-        const int st = t % STAGES;
-        const uint32_t mx = kMnLo | (smem_u32(sX + st * C::X_STAGE) >> 4);
-        const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
-        const uint32_t acc = t > 0;
-        // Contraction step kk = NP * term + piece: rows 16 * piece .. of X tile (slot + term), operand piece at
-        // column 16 * piece + 8 * term of the accumulator it was written over.
-        // dK or dQ += gS x0 + gtS x1
-        umma_ts_lo_dyn(tmem + C::COL_OUT0, sc + C::COL_S, mx, idesc_out, acc);
-#pragma unroll
-        for (int kk = 1; kk < (HAS_GT ? 2 : 1) * NP; ++kk)
-          umma_ts_lo<true>(tmem + C::COL_OUT0, sc + C::COL_S + 16 * (kk % NP) + 8 * (kk / NP), mx + kk * 128, idesc_out);
-        if constexpr (OWN_KEYS) {
-          if constexpr (HAS_GT) {
-            // dV += A G + P gO   (X slots 2, 3)
-            constexpr uint32_t o2 = (2 * C::LQ_BYTES) >> 4;
-            umma_ts_lo_dyn(tmem + C::COL_OUT1, sc + C::COL_TS, mx + o2, idesc_out, acc);
-#pragma unroll
-            for (int kk = 1; kk < (HAS_GO ? 2 : 1) * NP; ++kk)
-              umma_ts_lo<true>(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * (kk % NP) + 8 * (kk / NP), mx + o2 + kk * 128, idesc_out);
-          } else {
-            // dV += P gO   (X slot 3)
-            constexpr uint32_t o3 = (3 * C::LQ_BYTES) >> 4;
-            umma_ts_lo_dyn(tmem + C::COL_OUT1, sc + C::COL_TS + 8, mx + o3, idesc_out, acc);
-#pragma unroll
-            for (int kk = 1; kk < NP; ++kk)
-              umma_ts_lo<true>(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * kk + 8, mx + o3 + kk * 128, idesc_out);
-          }
+      if (second) {
+        if (ok) ok = issue_e(0);
+        for (int t = 0; ok && t + 1 < n_tiles; ++t) {
+          if (!issue_e(t + 1)) break;
+          if (!mbar_wait(p_full + (t & 1), (t >> 1) & 1, ab, kAbortBwdPFull)) break;
         }
-        tc_commit(loop_empty + st);
+      } else {
+        if (ok) ok = issue_s(0);
+        for (int t = 0; ok && t < n_tiles; ++t) {
+          if (t + 1 < n_tiles && !issue_s(t + 1)) break;
+          if (!mbar_wait(p_full + (t & 1), (t >> 1) & 1, ab, kAbortBwdPFull)) break;
+          tc_fence_after();
+          const int st = t % STAGES;
+          const uint32_t mx = kMnLo | (smem_u32(sX + st * C::X_STAGE) >> 4);
+          const uint32_t sc = tmem + (t & 1) * C::SC_COLS;
+          const uint32_t acc = t > 0;
+          // Contraction step kk = NP * term + piece: rows 16 * piece .. of X tile (slot + term), operand piece at
+          // column 16 * piece + 8 * term of the accumulator it was written over.
+          // dK or dQ += gS x0 + gtS x1
+          umma_ts_lo_dyn(tmem + C::COL_OUT0, sc + C::COL_S, mx, idesc_out, acc);
+#pragma unroll
+          for (int kk = 1; kk < (HAS_GT ? 2 : 1) * NP; ++kk)
+            umma_ts_lo<true>(tmem + C::COL_OUT0, sc + C::COL_S + 16 * (kk % NP) + 8 * (kk / NP), mx + kk * 128, idesc_out);
+          if constexpr (OWN_KEYS) {
+            if constexpr (HAS_GT) {
+              // dV += A G + P gO   (X slots 2, 3)
+              constexpr uint32_t o2 = (2 * C::LQ_BYTES) >> 4;
+              umma_ts_lo_dyn(tmem + C::COL_OUT1, sc + C::COL_TS, mx + o2, idesc_out, acc);
+#pragma unroll
+              for (int kk = 1; kk < (HAS_GO ? 2 : 1) * NP; ++kk)
+                umma_ts_lo<true>(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * (kk % NP) + 8 * (kk / NP), mx + o2 + kk * 128, idesc_out);
+            } else {
+              // dV += P gO   (X slot 3)
+              constexpr uint32_t o3 = (3 * C::LQ_BYTES) >> 4;
+              umma_ts_lo_dyn(tmem + C::COL_OUT1, sc + C::COL_TS + 8, mx + o3, idesc_out, acc);
+#pragma unroll
+              for (int kk = 1; kk < NP; ++kk)
+                umma_ts_lo<true>(tmem + C::COL_OUT1, sc + C::COL_TS + 16 * kk + 8, mx + o3 + kk * 128, idesc_out);
+            }
+          }
+          tc_commit(loop_empty + st);
+        }
+        tc_commit(done);
       }
-      tc_commit(done);
     }
   } else {
     // ------------------------------------------------------------------ elementwise + epilogue
