@@ -289,27 +289,60 @@ class _TangentBridge(Function):
     """
 
     @staticmethod
-    def forward(q, k, v, tq, tk, tv, to, o, lse, mu, spec, sm_scale):
+    def forward(q, k, v, tq, tk, tv, to, o, lse, mu, spec, sm_scale, relay=None, link=None):
         return to.detach()
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        q, k, v, tq, tk, tv, to, o, lse, mu, spec, sm_scale = inputs
+        q, k, v, tq, tk, tv, to, o, lse, mu, spec, sm_scale, relay, link = inputs
         ctx.save_for_backward(q, k, v, tq, tk, tv, to, o, lse, mu)
-        ctx.spec, ctx.sm_scale = spec, sm_scale
+        ctx.spec, ctx.sm_scale, ctx.link = spec, sm_scale, link
 
     @staticmethod
     @once_differentiable
     def backward(ctx, gto):
         q, k, v, tq, tk, tv, to, o, lse, mu = ctx.saved_tensors
         _check_bwd_layout(q, k, v, o)
-        gq = gk = gv = gtq = gtk = gtv = None
-        if any(ctx.needs_input_grad[:3]):
+        gq = gk = gv = gtq = gtk = gtv = grelay = None
+        if ctx.link is not None and ctx.needs_input_grad[12]:
+            # The node of the primal output runs after this one (it produced `relay`) and takes the cotangent of tO
+            # along with its own: one preprocess and one backward launch for a loss on both outputs.
+            ctx.link.value = (gto, tq, tk, tv, to, mu)
+            grelay = _zero_scalar(gto.device)
+        elif any(ctx.needs_input_grad[:3]):
             gq, gk, gv = _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, None, gto, ctx.spec, ctx.sm_scale)
         if any(ctx.needs_input_grad[3:6]):
             gtq, gtk, gtv = _launch_bwd(q, k, v, None, None, None, o, None, lse, None, gto, None, ctx.spec,
                                         ctx.sm_scale)
-        return gq, gk, gv, gtq, gtk, gtv, None, None, None, None, None, None
+        return gq, gk, gv, gtq, gtk, gtv, None, None, None, None, None, None, grelay, None
+
+
+class _BwdThroughTangent(Function):
+    """(dq, dk, dv) of <gtO, tO> while a graph is being recorded for a second differentiation: like
+    ``_TangentBridge.backward``, this part cannot be differentiated again, and says so when asked."""
+
+    @staticmethod
+    def forward(q, k, v, tq, tk, tv, o, to, lse, mu, gto, spec, sm_scale):
+        return _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, None, gto, spec, sm_scale)
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        pass
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise RuntimeError("the gradient through the tangent output of JVPAttn cannot be differentiated a second time")
+
+
+_ZERO_SCALARS: dict = {}
+
+
+def _zero_scalar(device) -> Tensor:
+    """A fresh tensor object over one cached fp32 zero per device (no kernel launch)."""
+    z = _ZERO_SCALARS.get(device)
+    if z is None:
+        z = _ZERO_SCALARS[device] = torch.zeros((), dtype=torch.float32, device=device)
+    return z.detach()
 
 
 def _forward_impl(q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale, verify_attn_mask):
@@ -534,10 +567,10 @@ class JVPAttn(Function):
         return JVPAttn.BwdOut(dq, dk, dv, None, None, None, None, None, None, None, None, None, None)
 
 
-def _jvp_impl(ctx, gq, gk, gv):
+def _jvp_impl(ctx, gq, gk, gv, relay=None, link=None):
     """The tangent output of a call whose forward has run: the kernel's tangent, behind ``_TangentBridge`` when a
     gradient of it can be asked for."""
-    o_t, q, k, v, q_t, k_t, v_t, o, M, mu = ctx.saved_for_forward
+    o_t, q, k, v, q_t, k_t, v_t, o, M, mu = ctx.saved_for_forward[:10]
     if o_t is None:
         raise RuntimeError(
             "JVPAttn.jvp needs tangents at forward time: call JVPAttn.fwd_dual (or pass q_t, k_t, v_t to apply)"
@@ -550,7 +583,7 @@ def _jvp_impl(ctx, gq, gk, gv):
     tq = gq if gq is not None else (q_t if q_t is not None else torch.zeros_like(q))
     tk = gk if gk is not None else (k_t if k_t is not None else torch.zeros_like(k))
     tv = gv if gv is not None else (v_t if v_t is not None else torch.zeros_like(v))
-    return _TangentBridge.apply(q, k, v, tq, tk, tv, o_t, o, M, mu, ctx.mask_spec, ctx.sm_scale)
+    return _TangentBridge.apply(q, k, v, tq, tk, tv, o_t, o, M, mu, ctx.mask_spec, ctx.sm_scale, relay, link)
 
 
 def _backward_impl(ctx, do):
@@ -583,26 +616,50 @@ class _Attn(Function):
     def forward(q, k, v, q_t, k_t, v_t, attn_mask, causal, sm_scale, verify_attn_mask):
         o, o_t, M, mu, spec, _, _, sm_scale, _, _ = _forward_impl(q, k, v, q_t, k_t, v_t, attn_mask, 0.0, causal, sm_scale,
                                                                  verify_attn_mask)
-        return o, _Box((o_t, M, mu, spec, sm_scale))
+        # Third output (with tangents only): a scalar that the tangent's node takes as an input, so that autograd runs
+        # that node before this one and the cotangent of tO can be handed over here (see backward).
+        # The holder through which that hand-over goes is made here, once per call: under torch.func transforms
+        # setup_context runs once per level, each time with another ctx.
+        relay = _zero_scalar(o.device) if o_t is not None else None
+        link = _Box(None) if o_t is not None else None
+        return o, _Box((o_t, M, mu, spec, sm_scale, link)), relay
 
     @staticmethod
     def setup_context(ctx, inputs, outputs):
         q, k, v, q_t, k_t, v_t, *_ = inputs
-        o, aux = outputs
-        o_t, M, mu, ctx.mask_spec, ctx.sm_scale = aux.value
-        ctx.save_for_forward(o_t, q, k, v, q_t, k_t, v_t, o, M, mu)
+        o, aux, relay = outputs
+        o_t, M, mu, ctx.mask_spec, ctx.sm_scale, ctx.link = aux.value
+        ctx.save_for_forward(o_t, q, k, v, q_t, k_t, v_t, o, M, mu, relay)
         ctx.save_for_backward(q, k, v, o, M)
         ctx.set_materialize_grads(False)
 
     @staticmethod
     def jvp(ctx, gq, gk, gv, *_):
-        return _jvp_impl(ctx, gq, gk, gv), None
+        relay = ctx.saved_for_forward[10]
+        return _jvp_impl(ctx, gq, gk, gv, relay, ctx.link), None, _zero_scalar(relay.device)
 
     @staticmethod
-    def backward(ctx, do, _):
-        if do is None:
-            return (None,) * 10
-        dq, dk, dv = _backward_impl(ctx, do)
+    def backward(ctx, do, _, _relay=None):
+        handed = None
+        if ctx.link is not None:
+            handed, ctx.link.value = ctx.link.value, None
+        if handed is None:
+            if do is None:
+                return (None,) * 10
+            dq, dk, dv = _backward_impl(ctx, do)
+            return (dq, dk, dv) + (None,) * 7
+        gto, tq, tk, tv, to, mu = handed
+        q, k, v, o, M = (fwAD.unpack_dual(x).primal for x in ctx.saved_tensors)
+        _check_bwd_layout(q, k, v, o)
+        if do is not None and torch.is_grad_enabled():
+            # a second differentiation was asked for: the part through O stays a differentiable node of its own
+            dq, dk, dv = _backward_impl(ctx, do)
+            hq, hk, hv = _BwdThroughTangent.apply(q, k, v, tq, tk, tv, o, to, M, mu, gto, ctx.mask_spec, ctx.sm_scale)
+            return (dq + hq, dk + hk, dv + hv) + (None,) * 7
+        go = None if do is None else fwAD.unpack_dual(do).primal
+        with torch.no_grad():
+            dq, dk, dv = _launch_bwd(q.detach(), k.detach(), v.detach(), tq, tk, tv, o.detach(), to, M, mu, go, gto,
+                                     ctx.mask_spec, ctx.sm_scale)
         return (dq, dk, dv) + (None,) * 7
 
 

@@ -56,6 +56,60 @@ def test_grad_through_primal_and_tangent(cpu_kernels, route, kind):
         assert orc.max_abs_err(x, y) < 1e-9
 
 
+@pytest.mark.parametrize("route", ["func_jvp", "fwad"])
+@pytest.mark.parametrize("which", ["both", "o", "to"])
+def test_one_backward_launch_per_step_whatever_the_loss_uses(cpu_kernels, monkeypatch, route, which):
+    """A loss on O and tO reaches the kernels as one launch with both cotangents (the node of the tangent output hands
+    its cotangent to the node of the primal output, which autograd runs after it), also when the backward is run twice
+    over a retained graph; a loss on one of the two as one launch with that cotangent."""
+    q, k, v, tq, tk, tv, w1, w2 = _inputs(3)
+    calls = []
+    inner = stand_in.launch_bwd
+
+    def counting(*args):
+        calls.append((args[10] is not None, args[11] is not None))  # (go given, gto given)
+        return inner(*args)
+
+    monkeypatch.setattr(ja, "_launch_bwd", counting)
+    a = [x.clone().requires_grad_() for x in (q, k, v)]
+
+    def loss_of(o, to):
+        return {"both": (o * w1).sum() + (to * w2).sum(), "o": (o * w1).sum(), "to": (to * w2).sum()}[which]
+
+    go = w1 if which != "to" else None
+    gto = w2 if which != "o" else None
+    _, _, rdq, rdk, rdv = orc.grads_through_both(q, k, v, tq, tk, tv, go, gto)
+    if route == "func_jvp":
+        o, to = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a), (tq, tk, tv))
+        loss = loss_of(o, to)
+        g1 = torch.autograd.grad(loss, a, retain_graph=True)
+        g2 = torch.autograd.grad(loss, a)
+    else:
+        with fwAD.dual_level(), torch.enable_grad():
+            out = ja.JVPAttn.fwd_dual(*[fwAD.make_dual(x, t) for x, t in zip(a, (tq, tk, tv))])
+            o, to = fwAD.unpack_dual(out)
+            loss = loss_of(o, to)
+            g1 = torch.autograd.grad(loss, a, retain_graph=True)
+            g2 = torch.autograd.grad(loss, a)
+    assert calls == [(which != "to", which != "o")] * 2, calls
+    for g in (g1, g2):
+        for x, y in zip(g, (rdq, rdk, rdv)):
+            assert orc.max_abs_err(x, y) < 1e-9
+
+
+def test_second_derivative_with_a_loss_on_both_outputs(cpu_kernels):
+    """create_graph=True with a loss on O and tO: the part through O can be differentiated again (Hessian-vector
+    product), the part through tO refuses loudly instead of being treated as a constant."""
+    q, k, v, tq, tk, tv, w1, w2 = _inputs(4)
+    a = [x.clone().requires_grad_() for x in (q, k, v)]
+    o, to = torch.func.jvp(ja.JVPAttn.fwd_dual, tuple(a), (tq, tk, tv))
+    (gq,) = torch.autograd.grad((o * w1).sum() + (to * w2).sum(), a[:1], create_graph=True)
+    _, _, rdq, _, _ = orc.grads_through_both(q, k, v, tq, tk, tv, w1, w2)
+    assert orc.max_abs_err(gq, rdq) < 1e-9
+    with pytest.raises(RuntimeError, match="second time"):
+        torch.autograd.grad((gq * tq).sum(), a[:1])
+
+
 def test_loss_on_tangent_only_and_tangent_grads(cpu_kernels):
     q, k, v, tq, tk, tv, w1, w2 = _inputs(1)
     a = [x.clone().requires_grad_() for x in (q, k, v)]
