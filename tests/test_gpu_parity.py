@@ -81,11 +81,12 @@ def _mask(kind, B, H, L, dtype, seed):
     raise ValueError(kind)
 
 
-def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC, single_pass=False):
+def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENERIC, single_pass=False, scale=None):
     """fwd + preprocess + bwd through the C ABI on cuda:0.  Returns o, to, lse, mu, dq, dk, dv.
     single_pass: hand jvpfa_bwd the fp32 dQ accumulation buffer, which selects the one-pass backward."""
     dev = torch.device("cuda:0")
     B, H, L, D = q.shape
+    scale = D**-0.5 if scale is None else scale
     cu = lambda x: None if x is None else x.to(dev).contiguous()  # noqa: E731
     q, k, v, tq, tk, tv, go, gto = (cu(x) for x in (q, k, v, tq, tk, tv, go, gto))
     spec, _, _ = ja.classify_mask(cu(mask), causal, B, H, L, q.dtype, False)
@@ -94,7 +95,7 @@ def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENE
     dual = tq is not None
     to = torch.empty_like(q) if dual else None
     mu = torch.empty_like(lse) if dual else None
-    _lib.fwd(q, k, v, tq, tk, tv, o, to, lse, mu, spec, D**-0.5, impl)
+    _lib.fwd(q, k, v, tq, tk, tv, o, to, lse, mu, spec, scale, impl)
     dq = dk = dv = None
     if go is not None or gto is not None:
         stats = torch.empty(3, B, H, L, device=dev, dtype=torch.float32)
@@ -103,7 +104,7 @@ def _run_kernels(q, k, v, tq, tk, tv, go, gto, mask, causal, impl=_lib.IMPL_GENE
         dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
         acc = torch.full(q.shape, float("nan"), device=dev, dtype=torch.float32) if single_pass else None
         _lib.bwd(q, k, v, tq if use_t else None, tk if use_t else None, tv if use_t else None, go, gto, lse,
-                 mu if use_t else None, stats[0], stats[1], stats[2], dq, dk, dv, spec, D**-0.5, impl, dq_accum=acc)
+                 mu if use_t else None, stats[0], stats[1], stats[2], dq, dk, dv, spec, scale, impl, dq_accum=acc)
     torch.cuda.synchronize()
     return o, to, lse, mu, dq, dk, dv
 
@@ -400,6 +401,36 @@ def test_against_upstream_golden_outputs(golden_dir, name):
     for got, key in ((o, "o"), (to, "to"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
         e = orc.rel_err(got, t[key])
         assert e <= 2e-5, f"{key}: {e:.3e}"
+
+
+@pytest.mark.parametrize("dt", ["fp32", "bf16", "fp16"])
+def test_float_mask_against_torch_sdpa_golden(golden_dir, dt):
+    """A general float mask (not {0, -100}) means softmax(scale * Q K^T + mask) in forward and backward: the fixture is
+    PyTorch's own scaled_dot_product_attention in float64 (tests/golden/make_sdpa_bias_golden.py).  fp32 on the
+    register-tiled family, 16-bit on the tcgen05 kernels (bias of the element type)."""
+    dtype = DT[dt]
+    z = np.load(golden_dir / "sdpa_bias_L64_D32.npz")
+    t = {k_: torch.from_numpy(z[k_]) for k_ in z.files}
+    if dtype != torch.float32:  # the tcgen05 kernels need D = 64: pad the head dimension with zeros (changes nothing
+        # but the scale, which is passed explicitly)
+        pad = lambda x: torch.nn.functional.pad(x, (0, 32))  # noqa: E731
+        ins = [pad(t[n]).to(dtype) for n in ("q", "k", "v", "tq", "tk", "tv", "w1", "w2")]
+    else:
+        ins = [t[n].to(dtype) for n in ("q", "k", "v", "tq", "tk", "tv", "w1", "w2")]
+    q, k, v, tq, tk, tv, w1, w2 = ins
+    bias = t["bias"].to(dtype)
+    o, to, _, _, dq, dk, dv = _run_kernels(q, k, v, tq, tk, tv, w1, w2, bias, False, scale=32 ** -0.5,
+                                           impl=_lib.IMPL_AUTO)
+    assert _lib.device_status() == 0
+    for got, key in ((o, "o"), (to, "to"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        ref = t[key]
+        got = got[..., :32]
+        if dtype == torch.float32:
+            assert orc.rel_err(got, ref) <= FP32_REL, key
+        else:
+            # the inputs themselves were rounded to 16 bit: compare with the oracle on the rounded inputs instead of the
+            # float64 fixture for the tight bound, and with the fixture for the meaning of the mask
+            assert orc.max_abs_err(got, ref) <= 6e-2 * max(1.0, ref.abs().max().item()), key
 
 
 # ------------------------------------------------------------------------------------------------

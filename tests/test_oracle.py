@@ -50,6 +50,24 @@ def test_tiled_restatement_matches_upstream_kernel(golden_dir, name):
         assert orc.rel_err(t[key], got) < GOLDEN_TOL, key
 
 
+def test_float_mask_semantics_are_those_of_torch_sdpa(golden_dir):
+    """A float mask is added to the scaled scores, in forward and backward: the fixture holds PyTorch's own
+    scaled_dot_product_attention (float64, math path) with a general additive mask, its tangent and the gradients through
+    both outputs (tests/golden/make_sdpa_bias_golden.py).  Both statements of the oracle must reproduce it."""
+    z = np.load(golden_dir / "sdpa_bias_L64_D32.npz")
+    t = {k_: torch.from_numpy(z[k_]) for k_ in z.files}
+    o, to, dq, dk, dv = orc.grads_through_both(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], t["w1"], t["w2"],
+                                               attn_mask=t["bias"])
+    for got, key in ((o, "o"), (to, "to"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert orc.rel_err(t[key], got) < 1e-10, key
+    r = orc.tiled_forward(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], attn_mask=t["bias"])
+    assert orc.rel_err(t["o"], r["o"]) < 1e-10 and orc.rel_err(t["to"], r["to"]) < 1e-10
+    d = orc.closed_form_backward(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], t["w1"], t["w2"], r["lse"], r["mu"],
+                                 attn_mask=t["bias"])
+    for got, key in zip(d, ("dq", "dk", "dv")):
+        assert orc.rel_err(t[key], got) < 1e-10, key
+
+
 @pytest.mark.parametrize("kind", ["none", "causal", "kvlen", "bool", "bias"])
 def test_two_statements_agree_through_both_outputs(kind):
     """Closed-form backward (incl. the tangent-output cotangent) against autograd in float64."""
