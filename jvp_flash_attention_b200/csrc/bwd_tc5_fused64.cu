@@ -31,7 +31,19 @@ namespace tc5 {
 struct BwdFMaps {
   CUtensorMap k, v, tk, tv;  // key side, box 128 rows
   CUtensorMap q, go, tq, g;  // query side, box 64 rows (g = cotangent of tO)
+  CUtensorMap dq;            // the fp32 dQ accumulation buffer, box 64 rows x 32 columns
 };
+
+// TMA reduction (add) of one fp32 tile from shared memory into global memory; rows past the tensor's extent are
+// not touched.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t smem_src, int x, int y, int z, int w) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+               "r"(smem_src), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <bool HAS_GO, bool HAS_GT>
 struct BwdFCfg {
@@ -56,7 +68,11 @@ struct BwdFCfg {
   static constexpr int OFF_OUT = OFF_RING + STAGES * STAGE_BYTES;
   static constexpr int OBUF_BYTES = N_OUT * OUT_BYTES;
   static constexpr int OFF_STAT = OFF_OUT + N_OBUF * OBUF_BYTES;
-  static constexpr int TILE_BYTES = OFF_STAT + STAGES * STAT_STAGE_BYTES;
+  // dQ of a sub-tile on its way out: fp32 [64 queries][64 columns] as two 128-byte-swizzled halves of 32 columns
+  static constexpr int OFF_DQS = OFF_STAT + STAGES * STAT_STAGE_BYTES;
+  static constexpr int DQS_BYTES = BL * D * 4;
+  static_assert(OFF_DQS % 1024 == 0, "swizzled staging tile alignment");
+  static constexpr int TILE_BYTES = OFF_DQS + DQS_BYTES;
   static constexpr int SMEM_NEEDED = TILE_BYTES + 512 + 1024;
   // At least 120 KiB so that a second CTA can never share the SM (the CTA allocates all of TMEM).
   static constexpr int SMEM_BYTES = SMEM_NEEDED > 120 * 1024 ? SMEM_NEEDED : 120 * 1024;
@@ -115,14 +131,19 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
   uint64_t* stat_full = loop_empty + STAGES;  // [STAGES]
   uint64_t* s_full = stat_full + STAGES;
   uint64_t* s_free = s_full + 1;    // 256 elementwise threads hold the scores in registers
-  uint64_t* p_full = s_free + 1;    // 256: gS, gtS, A, P are in shared memory (one phase per sub-tile)
-  uint64_t* out_free = p_full + 1;  // [2] per result buffer: dK/dV issuer + dQ issuer have read it
+  // [2] by g & 1, 256 each: gS, gtS, A, P of the sub-tile are in shared memory. A pair, because the elementwise
+  // threads can finish sub-tile g + 1 before the dQ issuer has looked at g (sub-tile g + 1 needs the dV products of
+  // g, not its dQ product): on one barrier the issuer would then be two phases behind, where a parity wait no longer
+  // tells "done" from "not yet". Sub-tile g + 2 does need dQ of g (out_free), so one phase per barrier is the most.
+  uint64_t* p_full = s_free + 1;
+  uint64_t* out_free = p_full + 2;  // [2] per result buffer: dK/dV issuer + dQ issuer have read it
   uint64_t* av_free = out_free + 2;  // the dV products have read the packed A / P columns
   uint64_t* dq_full = av_free + 1;
   uint64_t* dq_free = dq_full + 1;   // 128 read-back threads
   uint64_t* done = dq_free + 1;      // the item's dK / dV are complete
   uint64_t* acc_free = done + 1;     // 256: the epilogue has read them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
+  uint64_t* rb_bar = acc_free + 1;   // 128: meeting point of the read-back warpgroup (bounded, unlike bar.sync)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rb_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -192,6 +213,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     mbar_init(s_full, 1);
     mbar_init(s_free, 256);
     mbar_init(p_full, 256);
+    mbar_init(p_full + 1, 256);
     mbar_init(out_free, 2);
     mbar_init(out_free + 1, 2);
     mbar_init(av_free, 1);
@@ -199,6 +221,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     mbar_init(dq_free, 128);
     mbar_init(done, 1);
     mbar_init(acc_free, 256);
+    mbar_init(rb_bar, 128);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -222,7 +245,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
   }
 
   // Phase counters kept alike by all roles: g counts the sub-tiles of this CTA (ring stage g % STAGES, dQ buffer
-  // g & 1; s_full, s_free, p_full, out_free complete once per sub-tile), kact the items that have sub-tiles.
+  // g & 1; s_full, s_free complete once per sub-tile, p_full and out_free of buffer g & 1 every other one), kact the items that have sub-tiles.
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer + per-query statistics
     if (lane == 0) {
@@ -378,7 +401,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
           if (!get_item(k, it) || it.n_sub == 0) continue;
           for (int s = 0; s < it.n_sub; ++s, ++g) {
             const int st = g % STAGES;
-            if (!mbar_wait(p_full, g & 1, ab, kAbortBwdPFull) ||
+            if (!mbar_wait(p_full + (g & 1), (g >> 1) & 1, ab, kAbortBwdPFull) ||
                 (s == 0 && kact > 0 && !mbar_wait(acc_free, (kact - 1) & 1, ab, kAbortBwdDone))) {
               ok = false;
               break;
@@ -420,7 +443,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         for (int k = 0; ok && k < k_max; ++k) {
           if (!get_item(k, it) || it.n_sub == 0) continue;
           for (int s = 0; s < it.n_sub; ++s, ++g) {
-            if (!mbar_wait(p_full, g & 1, ab, kAbortBwdPFull) ||
+            if (!mbar_wait(p_full + (g & 1), (g >> 1) & 1, ab, kAbortBwdPFull) ||
                 (g >= 1 && !mbar_wait(dq_free, (g - 1) & 1, ab, kAbortBwdDone))) {
               ok = false;
               break;
@@ -575,7 +598,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         }
         fence_async_smem();
         tc_fence_before();
-        mbar_arrive(p_full);
+        mbar_arrive(p_full + (g & 1));
       }
       if (!alive) break;
       // item epilogue: group 0 stores dK, group 1 dV
@@ -597,9 +620,17 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     // ------------------------------------------------------------------ dQ read-back
     const int quarter = warp & 3;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + C::COL_DQ;
+    const uint32_t dqs = smem_u32(smem + C::OFF_DQS);
     int g = 0;
+    uint32_t rb_phase = 0;
     bool alive = true;
     FItem it;
+    auto rb_sync = [&]() -> bool {
+      mbar_arrive(rb_bar);
+      const bool ok = mbar_wait(rb_bar, rb_phase & 1, ab, kAbortBwdDone);
+      ++rb_phase;
+      return ok;
+    };
     for (int k = 0; alive && k < k_max; ++k) {
       if (!get_item(k, it) || it.n_sub == 0) continue;
       for (int s = 0; s < it.n_sub; ++s, ++g) {
@@ -614,21 +645,39 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(dq_free);
-        // an M = 64 accumulator: row 16 * quarter + l of the sub-tile is in lane l < 16 of this quarter
-        const int i = it.loop_begin + s * BL + 16 * quarter + lane;
-        if (lane < 16 && i < L) {
-          float* dst = dq_acc + ((size_t)it.bh * L + i) * D;
+        // An M = 64 accumulator: row 16 * quarter + l of the sub-tile is in lane l < 16 of this quarter.  The tile goes
+        // to a staging area in shared memory and from there to the accumulation buffer as two TMA reductions (one
+        // instruction each, coalesced and asynchronous) instead of sixteen vector reductions per thread.
+        if (g > 0) {  // the previous sub-tile's reductions must have read the staging area
+          if (tid == 384) bulk_wait_read();
+          if (!rb_sync()) {
+            alive = false;
+            break;
+          }
+        }
+        if (lane < 16) {
+          const int r = 16 * quarter + lane;
+          const uint32_t rowa = dqs + r * 128, sw = (uint32_t)(r & 7);
 #pragma unroll
-          for (int x = 0; x < 8; ++x)
-            red_add_v4(dst + 4 * x, __uint_as_float(r0[4 * x]), __uint_as_float(r0[4 * x + 1]), __uint_as_float(r0[4 * x + 2]),
-                       __uint_as_float(r0[4 * x + 3]));
-#pragma unroll
-          for (int x = 0; x < 8; ++x)
-            red_add_v4(dst + 32 + 4 * x, __uint_as_float(r1[4 * x]), __uint_as_float(r1[4 * x + 1]),
-                       __uint_as_float(r1[4 * x + 2]), __uint_as_float(r1[4 * x + 3]));
+          for (int c = 0; c < 8; ++c) {
+            sts_v4(rowa + (((uint32_t)c ^ sw) << 4), r0[4 * c], r0[4 * c + 1], r0[4 * c + 2], r0[4 * c + 3]);
+            sts_v4(rowa + 8192 + (((uint32_t)c ^ sw) << 4), r1[4 * c], r1[4 * c + 1], r1[4 * c + 2], r1[4 * c + 3]);
+          }
+        }
+        fence_async_smem();
+        if (!rb_sync()) {
+          alive = false;
+          break;
+        }
+        if (tid == 384) {
+          const int i0 = it.loop_begin + s * BL;
+          tma_reduce_add_4d(&maps.dq, dqs, 0, i0, it.h, it.b);
+          tma_reduce_add_4d(&maps.dq, dqs + 8192, 32, i0, it.h, it.b);
+          bulk_commit();
         }
       }
     }
+    if (tid == 384) bulk_wait_all();  // the reductions must have landed (and read shared memory) before the CTA ends
   }
 
   tc_fence_before();
@@ -688,6 +737,7 @@ static int launch_fused64(const jvpfa_bwd_args& a, cudaStream_t stream) {
   if (HAS_GT)
     ok = ok && encode_map4(&m.tk, dt, a.tk, a.L, a.H, a.B, st, C::OWN) && encode_map4(&m.tv, dt, a.tv, a.L, a.H, a.B, st, C::OWN) &&
          encode_map4(&m.tq, dt, a.tq, a.L, a.H, a.B, st, C::BL) && encode_map4(&m.g, dt, a.gto, a.L, a.H, a.B, nullptr, C::BL);
+  ok = ok && encode_map4d_f32(&m.dq, a.dq_accum, C::D, a.L, a.H, a.B, C::BL);
   if (!ok) {
     set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled(bwd fused64)");
     return JVPFA_ERR_CUDA;

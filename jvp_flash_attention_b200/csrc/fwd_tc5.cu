@@ -475,6 +475,20 @@ bool encode_map4d(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D
   return r == CUDA_SUCCESS;
 }
 
+// Row-major fp32 (B, H, L, D) tensor as a 4-D map with 32-column (128-byte) swizzled boxes: target of TMA reductions.
+bool encode_map4d_f32(CUtensorMap* m, const void* ptr, int D, int L, int H, int B, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 4, (cuuint64_t)L * D * 4, (cuuint64_t)H * L * D * 4};
+  cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L, int H, int B, const int64_t* st,
                  int box_rows) {
   return encode_map4d(m, dt, ptr, 64, L, H, B, st, box_rows);

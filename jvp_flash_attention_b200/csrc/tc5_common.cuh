@@ -110,6 +110,8 @@ bool encode_map4(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int L,
 // The same for head dimension D (64-column boxes: a D = 128 tile is two loads).
 bool encode_map4d(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int D, int L, int H, int B, const int64_t* stride_bhl,
                   int box_rows);
+// Row-major fp32 (B, H, L, D) tensor, 32-column boxes with 128-byte swizzle (target of TMA reductions).
+bool encode_map4d_f32(CUtensorMap* m, const void* ptr, int D, int L, int H, int B, int box_rows);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
