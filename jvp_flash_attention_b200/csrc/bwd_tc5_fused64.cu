@@ -142,9 +142,9 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
   uint64_t* dq_free = dq_full + 1;   // 128 read-back threads
   uint64_t* done = dq_free + 1;      // the item's dK / dV are complete
   uint64_t* acc_free = done + 1;     // 256: the epilogue has read them
-  uint64_t* rb_bar = acc_free + 1;   // 128: meeting point of the read-back warpgroup (bounded, unlike bar.sync)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rb_bar + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* rb_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);  // the read-back group's poller tells the rest
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
@@ -221,7 +221,6 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     mbar_init(dq_free, 128);
     mbar_init(done, 1);
     mbar_init(acc_free, 256);
-    mbar_init(rb_bar, 128);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -262,7 +261,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     for (int k = 0; ok && k < k_max; ++k) {
       if (!get_item(k, it) || it.n_sub == 0) continue;
       // The own tiles are single-buffered: every MMA that reads the previous item's must be complete.
-      if (kact > 0 && !mbar_wait(own_free, (kact - 1) & 1, ab, kAbortBwdOwn)) break;
+      if (kact > 0 && !mbar_wait_backoff(own_free, (kact - 1) & 1, ab, kAbortBwdOwn)) break;
       if (lane == 0) {
         mbar_expect_tx(own_full, C::N_OWN * C::OWN_BYTES);
         tma_load_4d(sOwn + C::SLOT_K * C::OWN_BYTES, &maps.k, own_full, 0, it.own0, it.h, it.b);
@@ -294,7 +293,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
       load_stats(0, cur);
       for (int s = 0; s < it.n_sub; ++s, ++g) {
         const int st = g % STAGES;
-        if (!mbar_wait(loop_empty + st, ((g / STAGES) & 1) ^ 1, ab, kAbortBwdLoopEmpty)) {
+        if (!mbar_wait_backoff(loop_empty + st, ((g / STAGES) & 1) ^ 1, ab, kAbortBwdLoopEmpty)) {
           ok = false;
           break;
         }
@@ -622,19 +621,19 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + C::COL_DQ;
     const uint32_t dqs = smem_u32(smem + C::OFF_DQS);
     int g = 0;
-    uint32_t rb_phase = 0;
     bool alive = true;
     FItem it;
-    auto rb_sync = [&]() -> bool {
-      mbar_arrive(rb_bar);
-      const bool ok = mbar_wait(rb_bar, rb_phase & 1, ab, kAbortBwdDone);
-      ++rb_phase;
-      return ok;
-    };
+    // The 128 threads meet at a hardware barrier.  That is safe although it has no time limit: every decision to leave
+    // the loop is taken from rb_ok, which one thread writes before a meeting and all read after it, so nobody can be
+    // missing at the next one; and nothing between two meetings waits on another role.
+    auto rb_meet = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
     for (int k = 0; alive && k < k_max; ++k) {
       if (!get_item(k, it) || it.n_sub == 0) continue;
       for (int s = 0; s < it.n_sub; ++s, ++g) {
-        if (!mbar_wait(dq_full, g & 1, ab, kAbortBwdDone)) {
+        // one thread polls for the warpgroup (every polling warp is traffic on the shared-memory port)
+        if (tid == 384) *rb_ok = mbar_wait(dq_full, g & 1, ab, kAbortBwdDone) ? 1 : 0;
+        rb_meet();
+        if (*rb_ok == 0) {
           alive = false;
           break;
         }
@@ -650,10 +649,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         // instruction each, coalesced and asynchronous) instead of sixteen vector reductions per thread.
         if (g > 0) {  // the previous sub-tile's reductions must have read the staging area
           if (tid == 384) bulk_wait_read();
-          if (!rb_sync()) {
-            alive = false;
-            break;
-          }
+          rb_meet();
         }
         if (lane < 16) {
           const int r = 16 * quarter + lane;
@@ -665,10 +661,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
           }
         }
         fence_async_smem();
-        if (!rb_sync()) {
-          alive = false;
-          break;
-        }
+        rb_meet();
         if (tid == 384) {
           const int i0 = it.loop_begin + s * BL;
           tma_reduce_add_4d(&maps.dq, dqs, 0, i0, it.h, it.b);

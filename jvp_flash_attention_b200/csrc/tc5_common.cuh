@@ -188,6 +188,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
   }
 }
+// For roles far from the critical path (a producer several stages ahead): sleeps between attempts, because every
+// attempt is an access on the shared-memory port that the MMA operands come through.
+template <int NS = 128>
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, const AbortState& ab, int code) {
+  const uint32_t addr = smem_u32(bar);
+  if (mbar_try_wait_u32(addr, parity)) return true;
+  const long long t0 = clock64();
+  int polls = 0;
+  while (true) {
+    __nanosleep(NS);
+    if (mbar_try_wait_u32(addr, parity)) return true;
+    if ((++polls & 63) == 0) {
+      if (*ab.cta_flag != 0) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *ab.cta_flag = code;
+        atomicCAS(ab.global_status, 0, code);
+        return false;
+      }
+    }
+  }
+}
 static __device__ __noinline__ bool mbar_wait_slow_u32(uint32_t bar, uint32_t parity, volatile int* cta_flag,
                                                        int* global_status, int code) {
   const long long t0 = clock64();
