@@ -40,7 +40,8 @@ typedef enum {
   JVPFA_ERR_STRUCT = -7,      /* struct_size does not match this library            */
   JVPFA_ERR_ALIGN = -8,       /* a tensor base pointer is not 16-byte aligned       */
   JVPFA_ERR_UNSUPPORTED = -9, /* valid request that this build cannot serve         */
-  JVPFA_ERR_TOO_LARGE = -10   /* problem exceeds a fixed internal capacity          */
+  JVPFA_ERR_TOO_LARGE = -10,  /* problem exceeds a fixed internal capacity          */
+  JVPFA_ERR_DEVICE_STATUS = -11 /* an earlier tcgen05 launch gave up a bounded wait; see jvpfa_device_status */
 } jvpfa_status;
 
 typedef enum {
@@ -294,10 +295,19 @@ const char* jvpfa_last_cuda_error(void);
  * kernels then drained and exited early, the output rows of the affected CTAs (lse in the
  * forward; dq / dk / dv rows in the backward) hold NaN, and while the word stays non-zero every
  * later tcgen05 launch on the device writes NaN and returns at once.  clear != 0 resets the
- * word.  This call synchronises with the device (it is a cudaMemcpyFromSymbol): poll it where
- * the caller synchronises anyway, not per launch.  No upstream counterpart: Triton kernels have
- * no such waits. */
+ * word.  This call synchronises with the device (it copies the word): poll it where the caller
+ * synchronises anyway, not per launch.  A caller that never polls is still told: the thread that
+ * gives up also writes the code to a host-visible mirror (pinned, mapped memory), and jvpfa_fwd,
+ * jvpfa_bwd and jvpfa_bwd_noalloc look at that mirror (a host read, no synchronisation) before they
+ * launch a tcgen05 kernel and return JVPFA_ERR_DEVICE_STATUS while it is non-zero, i.e. from the
+ * first call after the failing kernel has run until jvpfa_device_status(.., 1) clears the word.
+ * No upstream counterpart: Triton kernels have no such waits. */
 int jvpfa_device_status(int* status, int clear);
+
+/* Sets the status word and its mirror to `code` from the host, exactly what a kernel thread that gives
+ * up a wait leaves behind (without the NaN rows).  For exercising a caller's handling of
+ * JVPFA_ERR_DEVICE_STATUS without a device fault; code 0 is the same as clearing.  Synchronises. */
+int jvpfa_device_status_inject(int code);
 
 /* 1 if jvpfa_fwd / jvpfa_bwd with impl == JVPFA_IMPL_AUTO would take the
  * tcgen05 kernels for this shape, else 0 (pure host logic; no CUDA call). */

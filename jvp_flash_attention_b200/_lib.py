@@ -45,6 +45,7 @@ EXPORTS = (
     "jvpfa_fwd_uses_tcgen05",
     "jvpfa_bwd_uses_tcgen05",
     "jvpfa_device_status",
+    "jvpfa_device_status_inject",
     "jvpfa_bwd_noalloc",
     "jvpfa_mask_check",
     "jvpfa_mask_tiles",
@@ -229,6 +230,8 @@ def load() -> C.CDLL:
     lib.jvpfa_bwd_uses_tcgen05.restype = C.c_int
     lib.jvpfa_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
     lib.jvpfa_device_status.restype = C.c_int
+    lib.jvpfa_device_status_inject.argtypes = [C.c_int]
+    lib.jvpfa_device_status_inject.restype = C.c_int
     lib.jvpfa_bwd_noalloc.argtypes = [C.POINTER(BwdNoAllocArgs), C.c_void_p]
     lib.jvpfa_bwd_noalloc.restype = C.c_int
     lib.jvpfa_mask_check.argtypes = [C.POINTER(MaskCheckArgs), C.c_void_p]
@@ -245,6 +248,12 @@ def device_status(clear: bool = True) -> int:
     out = C.c_int(0)
     check(lib.jvpfa_device_status(C.byref(out), 1 if clear else 0), "jvpfa_device_status")
     return out.value
+
+
+def device_status_inject(code: int) -> None:
+    """Sets the status word from the host as a kernel that gave up a wait would (``jvpfa_device_status_inject``):
+    every tcgen05 call then fails with JVPFA_ERR_DEVICE_STATUS until ``device_status(clear=True)``."""
+    check(load().jvpfa_device_status_inject(int(code)), "jvpfa_device_status_inject")
 
 
 def check(status: int, what: str) -> None:

@@ -174,7 +174,10 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   if (a->impl == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
   // strided inputs are read in place by the tcgen05 kernels (their tensor maps carry the strides)
   if (has_strides(a->in_stride) && !(tc5 && a->impl != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
-  if (tc5 && a->impl != JVPFA_IMPL_GENERIC) return launch_fwd_tc5(*a, s);
+  if (tc5 && a->impl != JVPFA_IMPL_GENERIC) {
+    if (tc5_status_peek() != 0) return JVPFA_ERR_DEVICE_STATUS;
+    return launch_fwd_tc5(*a, s);
+  }
   return launch_fwd_generic(*a, s);
 }
 
@@ -190,7 +193,10 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc5 = bwd_tc5_eligible(*a);
   const int fam = impl_family(a->impl);
-  if (tc5 && fam != JVPFA_IMPL_GENERIC) return launch_bwd_tc5(*a, s);
+  if (tc5 && fam != JVPFA_IMPL_GENERIC) {
+    if (tc5_status_peek() != 0) return JVPFA_ERR_DEVICE_STATUS;
+    return launch_bwd_tc5(*a, s);
+  }
   return launch_bwd_generic(*a, s);
 }
 
@@ -232,6 +238,12 @@ int jvpfa_device_status(int* status, int clear) {
   return tc5_read_status(status, clear);
 }
 
+int jvpfa_device_status_inject(int code) {
+  const int rc = check_arch();
+  if (rc) return rc;
+  return tc5_inject_status(code);
+}
+
 const char* jvpfa_strerror(int status) {
   switch (status) {
     case JVPFA_OK:
@@ -256,6 +268,9 @@ const char* jvpfa_strerror(int status) {
       return "request not supported by the selected kernel family";
     case JVPFA_ERR_TOO_LARGE:
       return "problem exceeds a fixed internal capacity";
+    case JVPFA_ERR_DEVICE_STATUS:
+      return "an earlier tcgen05 launch on this device gave up a bounded wait: its outputs hold NaN; read and clear the "
+             "status word with jvpfa_device_status";
     default:
       return "unknown status";
   }

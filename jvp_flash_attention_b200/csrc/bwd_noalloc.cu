@@ -105,6 +105,7 @@ extern "C" int jvpfa_bwd_noalloc(const jvpfa_bwd_noalloc_args* a, void* stream) 
   if (rc) return rc;
   rc = check_bwd_request(&g);
   if (rc) return rc;
+  if (jvpfa_bwd_uses_tcgen05(&g) && tc5_status_peek() != 0) return JVPFA_ERR_DEVICE_STATUS;
   rc = jvpfa_bwd_preprocess(&p, stream);
   if (rc) return rc;
   return jvpfa_bwd(&g, stream);

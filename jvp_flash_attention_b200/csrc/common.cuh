@@ -383,6 +383,8 @@ int launch_mask_tiles(const jvpfa_mask_tiles_args& a, cudaStream_t stream);
 int launch_fwd_tc5(const jvpfa_fwd_args& a, cudaStream_t stream);
 bool fwd_tc5_eligible(const jvpfa_fwd_args& a);
 int tc5_read_status(int* out, int clear);
+int tc5_status_peek();
+int tc5_inject_status(int code);
 int* tc5_status_device_ptr();
 int launch_bwd_tc5(const jvpfa_bwd_args& a, cudaStream_t stream);
 int launch_bwd_tc5_d64(const jvpfa_bwd_args& a, cudaStream_t stream);

@@ -23,19 +23,53 @@
 
 namespace jvpfa {
 
-__device__ int g_tc5_status = 0;
+// [0]: the status word.  [2], [3]: device address of its host-visible mirror (pinned, mapped host memory), written by
+// a thread that gives up a wait, so that the host can see a failure without synchronising.
+__device__ __align__(16) int g_tc5_status[4] = {0, 0, 0, 0};
+
+namespace {
+struct StatusSlot {
+  int* dev = nullptr;            // device address of g_tc5_status on that device
+  volatile int* mirror = nullptr;  // host address of the mirror (null if it could not be set up)
+};
+StatusSlot* status_slot() {
+  static StatusSlot cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  StatusSlot& sl = cache[dev];
+  if (!sl.dev) {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc5_status) != cudaSuccess) return nullptr;
+    int* host = nullptr;
+    int* host_dev = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped) == cudaSuccess) {
+      *host = 0;
+      if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&host_dev), host, 0) == cudaSuccess &&
+          cudaMemcpy(p + 2, &host_dev, sizeof(host_dev), cudaMemcpyHostToDevice) == cudaSuccess) {
+        sl.mirror = host;
+      } else {
+        cudaFreeHost(host);
+      }
+    }
+    (void)cudaGetLastError();  // a missing mirror only costs the early warning
+    sl.dev = p;
+  }
+  return &sl;
+}
+}  // namespace
+
 // Device address of the status word on the current device (other translation units receive it
 // as a kernel argument).  Looked up once per device.
 int* tc5_status_device_ptr() {
-  static int* cache[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!cache[dev]) {
-    int* p = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc5_status) != cudaSuccess) return nullptr;
-    cache[dev] = p;
-  }
-  return cache[dev];
+  StatusSlot* sl = status_slot();
+  return sl ? sl->dev : nullptr;
+}
+
+// The mirror's value: non-zero once a kernel on the current device has given up a wait (no CUDA call, no
+// synchronisation; it can lag behind the device by the kernels still in flight).
+int tc5_status_peek() {
+  StatusSlot* sl = status_slot();
+  return (sl && sl->mirror) ? *sl->mirror : 0;
 }
 
 namespace tc5 {
@@ -78,7 +112,7 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   constexpr int KSTEPS_N = BN / 16;  // contraction steps over the keys of a tile
   constexpr int HALVES = D / 64;     // 64-column TMA boxes per row
 
-  const bool dead_on_entry = *(volatile int*)&g_tc5_status != 0;  // an earlier bounded wait gave up
+  const bool dead_on_entry = *(volatile int*)&g_tc5_status[0] != 0;  // an earlier bounded wait gave up
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -142,7 +176,7 @@ fwd_tc5_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdMaps maps) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const AbortState ab{abort_flag, &g_tc5_status};
+  const AbortState ab{abort_flag, &g_tc5_status[0]};
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -561,21 +595,43 @@ int launch_fwd_tc5(const jvpfa_fwd_args& a, cudaStream_t s) {
 }
 
 int tc5_read_status(int* out, int clear) {
+  StatusSlot* sl = status_slot();
+  if (!sl) {
+    set_last_cuda_error(cudaErrorUnknown, "status word address");
+    return JVPFA_ERR_CUDA;
+  }
   int v = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc5_status, sizeof(int));
+  cudaError_t e = cudaMemcpy(&v, sl->dev, sizeof(int), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) {
-    set_last_cuda_error(e, "cudaMemcpyFromSymbol(status)");
+    set_last_cuda_error(e, "cudaMemcpy(status)");
     return JVPFA_ERR_CUDA;
   }
   if (clear && v != 0) {
     const int zero = 0;
-    e = cudaMemcpyToSymbol(g_tc5_status, &zero, sizeof(int));
+    e = cudaMemcpy(sl->dev, &zero, sizeof(int), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
-      set_last_cuda_error(e, "cudaMemcpyToSymbol(status)");
+      set_last_cuda_error(e, "cudaMemcpy(status)");
       return JVPFA_ERR_CUDA;
     }
+    if (sl->mirror) *sl->mirror = 0;
   }
   *out = v;
+  return JVPFA_OK;
+}
+
+// Puts `code` into the status word and its mirror from the host, as a kernel that gave up a wait would.
+int tc5_inject_status(int code) {
+  StatusSlot* sl = status_slot();
+  if (!sl) {
+    set_last_cuda_error(cudaErrorUnknown, "status word address");
+    return JVPFA_ERR_CUDA;
+  }
+  cudaError_t e = cudaMemcpy(sl->dev, &code, sizeof(int), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "cudaMemcpy(status)");
+    return JVPFA_ERR_CUDA;
+  }
+  if (sl->mirror) *sl->mirror = code;
   return JVPFA_OK;
 }
 

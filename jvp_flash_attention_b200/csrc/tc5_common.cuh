@@ -149,6 +149,17 @@ struct AbortState {
 // another thread of the CTA has already given up.  A measured mbarrier hand-off between two warps
 // costs ~200 cycles; reading the clock costs several tens of cycles, so the wait first polls
 // without looking at it.  The budget and the abort flag are checked in the out-of-line part.
+// First failure wins; the code also goes to the host-visible mirror whose device address sits beside the status word
+// (two ints further, 8-byte aligned), so that the host learns of it without synchronising.
+__device__ __forceinline__ void publish_abort(int* global_status, int code) {
+  if (atomicCAS(global_status, 0, code) == 0) {
+    int* mirror = *reinterpret_cast<int* const*>(global_status + 2);
+    if (mirror) {
+      *reinterpret_cast<volatile int*>(mirror) = code;
+      __threadfence_system();
+    }
+  }
+}
 static __device__ __noinline__ bool mbar_wait_slow_u32(uint32_t bar, uint32_t parity, volatile int* cta_flag,
                                                        int* global_status, int code);
 __device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
@@ -182,7 +193,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       if (*ab.cta_flag != 0) return false;
       if (clock64() - t0 > kWaitBudgetCycles) {
         *ab.cta_flag = code;
-        atomicCAS(ab.global_status, 0, code);
+        publish_abort(ab.global_status, code);
         return false;
       }
     }
@@ -203,7 +214,7 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity
       if (*ab.cta_flag != 0) return false;
       if (clock64() - t0 > kWaitBudgetCycles) {
         *ab.cta_flag = code;
-        atomicCAS(ab.global_status, 0, code);
+        publish_abort(ab.global_status, code);
         return false;
       }
     }
@@ -219,7 +230,7 @@ static __device__ __noinline__ bool mbar_wait_slow_u32(uint32_t bar, uint32_t pa
       if (*cta_flag != 0) return false;
       if (clock64() - t0 > kWaitBudgetCycles) {
         *cta_flag = code;
-        atomicCAS(global_status, 0, code);
+        publish_abort(global_status, code);
         return false;
       }
     }

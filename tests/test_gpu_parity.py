@@ -636,6 +636,37 @@ def test_library_rejects_bad_arguments_without_launching():
     assert b"mask" in lib.jvpfa_strerror(-4)
 
 
+def test_calls_fail_loudly_after_a_wait_gave_up_until_the_status_is_cleared():
+    """A kernel thread that gives up a bounded wait leaves its code in the status word and in the host-visible mirror.
+    The failure is made on the host here (jvpfa_device_status_inject writes exactly those two words; no wait runs out
+    on the GPU): from then on every call that would launch a tcgen05 kernel is refused with JVPFA_ERR_DEVICE_STATUS,
+    through the C ABI and through the Python API, the register-tiled family still runs, and after
+    jvpfa_device_status(clear=1) everything works again."""
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(1, 2, 128, 64, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+    assert _lib.device_status() == 0
+    ref = ja.attention(q, k, v, causal=True)
+    _lib.device_status_inject(7)
+    try:
+        with pytest.raises(RuntimeError, match="gave up a bounded wait"):
+            ja.attention(q, k, v, causal=True)
+        o, lse = torch.empty_like(q), torch.empty(1, 2, 128, device=dev)
+        with pytest.raises(RuntimeError, match=r"\[-11\]"):
+            _lib.fwd(q, k, v, None, None, None, o, None, lse, None, _lib.MaskSpec(_lib.MASK_CAUSAL), 0.125, _lib.IMPL_TCGEN05)
+        # the other kernel family neither reads nor sets the word
+        _lib.fwd(q, k, v, None, None, None, o, None, lse, None, _lib.MaskSpec(_lib.MASK_CAUSAL), 0.125, _lib.IMPL_GENERIC)
+        torch.cuda.synchronize()
+        assert (o.float() - ref.float()).abs().max().item() < 2e-2
+        assert _lib.device_status(clear=False) == 7
+    finally:
+        assert _lib.device_status(clear=True) in (0, 7)
+    assert _lib.device_status() == 0
+    again = ja.attention(q, k, v, causal=True)
+    torch.cuda.synchronize()
+    assert torch.equal(again, ref)
+
+
 def test_config4_full_size_bias_hvp_sampled_heads():
     """fp32 B2 H8 L1024 D128 with a (B,H,L,L) bias: primal + tangent forward and the Hessian-vector
     product d/dq <d/dq sum(O*w), v_dir>; two (batch, head) slices against the float64 oracle."""
