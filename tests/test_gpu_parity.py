@@ -274,8 +274,8 @@ def test_single_pass_backward_against_two_launch_and_oracle(cot, kind, dt, B, H,
 
 
 def test_tcgen05_dispatch_rules():
-    """AUTO takes the tcgen05 kernels for 16-bit, D in {64,128}, none / causal / key padding, and boolean masks or bias
-    of the element type whose rows can be read as 16-byte pieces."""
+    """AUTO takes the tcgen05 kernels for 16-bit, D in {64,128} (D = 64: positive softmax scale), none / causal / key
+    padding, and boolean masks or bias of the element type whose rows can be read as 16-byte pieces."""
     import ctypes as C
 
     lib = _lib.load()
@@ -286,7 +286,13 @@ def test_tcgen05_dispatch_rules():
     a.dtype, a.B, a.H, a.L, a.D = _lib.BF16, 1, 1, 64, 64
     a.q = a.k = a.v = a.o = x.data_ptr()
     a.lse = lse.data_ptr()
+    a.sm_scale = 0.125
     assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 1
+    a.sm_scale = -0.125  # the D = 64 kernel takes row maxima before scaling: positive scales only
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
+    a.D = 128
+    assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 1
+    a.D, a.sm_scale = 64, 0.125
     a.impl = _lib.IMPL_GENERIC
     assert lib.jvpfa_fwd_uses_tcgen05(C.byref(a)) == 0
     a.impl = _lib.IMPL_AUTO
