@@ -63,8 +63,13 @@ struct BwdFCfg {
   static constexpr int OUT_BYTES = OWN * BL * 2;  // 16 KiB: [128 keys][64 queries]
   static constexpr int STAGE_BYTES = N_LOOP * LOOP_BYTES;
   static constexpr int STAT_STAGE_BYTES = (BL / 2) * 32;  // per query pair two float4
+  // Two sets of own tiles where shared memory allows it (backward through O alone: K and V only): the next item's
+  // are then loaded while this item's last sub-tiles run.  With one set the item boundary is exposed - the next
+  // load can only be requested when the last dQ product has completed (about an eighth of the kernel's time).
+  static constexpr int OWN_BUFS = HAS_GT ? 1 : 2;
+  static constexpr int OWN_SET_BYTES = N_OWN * OWN_BYTES;
   static constexpr int OFF_OWN = 0;
-  static constexpr int OFF_RING = N_OWN * OWN_BYTES;
+  static constexpr int OFF_RING = OWN_BUFS * OWN_SET_BYTES;
   static constexpr int OFF_OUT = OFF_RING + STAGES * STAGE_BYTES;
   static constexpr int OBUF_BYTES = N_OUT * OUT_BYTES;
   static constexpr int OFF_STAT = OFF_OUT + N_OBUF * OBUF_BYTES;
@@ -124,9 +129,9 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
   unsigned char* sOut = smem + C::OFF_OUT;
   float4* sStat = reinterpret_cast<float4*>(smem + C::OFF_STAT);  // [STAGES][BL/2][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::TILE_BYTES);
-  uint64_t* own_full = bars + 0;
-  uint64_t* own_free = bars + 1;             // score issuer + dQ issuer are through with the item's own tiles
-  uint64_t* loop_full = bars + 2;            // [STAGES]
+  uint64_t* own_full = bars + 0;             // [2] per set of own tiles (item kact uses set kact % OWN_BUFS)
+  uint64_t* own_free = bars + 2;             // [2] score issuer + dQ issuer are through with the set
+  uint64_t* loop_full = bars + 4;            // [STAGES]
   uint64_t* loop_empty = loop_full + STAGES;  // [STAGES]: score issuer + dK/dV issuer
   uint64_t* stat_full = loop_empty + STAGES;  // [STAGES]
   uint64_t* s_full = stat_full + STAGES;
@@ -204,7 +209,9 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
 
   if (tid == 0) {
     mbar_init(own_full, 1);
+    mbar_init(own_full + 1, 1);
     mbar_init(own_free, 2);
+    mbar_init(own_free + 1, 2);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(loop_full + s, 1);
       mbar_init(loop_empty + s, 2);
@@ -261,14 +268,17 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
     for (int k = 0; ok && k < k_max; ++k) {
       if (!get_item(k, it) || it.n_sub == 0) continue;
       // The own tiles are single-buffered: every MMA that reads the previous item's must be complete.
-      if (kact > 0 && !mbar_wait_backoff(own_free, (kact - 1) & 1, ab, kAbortBwdOwn)) break;
+      const int oset = kact % C::OWN_BUFS, ouse = kact / C::OWN_BUFS;  // set of own tiles and how often it was used
+      if (ouse > 0 && !mbar_wait_backoff(own_free + oset, (ouse - 1) & 1, ab, kAbortBwdOwn)) break;
       if (lane == 0) {
-        mbar_expect_tx(own_full, C::N_OWN * C::OWN_BYTES);
-        tma_load_4d(sOwn + C::SLOT_K * C::OWN_BYTES, &maps.k, own_full, 0, it.own0, it.h, it.b);
-        tma_load_4d(sOwn + C::SLOT_V * C::OWN_BYTES, &maps.v, own_full, 0, it.own0, it.h, it.b);
+        unsigned char* dst = sOwn + oset * C::OWN_SET_BYTES;
+        uint64_t* full = own_full + oset;
+        mbar_expect_tx(full, C::N_OWN * C::OWN_BYTES);
+        tma_load_4d(dst + C::SLOT_K * C::OWN_BYTES, &maps.k, full, 0, it.own0, it.h, it.b);
+        tma_load_4d(dst + C::SLOT_V * C::OWN_BYTES, &maps.v, full, 0, it.own0, it.h, it.b);
         if constexpr (HAS_GT) {
-          tma_load_4d(sOwn + C::SLOT_TK * C::OWN_BYTES, &maps.tk, own_full, 0, it.own0, it.h, it.b);
-          tma_load_4d(sOwn + C::SLOT_TV * C::OWN_BYTES, &maps.tv, own_full, 0, it.own0, it.h, it.b);
+          tma_load_4d(dst + C::SLOT_TK * C::OWN_BYTES, &maps.tk, full, 0, it.own0, it.h, it.b);
+          tma_load_4d(dst + C::SLOT_TV * C::OWN_BYTES, &maps.tv, full, 0, it.own0, it.h, it.b);
         }
       }
       const size_t stat_off = (size_t)it.bh * L;
@@ -331,8 +341,9 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
       constexpr uint32_t kLoMN = (uint32_t)(8192 >> 4) << 16;
       constexpr uint32_t OWN16 = C::OWN_BYTES >> 4, LOOP16 = C::LOOP_BYTES >> 4, OUT16 = C::OUT_BYTES >> 4,
                          STAGE16 = C::STAGE_BYTES >> 4;
-      const uint32_t own_k = kDescLo | (smem_u32(sOwn) >> 4);    // own tiles as K-major A operands
-      const uint32_t own_mn = kLoMN | (smem_u32(sOwn) >> 4);     // ... as MN-major B operands (dQ)
+      const uint32_t own_k0 = kDescLo | (smem_u32(sOwn) >> 4);    // own tiles (first set) as K-major A operands
+      const uint32_t own_mn0 = kLoMN | (smem_u32(sOwn) >> 4);     // ... as MN-major B operands (dQ)
+      constexpr uint32_t OWNSET16 = C::OWN_SET_BYTES >> 4;
       const uint32_t ring_k = kDescLo | (smem_u32(sRing) >> 4);  // streamed tiles as K-major B operands (scores)
       const uint32_t ring_mn = kLoMN | (smem_u32(sRing) >> 4);   // ... as MN-major B operands (dK, dV)
       const uint32_t out_k = kDescLo | (smem_u32(sOut) >> 4);    // elementwise results as K-major A operands (dK, dV)
@@ -342,6 +353,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
       FItem it;
       if (warp == 1) {
         // ---------------------------------------------------------------- scores
+        uint32_t own_k = own_k0;  // this item's set
         auto score = [&](uint32_t col, uint32_t own_slot, uint32_t b_lo, uint32_t id, bool first) {
           const uint32_t a_lo = own_k + own_slot * OWN16;
           if (first)
@@ -353,7 +365,9 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         };
         for (int k = 0; ok && k < k_max; ++k) {
           if (!get_item(k, it) || it.n_sub == 0) continue;
-          if (!mbar_wait(own_full, kact & 1, ab, kAbortBwdOwn)) break;
+          const int oset = kact % C::OWN_BUFS;
+          if (!mbar_wait(own_full + oset, (kact / C::OWN_BUFS) & 1, ab, kAbortBwdOwn)) break;
+          own_k = own_k0 + oset * OWNSET16;
           for (int s = 0; s < it.n_sub; ++s, ++g) {
             const int st = g % STAGES;
             if (!mbar_wait(loop_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull) ||
@@ -377,7 +391,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
             tc_commit(loop_empty + st);
           }
           if (!ok) break;
-          tc_commit(own_free);
+          tc_commit(own_free + oset);
           ++kact;
         }
       } else if (warp == 2) {
@@ -430,6 +444,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         // ---------------------------------------------------------------- dQ of the sub-tile
         // dQ (+)= result tile (A, MN-major: 64 queries x 128 keys) x own tile (B, MN-major: 128 keys x 64)
         uint32_t ob16 = 0;
+        uint32_t own_mn = own_mn0;  // this item's set
         auto inner = [&](uint32_t col, uint32_t out_slot, uint32_t own_slot, bool first) {
           const uint32_t a_lo = out_mn + ob16 + out_slot * OUT16, b_lo = own_mn + own_slot * OWN16;
           if (first)
@@ -441,6 +456,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         };
         for (int k = 0; ok && k < k_max; ++k) {
           if (!get_item(k, it) || it.n_sub == 0) continue;
+          own_mn = own_mn0 + (kact % C::OWN_BUFS) * OWNSET16;
           for (int s = 0; s < it.n_sub; ++s, ++g) {
             if (!mbar_wait(p_full + (g & 1), (g >> 1) & 1, ab, kAbortBwdPFull) ||
                 (g >= 1 && !mbar_wait(dq_free, (g - 1) & 1, ab, kAbortBwdDone))) {
@@ -457,7 +473,7 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
             tc_commit(out_free + ob);
           }
           if (!ok) break;
-          tc_commit(own_free);
+          tc_commit(own_free + kact % C::OWN_BUFS);
           ++kact;
         }
       }

@@ -50,11 +50,13 @@ def in_order(w, gen):
         yield x
 
 
-def run_fused64(n_subs, stages, seed, single_p_full=False, slow_dq=0.0):
+def run_fused64(n_subs, stages, seed, single_p_full=False, slow_dq=0.0, own_bufs=1):
     """One random interleaving for a CTA whose item k has n_subs[k] sub-tiles (0: an item of padding only, which every
-    role skips).  slow_dq: probability with which the dQ issuer lets a turn pass without doing anything."""
+    role skips).  slow_dq: probability with which the dQ issuer lets a turn pass without doing anything.  own_bufs: sets
+    of own tiles (2 in the variant without tangents: the next item's are loaded while this item still runs)."""
     w = World(seed)
-    own_full, own_free = w.bar(1), w.bar(2)
+    own_full = [w.bar(1) for _ in range(own_bufs)]
+    own_free = [w.bar(2) for _ in range(own_bufs)]
     loop_full = [w.bar(1) for _ in range(stages)]
     loop_empty = [w.bar(2) for _ in range(stages)]
     stat_full = [w.bar(1) for _ in range(stages)]
@@ -73,9 +75,10 @@ def run_fused64(n_subs, stages, seed, single_p_full=False, slow_dq=0.0):
     def producer():
         g = 0
         for kact, (k, n) in enumerate(items):
-            if kact > 0:
-                yield from w.wait(own_free, (kact - 1) & 1, ("own_released", kact - 1))
-            w.later(lambda kact=kact: (w.events.add(("own", kact)), own_full.arrive()))
+            oset, ouse = kact % own_bufs, kact // own_bufs
+            if ouse > 0:
+                yield from w.wait(own_free[oset], (ouse - 1) & 1, ("own_released", kact - own_bufs))
+            w.later(lambda kact=kact, oset=oset: (w.events.add(("own", kact)), own_full[oset].arrive()))
             for _ in range(n):
                 st = g % stages
                 yield from w.wait(loop_empty[st], ((g // stages) & 1) ^ 1, ("ring_free", g - stages) if g >= stages else None)
@@ -90,7 +93,7 @@ def run_fused64(n_subs, stages, seed, single_p_full=False, slow_dq=0.0):
     def scores():
         g = 0
         for kact, (k, n) in enumerate(items):
-            yield from w.wait(own_full, kact & 1, ("own", kact))
+            yield from w.wait(own_full[kact % own_bufs], (kact // own_bufs) & 1, ("own", kact))
             for _ in range(n):
                 st = g % stages
                 yield from w.wait(loop_full[st], (g // stages) & 1, ("loop", g))
@@ -100,7 +103,7 @@ def run_fused64(n_subs, stages, seed, single_p_full=False, slow_dq=0.0):
                                             w.tally(("rf", g), 2, ("ring_free", g)), loop_empty[st].arrive()))
                 g += 1
                 yield
-            w.later(lambda kact=kact: (w.tally(("or", kact), 2, ("own_released", kact)), own_free.arrive()))
+            w.later(lambda kact=kact: (w.tally(("or", kact), 2, ("own_released", kact)), own_free[kact % own_bufs].arrive()))
 
     def dkdv():
         g = 0
@@ -131,7 +134,7 @@ def run_fused64(n_subs, stages, seed, single_p_full=False, slow_dq=0.0):
                                             w.tally(("of", g), 2, ("out_read", g)), out_free[ob].arrive()))
                 g += 1
                 yield
-            w.later(lambda kact=kact: (w.tally(("or", kact), 2, ("own_released", kact)), own_free.arrive()))
+            w.later(lambda kact=kact: (w.tally(("or", kact), 2, ("own_released", kact)), own_free[kact % own_bufs].arrive()))
 
     def elementwise(grp):
         g = 0
@@ -178,6 +181,8 @@ def test_fused64_protocol_has_no_deadlock_and_no_premature_pass(n_subs, stages):
     for seed in range(8):
         assert run_fused64(n_subs, stages, seed) == "ok", (n_subs, stages, seed)
         assert run_fused64(n_subs, stages, seed, slow_dq=0.9) == "ok", (n_subs, stages, seed, "slow dQ issuer")
+        assert run_fused64(n_subs, stages, seed, own_bufs=2) == "ok", (n_subs, stages, seed, "two sets of own tiles")
+        assert run_fused64(n_subs, stages, seed, slow_dq=0.9, own_bufs=2) == "ok", (n_subs, stages, seed, "two sets, slow dQ")
 
 
 def test_fused64_model_shows_the_stall_of_a_single_p_full_barrier():
