@@ -74,13 +74,18 @@ def test_repeated_launches_stay_clean_and_reproducible(name, B, H, L, D, kind, d
     dq, dk, dv = (torch.empty_like(o) for _ in range(3))
     _soak(lambda: _lib.bwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], d["go"], d["gto"], lse, mu, stats[0],
                            stats[1], stats[2], dq, dk, dv, spec, scale, _lib.IMPL_TCGEN05), [dq, dk, dv])
-    if D == 64:  # the single-pass backward, through both outputs and through the tangent output alone
+    if D == 64:  # the single-pass backward: through both outputs, through the tangent output alone
         acc = torch.empty(B, H, L, D, device=DEV, dtype=torch.float32)
         _soak(lambda: _lib.bwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], d["go"], d["gto"], lse, mu, stats[0],
                                stats[1], stats[2], dq, dk, dv, spec, scale, _lib.IMPL_TCGEN05, dq_accum=acc),
               [dk, dv], close=[dq])
         _lib.bwd_preprocess(o, to, None, d["gto"], mu, stats[0], stats[1], stats[2])
         _soak(lambda: _lib.bwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], None, d["gto"], lse, mu, stats[0],
+                               stats[1], stats[2], dq, dk, dv, spec, scale, _lib.IMPL_TCGEN05, dq_accum=acc),
+              [dk, dv], close=[dq])
+        # ... and through O alone (the variant with two sets of own tiles)
+        _lib.bwd_preprocess(o, None, d["go"], None, None, stats[0], stats[1], stats[2])
+        _soak(lambda: _lib.bwd(d["q"], d["k"], d["v"], None, None, None, d["go"], None, lse, None, stats[0],
                                stats[1], stats[2], dq, dk, dv, spec, scale, _lib.IMPL_TCGEN05, dq_accum=acc),
               [dk, dv], close=[dq])
 
