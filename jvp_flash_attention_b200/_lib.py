@@ -312,7 +312,8 @@ def _launch(t: torch.Tensor, entry, args) -> int:
 
 
 def _stream(t: torch.Tensor) -> int:
-    return torch.cuda.current_stream(t.device).cuda_stream
+    # the raw handle of the device's current stream, without building a torch.cuda.Stream object (~3 us per call)
+    return torch._C._cuda_getCurrentRawStream(t.device.index)
 
 
 ERR_UNSUPPORTED = -9
