@@ -626,10 +626,10 @@ def _fwd_dual_inside_func_jvp(interp, q, k, v, attn_mask, causal, sm_scale):
     raw = [fc._unwrap_for_grad(d.primal, level) for d in duals] + [fc._unwrap_for_grad(d.tangent, level) for d in duals]
     if isinstance(attn_mask, Tensor):
         attn_mask = fc._unwrap_for_grad(fwAD.unpack_dual(attn_mask).primal, level)
-    with torch.enable_grad(), interp.lower():
+    with interp.lower():  # the caller's grad mode stays as it is
         o, aux, relay = _Attn.apply(*raw, attn_mask, causal, sm_scale, True)
         o_t, M, mu, spec, scale, link = aux.value
-        if any(x.requires_grad for x in raw):  # the tangent output carries a gradient: same node as in _Attn.jvp
+        if torch.is_grad_enabled() and any(x.requires_grad for x in raw):  # the tangent output carries a gradient: same node as in _Attn.jvp
             o_t = _TangentBridge.apply(*raw, o_t, o, M, mu, spec, scale, relay, link)
     return fwAD.make_dual(fc._wrap_for_grad(o, level), fc._wrap_for_grad(o_t, level))
 

@@ -56,6 +56,20 @@ def test_grad_through_primal_and_tangent(cpu_kernels, route, kind):
         assert orc.max_abs_err(x, y) < 1e-9
 
 
+def test_func_jvp_keeps_the_callers_grad_mode(cpu_kernels):
+    """Inside torch.func.jvp the call runs one level down on the unwrapped tensors; the caller's no_grad must hold
+    there as well, and with grad enabled both outputs take part in the graph."""
+    q, k, v, tq, tk, tv, _, _ = _inputs(5)
+    a = [x.clone().requires_grad_() for x in (q, k, v)]
+    fn = lambda q_, k_, v_: ja.JVPAttn.fwd_dual(q_, k_, v_, causal=True)  # noqa: E731
+    with torch.no_grad():
+        o, to = torch.func.jvp(fn, tuple(a), (tq, tk, tv))
+    assert not o.requires_grad and not to.requires_grad
+    o2, to2 = torch.func.jvp(fn, tuple(a), (tq, tk, tv))
+    assert o2.requires_grad and to2.requires_grad
+    assert torch.equal(o, o2.detach()) and torch.equal(to, to2.detach())
+
+
 @pytest.mark.parametrize("route", ["func_jvp", "fwad"])
 @pytest.mark.parametrize("which", ["both", "o", "to"])
 def test_one_backward_launch_per_step_whatever_the_loss_uses(cpu_kernels, monkeypatch, route, which):
