@@ -21,7 +21,9 @@ Behaviour that goes beyond upstream, on purpose:
 """
 from __future__ import annotations
 
+import copy
 import inspect
+import weakref
 from typing import Any, Literal, NamedTuple
 
 import torch
@@ -119,6 +121,16 @@ def set_fp32_precision(mode: str) -> str:
     return prev
 
 
+# What classify_mask found out about a mask tensor, kept while the same tensor object is passed again unmodified
+# (same Python object, same version counter: every in-place operation of torch bumps it).  A mask is typically
+# built once and used by every layer and step; its verification is a pass over B*H*L*L elements and a read-back.
+# Writes that bypass torch (a foreign kernel writing through the raw pointer) are not seen; MASK_MEMO_ENABLED = False
+# turns the memo off.
+MASK_MEMO_ENABLED = True
+_MASK_MEMO: dict = {}
+_MASK_MEMO_MAX = 16
+
+
 def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int, qdtype: torch.dtype,
                   verify: bool) -> tuple[_lib.MaskSpec, int, Tensor | None]:
     """Turns the user's mask into the kernel's description.
@@ -131,6 +143,25 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
         return _lib.MaskSpec(_lib.MASK_CAUSAL), 0, None
     if attn_mask is None:
         return _lib.MaskSpec(_lib.MASK_NONE), 0, None
+    if not MASK_MEMO_ENABLED:
+        return _classify_mask_tensor(attn_mask, Z, H, N, verify)
+    key = (Z, H, N, verify, _unwrap(attn_mask)._version)
+    hit = _MASK_MEMO.get(id(attn_mask))
+    if hit is not None and hit[0]() is attn_mask and hit[1] == key:
+        spec, mask_type = hit[2]
+        return copy.copy(spec), mask_type, attn_mask  # a copy: the caller writes per-call state into the description
+    spec, mask_type, _ = _classify_mask_tensor(attn_mask, Z, H, N, verify)
+    if len(_MASK_MEMO) >= _MASK_MEMO_MAX:
+        _MASK_MEMO.clear()
+    try:
+        _MASK_MEMO[id(attn_mask)] = (weakref.ref(attn_mask), key, (copy.copy(spec), mask_type))
+    except TypeError:  # an object that cannot be weakly referenced: no memo
+        pass
+    return spec, mask_type, attn_mask
+
+
+def _classify_mask_tensor(attn_mask: Tensor, Z: int, H: int, N: int, verify: bool):
+    """classify_mask for a mask tensor: shape checks, key-padding recognition, verification passes."""
     assert attn_mask.dim() == 4, "The provided attention mask must have 4 dimensions (Z, H, N_CTX, N_CTX)."
     mz, mh, mi, mj = attn_mask.shape
     assert mz in (1, Z) and mh in (1, H) and mi in (1, N) and mj == N, (

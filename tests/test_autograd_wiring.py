@@ -56,6 +56,44 @@ def test_grad_through_primal_and_tangent(cpu_kernels, route, kind):
         assert orc.max_abs_err(x, y) < 1e-9
 
 
+def test_mask_verification_is_remembered_per_tensor_object_and_version(cpu_kernels, monkeypatch):
+    """The verification pass over a mask runs once while the same tensor object comes back unmodified; an in-place
+    change (torch bumps the version counter) or another tensor object runs it again; a failed verification is not
+    remembered."""
+    q, k, v, *_ = _inputs(7)
+    calls = []
+    inner = stand_in.mask_tiles
+
+    def counting(*args):
+        calls.append(1)
+        return inner(*args)
+
+    monkeypatch.setattr(_lib, "mask_tiles", counting)
+    ja._MASK_MEMO.clear()
+    g = torch.Generator().manual_seed(1)
+    mask = torch.rand(1, 2, 32, 32, generator=g) > 0.4
+    mask[..., 0] = True
+    o1 = ja.attention(q, k, v, attn_mask=mask)
+    o2 = ja.attention(q, k, v, attn_mask=mask)
+    assert len(calls) == 1 and torch.equal(o1, o2)
+    mask[0, 0, 3, 5] = not bool(mask[0, 0, 3, 5])  # in place: the version counter moves
+    o3 = ja.attention(q, k, v, attn_mask=mask)
+    assert len(calls) == 2 and not torch.equal(o1, o3)
+    ja.attention(q, k, v, attn_mask=mask.clone())  # another object
+    assert len(calls) == 3
+    bad = torch.zeros(1, 2, 32, 32, dtype=torch.bool)
+    bad[:, :, ::2, 1] = True  # not a key-padding prefix; head rows exist, but make one head all False
+    bad[0, 1] = False
+    for _ in range(2):
+        with pytest.raises(AssertionError, match="all False"):
+            ja.attention(q, k, v, attn_mask=bad)
+    monkeypatch.setattr(ja, "MASK_MEMO_ENABLED", False)
+    n = len(calls)
+    ja.attention(q, k, v, attn_mask=mask)
+    ja.attention(q, k, v, attn_mask=mask)
+    assert len(calls) == n + 2
+
+
 def test_func_jvp_keeps_the_callers_grad_mode(cpu_kernels):
     """Inside torch.func.jvp the call runs one level down on the unwrapped tensors; the caller's no_grad must hold
     there as well, and with grad enabled both outputs take part in the graph."""
