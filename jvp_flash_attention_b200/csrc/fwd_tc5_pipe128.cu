@@ -41,7 +41,10 @@ struct FwdPipeCfg {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = N_T * Q_BYTES;
   static constexpr int OFF_V = OFF_K + STAGES * K_STAGE;
-  static constexpr int TILE_BYTES = OFF_V + STAGES * V_STAGE;
+  // the live key tiles of the CTA's query tile, in order (boolean masks with a tile bitmap: the others are not visited)
+  static constexpr int MAX_KEY_TILES = 1024;
+  static constexpr int OFF_IDS = OFF_V + STAGES * V_STAGE;
+  static constexpr int TILE_BYTES = OFF_IDS + MAX_KEY_TILES * 2;
   static constexpr int SMEM_BYTES = TILE_BYTES + 256 /*barriers*/ + 1024 /*alignment slack*/;
   static constexpr int SC_COLS = DUAL ? 2 * BN : BN;  // one score buffer
   static constexpr int COL_O = 2 * SC_COLS;
@@ -55,7 +58,9 @@ struct FwdPipeMaps {
 
 // MK: 0 = none / causal / key padding; 1 = uint8 mask; 2 = bias of the element type T (the softmax thread of a
 // query row reads its 64 mask elements of the tile with 16-byte loads before it waits for the scores; key stride 1,
-// 16-byte aligned rows and L % 16 == 0 are the host's responsibility).
+// 16-byte aligned rows and L % 16 == 0 are the host's responsibility); 3 = uint8 mask with the bitmap of 128 x 64
+// tiles that hold a true entry (jvpfa_mask_tiles): the CTA lists its query tile's live key tiles once and every role
+// walks that list, so tiles without a true entry are neither loaded nor multiplied.
 template <typename T, bool DUAL, int MK>
 __global__ void __launch_bounds__(192, 1)
 fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMaps maps, int* status) {
@@ -82,6 +87,8 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
   uint64_t* o_full = bars + 14;   // all output MMAs of the CTA have landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_live = reinterpret_cast<int*>(tmem_slot + 2);  // MK == 3: length of the list
+  const unsigned short* ids = reinterpret_cast<const unsigned short*>(smem + C::OFF_IDS);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
@@ -97,7 +104,12 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
   }
   int n_end = n_valid;
   if (causal) n_end = min(n_end, m0 + BM);
-  const int n_tiles = (n_end + BN - 1) / BN;
+  int n_tiles = (n_end + BN - 1) / BN;
+  // key tile visited at step t
+  auto key_tile = [&](int t) -> int {
+    if constexpr (MK == 3) return (int)ids[t];
+    return t;
+  };
 
   // lse = NaN for this CTA's rows: the results of this launch are not to be trusted
   auto poison = [&]() {
@@ -122,6 +134,26 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
     mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
+    if constexpr (MK == 3) {
+      // the bitmap has the mask's own extents: broadcast dimensions (stride 0) have one entry
+      const int n_q_tiles = (L + BM - 1) / BM, n_words = ((L + BN - 1) / BN + 63) >> 6;
+      const long long hm = (a.mask.stride[0] ? (long long)tma_b * (a.mask.stride[1] ? a.H : 1) : 0) +
+                           (a.mask.stride[1] ? tma_h : 0);
+      const long long qm = a.mask.stride[2] ? hm * n_q_tiles + mt : hm;
+      const unsigned long long* live = reinterpret_cast<const unsigned long long*>(a.mask_tile_live) + qm * n_words;
+      unsigned short* out = reinterpret_cast<unsigned short*>(smem + C::OFF_IDS);
+      int cnt = 0;
+      for (int w = 0; w * 64 < n_tiles; ++w) {
+        unsigned long long bits = __ldg(live + w);
+        const int rem = n_tiles - 64 * w;
+        if (rem < 64) bits &= (1ull << rem) - 1ull;
+        while (bits) {
+          out[cnt++] = (unsigned short)(64 * w + __ffsll((long long)bits) - 1);
+          bits &= bits - 1ull;
+        }
+      }
+      *n_live = cnt;
+    }
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, C::COLS_ALLOC);
@@ -132,6 +164,7 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const AbortState ab{abort_flag, status};
+  if constexpr (MK == 3) n_tiles = *n_live;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -150,9 +183,9 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
         unsigned char* base = sK + st * C::K_STAGE;
         mbar_expect_tx(k_full + st, C::K_STAGE);
         for (int hf = 0; hf < 2; ++hf) {
-          tma_load_4d(base + hf * C::N_T * C::HALF_BYTES, &maps.k, k_full + st, hf * 64, t * BN, tma_h, tma_b);
+          tma_load_4d(base + hf * C::N_T * C::HALF_BYTES, &maps.k, k_full + st, hf * 64, key_tile(t) * BN, tma_h, tma_b);
           if constexpr (DUAL)
-            tma_load_4d(base + (hf * 2 + 1) * C::HALF_BYTES, &maps.tk, k_full + st, hf * 64, t * BN, tma_h, tma_b);
+            tma_load_4d(base + (hf * 2 + 1) * C::HALF_BYTES, &maps.tk, k_full + st, hf * 64, key_tile(t) * BN, tma_h, tma_b);
         }
         return true;
       };
@@ -162,9 +195,9 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
         unsigned char* base = sV + st * C::V_STAGE;
         mbar_expect_tx(v_full + st, C::V_STAGE);
         for (int hf = 0; hf < 2; ++hf) {
-          tma_load_4d(base + hf * C::HALF_BYTES, &maps.v, v_full + st, hf * 64, t * BN, tma_h, tma_b);
+          tma_load_4d(base + hf * C::HALF_BYTES, &maps.v, v_full + st, hf * 64, key_tile(t) * BN, tma_h, tma_b);
           if constexpr (DUAL)
-            tma_load_4d(base + (2 + hf) * C::HALF_BYTES, &maps.tv, v_full + st, hf * 64, t * BN, tma_h, tma_b);
+            tma_load_4d(base + (2 + hf) * C::HALF_BYTES, &maps.tv, v_full + st, hf * 64, key_tile(t) * BN, tma_h, tma_b);
         }
         return true;
       };
@@ -247,8 +280,8 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
     float m_used = -INFINITY, l_run = 0.f, mu_run = 0.f;
     bool alive = true;
 
-    constexpr bool BOOLM = MK == 1;
-    constexpr int MESZ = MK == 1 ? 1 : 2;        // bytes per mask element
+    constexpr bool BOOLM = MK == 1 || MK == 3;
+    constexpr int MESZ = BOOLM ? 1 : 2;        // bytes per mask element
     constexpr int MW = MK == 0 ? 1 : 16 * MESZ;  // 32-bit words per row of a 64-key tile
     const unsigned char* mrow = nullptr;
     if constexpr (MK != 0)
@@ -257,7 +290,7 @@ fwd_tc5_pipe128_kernel(const jvpfa_fwd_args a, const __grid_constant__ FwdPipeMa
               (long long)min(i, L - 1) * a.mask.stride[2]) * MESZ;
 
     for (int t = 0; t < n_tiles; ++t) {
-      const int n0 = t * BN;
+      const int n0 = key_tile(t) * BN;
       const int st = t & 1;
       const uint32_t tS = tmem + lane_off + st * C::SC_COLS, tTS = tS + BN;
       uint32_t mw[MW];
@@ -526,6 +559,8 @@ static int launch_pipe128(const jvpfa_fwd_args& a, cudaStream_t stream) {
 template <typename T>
 static int launch_pipe128_t(const jvpfa_fwd_args& a, cudaStream_t s) {
   const bool dual = a.tq != nullptr;
+  if (a.mask.kind == JVPFA_MASK_BOOL && a.mask_tile_live != nullptr && (a.L + 63) / 64 <= FwdPipeCfg<true>::MAX_KEY_TILES)
+    return dual ? launch_pipe128<T, true, 3>(a, s) : launch_pipe128<T, false, 3>(a, s);
   if (a.mask.kind == JVPFA_MASK_BOOL) return dual ? launch_pipe128<T, true, 1>(a, s) : launch_pipe128<T, false, 1>(a, s);
   if (a.mask.kind == JVPFA_MASK_BIAS) return dual ? launch_pipe128<T, true, 2>(a, s) : launch_pipe128<T, false, 2>(a, s);
   return dual ? launch_pipe128<T, true, 0>(a, s) : launch_pipe128<T, false, 0>(a, s);

@@ -961,6 +961,63 @@ def test_tcgen05_forward_steps_over_dead_mask_tiles(dt, B, H, L, kind, dual):
     torch.autograd.grad(out.float().sum(), a)
 
 
+@pytest.mark.parametrize("dual", [True, False], ids=["dual", "primal"])
+@pytest.mark.parametrize("kind", ["window", "blocks", "keys"])
+def test_head_dim_128_forward_steps_over_dead_mask_tiles(kind, dual):
+    """D = 128: with the tile bitmap the forward lists the live key tiles of its query tile and visits only those; the
+    results are bit for bit those of the plain masked loop (dead tiles contribute exact zeros) and agree with the
+    oracle; a query tile without any key gives zeros and lse = +inf; the public API takes the same route."""
+    dev, dtype = "cuda:0", torch.bfloat16
+    B, H, L = 2, 3, 640
+    g = torch.Generator().manual_seed(11)
+    i, j = torch.arange(L)[:, None], torch.arange(L)[None, :]
+    if kind == "window":
+        mask = ((i - j).abs() <= 96).expand(B, H, L, L).clone()
+    elif kind == "blocks":
+        mask = ((i // 128) % 3 == (j // 64) % 3).expand(1, H, L, L).clone() & (torch.rand(1, H, L, L, generator=g) > 0.2)
+        mask[0, :, torch.arange(L), (torch.arange(L) // 128 % 3) * 64] = True  # every row keeps a key
+        mask[0, H - 1, 128:256] = False  # a query tile without any key
+    else:
+        mask = torch.rand(B, 1, 1, L, generator=g) > 0.3
+        mask[..., 64:256] = False
+        mask[..., 5] = True
+    q, k, v, tq, tk, tv, *_ = _make(B, H, L, 128, dtype, seed=77)
+    if not dual:
+        tq = tk = tv = None
+    md = mask.to(dev)
+    spec = _lib.MaskSpec(_lib.MASK_BOOL, md.view(torch.uint8), tuple(0 if md.shape[d] == 1 else md.stride(d) for d in range(4)))
+    tile_live, head_live, _ = _lib.mask_tiles(spec, L)
+    n_kt = (L + 63) // 64
+    n_live = head_live[-1].item()
+    assert 0 < n_live < n_kt * (tile_live.numel() // ((n_kt + 63) // 64))  # the case does have dead tiles
+    cu = lambda x: None if x is None else x.to(dev)  # noqa: E731
+    outs = []
+    for bitmap in (None, tile_live):
+        spec.tile_live = bitmap
+        o = torch.empty(B, H, L, 128, device=dev, dtype=dtype)
+        to = torch.empty_like(o) if dual else None
+        lse = torch.empty(B, H, L, device=dev)
+        mu = torch.empty_like(lse) if dual else None
+        _lib.fwd(cu(q), cu(k), cu(v), cu(tq), cu(tk), cu(tv), o, to, lse, mu, spec, 128 ** -0.5, _lib.IMPL_TCGEN05)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        outs.append((o, to, lse, mu))
+    for a_, b_ in zip(outs[0], outs[1]):
+        if a_ is not None:
+            assert torch.equal(a_, b_)
+    o, to, lse, mu = outs[1]
+    if kind == "blocks":
+        assert o[0, H - 1, 128:256].abs().max() == 0 and torch.isinf(lse[0, H - 1, 128:256]).all()
+    if dual:
+        ro, rto = orc.sdpa_jvp(q, k, v, tq, tk, tv, attn_mask=mask)
+        _close(to, rto, dtype, "tO")
+    else:
+        ro = orc.sdpa_primal(q, k, v, attn_mask=mask)
+    _close(o, ro, dtype, "O")
+    out = ja.attention(cu(q), cu(k), cu(v), attn_mask=md)
+    assert torch.equal(out, outs[1][0])
+
+
 @pytest.mark.parametrize("D,L,kind", [(64, 160, "causal"), (128, 96, "bias"), (32, 128, "bool"), (64, 256, "none")])
 def test_fp32_single_pass_tf32_mode(D, L, kind):
     """`set_fp32_precision("tf32")`: fp32 tensors multiplied with one TF32 MMA per product, the precision of upstream's
