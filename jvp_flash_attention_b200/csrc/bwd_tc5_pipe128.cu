@@ -83,7 +83,37 @@ struct BwdPipeCfg {
 static_assert(BwdPipeCfg<true, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(BwdPipeCfg<false, true, true>::SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
-// MK: 0 = none / causal / key padding; 1 = uint8 mask; 2 = bias of the element type T.  For 1 and 2 every elementwise
+// MK == 3: walks the loop tiles of a CTA that hold a true mask entry, in order.  The bitmaps of jvpfa_mask_tiles have one
+// bit per 128-query x 64-key tile.  Own keys: w points at the transposed bitmap's entry of the own 128-key tile (bit =
+// 128-query tile, four 32-row loop tiles each).  Own queries: w points at the bitmap's entry of the own 128-query tile
+// (bit = 64-key tile); a 48-key loop tile is live if one of the one or two 64-key tiles it overlaps is.
+template <bool OWN_KEYS, int BL>
+struct LoopWalk {
+  const unsigned long long* w = nullptr;
+  int n_cand = 0, n_bits = 1, c = 0;
+  bool rows = true;  // false: the mask has one row for all queries
+  __device__ __forceinline__ bool bit(int b) const { return (__ldg(w + (b >> 6)) >> (b & 63)) & 1ull; }
+  __device__ __forceinline__ bool live(int cc) const {
+    if constexpr (OWN_KEYS) {
+      return bit(rows ? (cc * BL) >> 7 : 0);
+    } else {
+      const int lo = (cc * BL) >> 6, hi = min((cc * BL + BL - 1) >> 6, n_bits - 1);
+      return bit(lo) || bit(hi);
+    }
+  }
+  __device__ __forceinline__ int next() {  // index of the next live loop tile (the caller asks no more often than there are)
+    while (c < n_cand && !live(c)) ++c;
+    return c++;
+  }
+  __device__ __forceinline__ int count() const {
+    int n = 0;
+    for (int cc = 0; cc < n_cand; ++cc) n += live(cc) ? 1 : 0;
+    return n;
+  }
+};
+
+// MK: 0 = none / causal / key padding; 1 = uint8 mask; 2 = bias of the element type T; 3 = uint8 mask with the tile
+// bitmaps (loop tiles without a true entry are not visited).  For 1 and 2 every elementwise
 // thread fetches the 16 mask elements of its piece of the tile from global memory before it waits for the scores (own
 // queries: one or two 16-byte loads of the thread's mask row; own keys: one element of each of 16 query rows, the lanes
 // of a warp reading neighbouring keys).  Key stride 1, 16-byte aligned rows and L % 16 == 0 are the host's
@@ -117,6 +147,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
   uint64_t* y_empty = bars + 13;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_live = reinterpret_cast<int*>(tmem_slot + 2);  // MK == 3: live loop tiles of this CTA
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int L = a.L;
@@ -144,6 +175,24 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
     n_tiles = (n_end + BL - 1) / BL;
   }
   const size_t stat_off = (size_t)bh * L;
+  LoopWalk<OWN_KEYS, BL> walk0;
+  if constexpr (MK == 3) {
+    // the bitmaps have the mask's own extents: a broadcast dimension (stride 0) has one entry
+    const long long hm = (a.mask.stride[0] ? (long long)tma_b * (a.mask.stride[1] ? a.H : 1) : 0) +
+                         (a.mask.stride[1] ? tma_h : 0);
+    const int n_t128 = (L + 127) / 128;
+    walk0.rows = a.mask.stride[2] != 0;
+    walk0.n_cand = n_tiles;
+    if constexpr (OWN_KEYS) {
+      const int n_words_t = walk0.rows ? (n_t128 + 63) / 64 : 1;
+      walk0.w = reinterpret_cast<const unsigned long long*>(a.mask_tile_live_t) + (hm * n_t128 + own0 / OWN) * n_words_t;
+    } else {
+      walk0.n_bits = (L + 63) / 64;
+      const int n_words = (walk0.n_bits + 63) / 64;
+      walk0.w = reinterpret_cast<const unsigned long long*>(a.mask_tile_live) +
+                (walk0.rows ? hm * n_t128 + own0 / OWN : hm) * n_words;
+    }
+  }
 
   // NaN into this CTA's output rows: the results of this launch are not to be trusted
   auto poison = [&]() {
@@ -178,6 +227,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
     mbar_init(y_empty, 1);
     *abort_flag = 0;
     fence_mbar_init();
+    if constexpr (MK == 3) *n_live = walk0.count();
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, C::COLS_ALLOC);
@@ -188,6 +238,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const AbortState ab{abort_flag, status};
+  if constexpr (MK == 3) n_tiles = *n_live;
 
   // Tensor map of own slot s / loop slot s (nullptr: the slot is not used by this instance).
   auto own_map = [&](int s) -> const CUtensorMap* {
@@ -234,11 +285,12 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
             tma_load_4d(sOwn + s * C::OWN_BYTES + hf * C::OWN_HALF, m, own_full, hf * 64, own0, tma_h, tma_b);
         }
       }
+      auto walk = walk0;
       for (int t = 0; t < n_tiles; ++t) {
         const int st = t % STAGES;
         const uint32_t ph = (t / STAGES) & 1;
         if (!mbar_wait(loop_empty + st, ph ^ 1, ab, kAbortBwdLoopEmpty)) break;
-        const int l0 = loop_begin + t * BL;
+        const int l0 = MK == 3 ? walk.next() * BL : loop_begin + t * BL;
         if (lane == 0) {
           unsigned char* base = sX + st * C::X_STAGE;
           mbar_expect_tx(loop_full + st, C::N_X * 2 * C::LQ_BYTES);
@@ -441,7 +493,8 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
       }
     }
 
-    constexpr int MESZ = MK == 1 ? 1 : 2;  // bytes per mask element
+    constexpr bool BOOLM = MK == 1 || MK == 3;
+    constexpr int MESZ = BOOLM ? 1 : 2;  // bytes per mask element
     const unsigned char* mbase = nullptr;
     long long mpitch = 0;
     if constexpr (MK != 0) {
@@ -450,9 +503,10 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
       mpitch = a.mask.stride[2] * MESZ;
     }
 
+    auto walk = walk0;
     for (int t = 0; t < n_tiles; ++t) {
       const int st = t % STAGES;
-      const int l0 = loop_begin + t * BL;
+      const int l0 = MK == 3 ? walk.next() * BL : loop_begin + t * BL;
       // MK != 0: the piece's 16 mask / bias elements, one per column (indices clamped into the tensor; what lies
       // outside is switched off by the index tests below)
       uint32_t mraw[MK == 0 ? 1 : 16];
@@ -463,7 +517,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
 #pragma unroll
           for (int x = 0; x < 16; ++x) {
             const unsigned char* el = pm + (long long)min(c0 + x, L - 1) * mpitch;
-            mraw[x] = MK == 1 ? ldg_nc_u8(el) : ldg_nc_u16(el);
+            mraw[x] = BOOLM ? ldg_nc_u8(el) : ldg_nc_u16(el);
           }
         } else {
           const unsigned char* pm = mbase + (long long)min(own_idx, L - 1) * mpitch + (size_t)c0 * MESZ;
@@ -476,7 +530,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
           }
 #pragma unroll
           for (int x = 0; x < 16; ++x)
-            mraw[x] = MK == 1 ? ((w[x >> 2] >> ((x & 3) * 8)) & 0xffu) : ((w[x >> 1] >> ((x & 1) * 16)) & 0xffffu);
+            mraw[x] = BOOLM ? ((w[x >> 2] >> ((x & 3) * 8)) & 0xffu) : ((w[x >> 1] >> ((x & 1) * 16)) & 0xffffu);
         }
       }
       if constexpr (OWN_KEYS) {
@@ -530,7 +584,7 @@ bwd_tc5_pipe128_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdPipeMa
           float arg = fmaf(__uint_as_float(s[col]), scale_log2, -lse);
           if constexpr (MK == 2) arg = fmaf(unpack1<T>(mraw[col]), kLog2e, arg);  // scores are in log2 units
           float p = fast_exp2(arg);
-          if constexpr (MK == 1)
+          if constexpr (BOOLM)
             if (mraw[col] == 0u) p = 0.f;
           if (partial && (j >= n_valid || (causal && j > i))) p = 0.f;
           pv[h] = p;
@@ -682,6 +736,8 @@ static int launch_pipe_m(const jvpfa_bwd_args& a, cudaStream_t s) {
 
 template <typename T>
 static int launch_pipe_t(const jvpfa_bwd_args& a, cudaStream_t s) {
+  if (a.mask.kind == JVPFA_MASK_BOOL && a.mask_tile_live != nullptr && a.mask_tile_live_t != nullptr)
+    return launch_pipe_m<T, 3>(a, s);
   if (a.mask.kind == JVPFA_MASK_BOOL) return launch_pipe_m<T, 1>(a, s);
   if (a.mask.kind == JVPFA_MASK_BIAS) return launch_pipe_m<T, 2>(a, s);
   return launch_pipe_m<T, 0>(a, s);

@@ -1016,6 +1016,31 @@ def test_head_dim_128_forward_steps_over_dead_mask_tiles(kind, dual):
     _close(o, ro, dtype, "O")
     out = ja.attention(cu(q), cu(k), cu(v), attn_mask=md)
     assert torch.equal(out, outs[1][0])
+    # backward: both launches visit only loop tiles that overlap a live bitmap tile (own keys: 32-query tiles inside
+    # live 128-query tiles; own queries: 48-key tiles overlapping a live 64-key tile); dead ones would add exact zeros
+    gg = torch.Generator().manual_seed(78)
+    go = torch.randn(B, H, L, 128, generator=gg).to(dtype).to(dev)
+    gto = torch.randn(B, H, L, 128, generator=gg).to(dtype).to(dev) if dual else None
+    _, _, tile_live_t = _lib.mask_tiles(spec, L)
+    grads = []
+    for bitmaps in ((None, None), (tile_live, tile_live_t)):
+        spec.tile_live, spec.tile_live_t = bitmaps
+        stats = torch.empty(3, B, H, L, device=dev)
+        _lib.bwd_preprocess(o, to, go, gto, mu, stats[0], stats[1], stats[2])
+        dq, dk, dv = (torch.empty(B, H, L, 128, device=dev, dtype=dtype) for _ in range(3))
+        _lib.bwd(cu(q), cu(k), cu(v), cu(tq), cu(tk), cu(tv), go, gto, lse, mu, stats[0], stats[1], stats[2], dq, dk, dv,
+                 spec, 128 ** -0.5, _lib.IMPL_TCGEN05)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        grads.append((dq, dk, dv))
+    for name, x, y in zip(("dq", "dk", "dv"), grads[1], grads[0]):
+        assert torch.isfinite(x.float()).all(), name
+        assert torch.equal(x, y), name  # same tiles in the same order; the skipped ones held zeros
+    if dual:
+        refs = orc.grads_through_both(q[:1, :1], k[:1, :1], v[:1, :1], tq[:1, :1], tk[:1, :1], tv[:1, :1],
+                                      go[:1, :1].cpu(), gto[:1, :1].cpu(), attn_mask=mask[:1, :1])
+        for name, x, r in zip(("dq", "dk", "dv"), grads[1], refs[2:]):
+            _close(x[:1, :1], r, dtype, name)
 
 
 @pytest.mark.parametrize("D,L,kind", [(64, 160, "causal"), (128, 96, "bias"), (32, 128, "bool"), (64, 256, "none")])
