@@ -173,12 +173,14 @@ typedef struct {
   void *dq, *dk, *dv;
   jvpfa_mask mask;
   int64_t in_stride[3]; /* of q, k, v, tq, tk, tv, as in jvpfa_fwd_args; go, gto, dq, dk, dv are row-major */
-  /* Optional, JVPFA_MASK_BOOL only, both or neither, L <= 8192: tile_live and tile_live_t of jvpfa_mask_tiles.  The
-   * D = 64 tcgen05 kernels then visit only the 32-row sub-tiles of live tiles; other kernels ignore them. */
+  /* Optional, JVPFA_MASK_BOOL only, both or neither: tile_live and tile_live_t of jvpfa_mask_tiles.  The two-launch
+   * tcgen05 kernels (D = 64: L <= 8192) then visit only the loop tiles that overlap a live tile; other kernels ignore
+   * them. */
   const void* mask_tile_live;
   const void* mask_tile_live_t;
   /* Optional caller-owned scratch: B*H*L*D floats, 16-byte aligned, contents irrelevant on entry.  With it (D = 64,
-   * 16-bit types, mask kinds NONE / CAUSAL / KVLEN) the backward runs as ONE pass that forms every score tile once:
+   * 16-bit types, mask kinds NONE / CAUSAL / KVLEN, or BOOL without the two bitmaps above) the backward runs as ONE pass
+   * that forms every score tile once:
    * dK and dV accumulate on chip, dQ is summed into this buffer with floating-point reductions and converted at the
    * end, so dQ is reproducible to rounding but not bitwise from run to run.  NULL: the two-launch kernels, which
    * recompute the score tiles for dQ (as upstream does, jvp_attention.py:1415-1707) and are bitwise reproducible. */

@@ -113,7 +113,9 @@ struct FItem {
   int bh, b, h, own0, loop_begin, n_sub;
 };
 
-template <typename T, bool HAS_GO, bool HAS_GT>
+// MK: 0 = none / causal / key padding (index comparisons); 1 = uint8 mask with any strides (each elementwise thread
+// reads the 32 mask bytes of its key row and the sub-tile's queries before it waits for the scores).
+template <typename T, bool HAS_GO, bool HAS_GT, int MK>
 __global__ void __launch_bounds__(512, 1)
 bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps maps, float* dq_acc, int* status) {
   using C = BwdFCfg<HAS_GO, HAS_GT>;
@@ -527,12 +529,27 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
       for (int s = 0; s < it.n_sub; ++s, ++g) {
         const int st = g % STAGES;
         const int l0 = it.loop_begin + s * BL + 32 * wg;  // first query of this group's columns
+        // MK = 1: this key's mask bytes for the 32 queries, requested before the waits (indices clamped into the
+        // tensor; what lies outside is switched off by col_hi and by lse = +inf of the padding queries)
+        uint32_t mraw[MK == 1 ? 32 : 1];
+        if constexpr (MK == 1) {
+          const unsigned char* pm = reinterpret_cast<const unsigned char*>(a.mask.ptr) + (long long)it.b * a.mask.stride[0] +
+                                    (long long)it.h * a.mask.stride[1] + (long long)min(own_idx, L - 1) * a.mask.stride[3];
+#pragma unroll
+          for (int col = 0; col < 32; ++col) mraw[col] = ldg_nc_u8(pm + (long long)min(l0 + col, L - 1) * a.mask.stride[2]);
+        }
         if (!mbar_wait(stat_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull) ||
             !mbar_wait(s_full, g & 1, ab, kAbortBwdSFull)) {
           alive = false;
           break;
         }
         tc_fence_after();
+        uint32_t live = 0xffffffffu;  // MK = 1: bit col = the mask lets query l0 + col attend this key
+        if constexpr (MK == 1) {
+          live = 0u;
+#pragma unroll
+          for (int col = 0; col < 32; ++col) live |= (mraw[col] != 0u ? 1u : 0u) << col;
+        }
         uint32_t sv[32], fp[32], ts[HAS_GT ? 32 : 1], ev[HAS_GT ? 32 : 1];
         tmem_ld32(tbase + C::COL_S, sv);
         tmem_ld32(tbase + C::COL_FP, fp);
@@ -561,8 +578,13 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
           const float2 xs = __ffma2_rn(ff(sv[2 * x], sv[2 * x + 1]), c2, nl);
           float2 p = make_float2(fast_exp2(xs.x), fast_exp2(xs.y));
           if constexpr (MASKED) {
-            if (!(col >= col_lo && col < col_hi)) p.x = 0.f;
-            if (!(col + 1 >= col_lo && col + 1 < col_hi)) p.y = 0.f;
+            if constexpr (MK == 1) {
+              if (!((live >> col) & 1u)) p.x = 0.f;
+              if (!((live >> (col + 1)) & 1u)) p.y = 0.f;
+            } else {
+              if (!(col >= col_lo && col < col_hi)) p.x = 0.f;
+              if (!(col + 1 >= col_lo && col + 1 < col_hi)) p.y = 0.f;
+            }
           }
           const float2 u = __fadd2_rn(ff(fp[2 * x], fp[2 * x + 1]), nsub);
           if constexpr (HAS_GT) {
@@ -580,7 +602,11 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
           }
           if constexpr (HAS_GO) pk_p[x] = Elem<T>::pack(p.x, p.y);
         };
-        if (__any_sync(0xffffffffu, col_lo > 0 || col_hi < 32)) {
+        if constexpr (MK == 1) {  // the index range (key padding of the own tile) joins the mask bits
+          const int lo = max(col_lo, 0), hi = min(col_hi, 32);
+          live &= hi > lo ? ((hi - lo >= 32 ? 0xffffffffu : ((1u << (hi - lo)) - 1u)) << lo) : 0u;
+        }
+        if (MK == 1 || __any_sync(0xffffffffu, col_lo > 0 || col_hi < 32)) {
 #pragma unroll
           for (int x = 0; x < 16; ++x) pair(x, IntC<1>{});
         } else {
@@ -727,7 +753,7 @@ static int fused_sm_count() {
   return cache[dev];
 }
 
-template <typename T, bool HAS_GO, bool HAS_GT>
+template <typename T, bool HAS_GO, bool HAS_GT, int MK>
 static int launch_fused64(const jvpfa_bwd_args& a, cudaStream_t stream) {
   using C = BwdFCfg<HAS_GO, HAS_GT>;
   int* status = tc5_status_device_ptr();
@@ -762,7 +788,7 @@ static int launch_fused64(const jvpfa_bwd_args& a, cudaStream_t stream) {
     set_last_cuda_error(e, "cudaMemsetAsync(dq_accum)");
     return JVPFA_ERR_CUDA;
   }
-  auto kern = bwd_tc5_fused64_kernel<T, HAS_GO, HAS_GT>;
+  auto kern = bwd_tc5_fused64_kernel<T, HAS_GO, HAS_GT, MK>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "cudaFuncSetAttribute(bwd_tc5_fused64)");
@@ -789,19 +815,27 @@ static int launch_fused64(const jvpfa_bwd_args& a, cudaStream_t stream) {
 template <typename T>
 static int launch_fused64_t(const jvpfa_bwd_args& a, cudaStream_t s) {
   const bool go = a.go != nullptr, gt = a.gto != nullptr;
-  if (go && gt) return launch_fused64<T, true, true>(a, s);
-  if (gt) return launch_fused64<T, false, true>(a, s);
-  return launch_fused64<T, true, false>(a, s);
+  if (a.mask.kind == JVPFA_MASK_BOOL) {
+    if (go && gt) return launch_fused64<T, true, true, 1>(a, s);
+    if (gt) return launch_fused64<T, false, true, 1>(a, s);
+    return launch_fused64<T, true, false, 1>(a, s);
+  }
+  if (go && gt) return launch_fused64<T, true, true, 0>(a, s);
+  if (gt) return launch_fused64<T, false, true, 0>(a, s);
+  return launch_fused64<T, true, false, 0>(a, s);
 }
 
 }  // namespace tc5
 
-// The single-pass kernel serves D = 64 with index masks (none, causal, key padding) when the caller provides the
-// fp32 accumulation buffer for dQ.
+// The single-pass kernel serves D = 64 with index masks (none, causal, key padding) and boolean masks that come without
+// tile bitmaps, when the caller provides the fp32 accumulation buffer for dQ.
 bool bwd_tc5_fused64_eligible(const jvpfa_bwd_args& a) {
   if (a.D != 64 || a.dq_accum == nullptr) return false;
   if ((reinterpret_cast<uintptr_t>(a.dq_accum) & 15u) != 0) return false;
   const int k = a.mask.kind;
+  // A boolean mask without tile bitmaps (dense, or not looked at beforehand): with them the two-launch kernels, which
+  // step over dead tiles, are the better choice.
+  if (k == JVPFA_MASK_BOOL) return a.mask_tile_live == nullptr && a.mask_tile_live_t == nullptr;
   return k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN;
 }
 

@@ -265,9 +265,11 @@ def _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec: _lib.MaskSpe
     delta, eps, cterm = stats[0], stats[1], stats[2]
     _lib.bwd_preprocess(o, to, go, gto, mu, delta, eps, cterm, spec.fp32_mode)
     dq, dk, dv = (torch.empty(q.shape, device=q.device, dtype=q.dtype) for _ in range(3))
-    # fp32 scratch for dQ: with it the library forms every score tile once (head dimension 64, 16-bit, index masks)
+    # fp32 scratch for dQ: with it the library forms every score tile once (head dimension 64, 16-bit, index masks or a
+    # boolean mask without dead tiles)
     acc = None
-    if SINGLE_PASS_BACKWARD and q.shape[-1] == 64 and q.dtype != torch.float32 and spec.kind in _lib.INDEX_MASKS:
+    dense_bool = spec.kind == _lib.MASK_BOOL and spec.tile_live is None and spec.tile_live_t is None  # no tiles to step over
+    if SINGLE_PASS_BACKWARD and q.shape[-1] == 64 and q.dtype != torch.float32 and (spec.kind in _lib.INDEX_MASKS or dense_bool):
         acc = torch.empty(q.shape, device=q.device, dtype=torch.float32)
     if st is not None:
         try:

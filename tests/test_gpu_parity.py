@@ -245,6 +245,9 @@ SINGLE_PASS_CASES = [c for c in PERSISTENT_CASES if c[1] in ("none", "causal", "
     # ragged lengths (last key tile and last query sub-tile partly out of range), one sub-tile, odd sub-tile counts
     ("gt", "causal", "bf16", 2, 3, 34), ("both", "none", "fp16", 3, 2, 200), ("go", "kvlen", "bf16", 2, 2, 328),
     ("gt", "none", "bf16", 1, 1, 64), ("both", "causal", "bf16", 5, 31, 448), ("gt", "kvlen", "fp16", 9, 17, 576),
+    # boolean masks without tile bitmaps (full, broadcast over the batch, one row of keys per batch entry)
+    ("gt", "bool", "bf16", 2, 3, 256), ("both", "bool_bcast", "fp16", 2, 4, 320), ("go", "bool_keys", "bf16", 3, 2, 192),
+    ("both", "bool", "bf16", 3, 20, 1024),
 ]
 
 
