@@ -107,3 +107,7 @@ def test_repeated_launches_with_a_boolean_mask():
     dq, dk, dv = (torch.empty_like(o) for _ in range(3))
     _soak(lambda: _lib.bwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], d["go"], d["gto"], lse, mu, stats[0],
                            stats[1], stats[2], dq, dk, dv, spec, D ** -0.5, _lib.IMPL_TCGEN05), [dq, dk, dv])
+    acc = torch.empty(B, H, L, D, device=DEV, dtype=torch.float32)  # ... and the single pass with the mask
+    _soak(lambda: _lib.bwd(d["q"], d["k"], d["v"], d["tq"], d["tk"], d["tv"], d["go"], d["gto"], lse, mu, stats[0],
+                           stats[1], stats[2], dq, dk, dv, spec, D ** -0.5, _lib.IMPL_TCGEN05, dq_accum=acc),
+          [dk, dv], close=[dq])
