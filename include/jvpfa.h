@@ -110,10 +110,10 @@ typedef struct {
   jvpfa_mask mask;
   /* Element strides of the batch, head and row dimensions of q, k, v, tq, tk, tv (all six alike; the
    * head dimension D is always contiguous).  {0,0,0} means (B,H,L,D) row-major.  Anything else, e.g. the
-   * (B,H,L,D) view of a (B,L,H,D) tensor, {L*H*D, D, H*D}, is read in place by the tcgen05 kernels
-   * (strides must be multiples of 8 elements); requests with strides that go to the register-tiled kernels
-   * return JVPFA_ERR_UNSUPPORTED and the caller passes contiguous copies instead (upstream always copies:
-   * jvp_attention.py:2733-2734, 2787-2788).  Outputs are always (B,H,L,D) row-major. */
+   * (B,H,L,D) view of a (B,L,H,D) tensor, {L*H*D, D, H*D}, is read in place by both kernel families (tensor
+   * maps with those strides, or tile loads with the row stride); strides must be positive multiples of 8
+   * elements.  Upstream always copies: jvp_attention.py:2733-2734, 2787-2788.  Outputs are always (B,H,L,D)
+   * row-major. */
   int64_t in_stride[3];
   /* Optional, JVPFA_MASK_BOOL only: the bitmap written by jvpfa_mask_tiles for this mask.  The tcgen05
    * kernel then steps over 128 x 64 tiles without a true entry; other kernels ignore it.  NULL = none. */

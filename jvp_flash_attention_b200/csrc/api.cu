@@ -142,7 +142,6 @@ int check_bwd_request(const jvpfa_bwd_args* a) {
   const bool tc5 = bwd_tc5_eligible(*a);
   const int fam = impl_family(a->impl);
   if (fam == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
-  if (has_strides(a->in_stride) && !(tc5 && fam != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
   return JVPFA_OK;
 }
 
@@ -172,8 +171,7 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc5 = fwd_tc5_eligible(*a);
   if (a->impl == JVPFA_IMPL_TCGEN05 && !tc5) return JVPFA_ERR_UNSUPPORTED;
-  // strided inputs are read in place by the tcgen05 kernels (their tensor maps carry the strides)
-  if (has_strides(a->in_stride) && !(tc5 && a->impl != JVPFA_IMPL_GENERIC)) return JVPFA_ERR_UNSUPPORTED;
+  // strided inputs are read in place by both kernel families (tensor maps or plain row strides)
   if (tc5 && a->impl != JVPFA_IMPL_GENERIC) {
     if (tc5_status_peek() != 0) return JVPFA_ERR_DEVICE_STATUS;
     return launch_fwd_tc5(*a, s);

@@ -269,12 +269,16 @@ __global__ void __launch_bounds__(128) bwd_dkdv_kernel(const jvpfa_bwd_args a) {
   const size_t head_off = (size_t)bh * L * D;
   const size_t stat_off = (size_t)bh * L;
 
-  const T* gQ = reinterpret_cast<const T*>(a.q) + head_off;
-  const T* gK = reinterpret_cast<const T*>(a.k) + head_off;
-  const T* gV = reinterpret_cast<const T*>(a.v) + head_off;
-  const T* gTQ = HAS_GT ? reinterpret_cast<const T*>(a.tq) + head_off : nullptr;
-  const T* gTK = HAS_GT ? reinterpret_cast<const T*>(a.tk) + head_off : nullptr;
-  const T* gTV = HAS_GT ? reinterpret_cast<const T*>(a.tv) + head_off : nullptr;
+  // the six inputs may share a strided (batch, head, row) layout (in_stride, elements; all zero = row-major)
+  const bool strided = (a.in_stride[0] | a.in_stride[1] | a.in_stride[2]) != 0;
+  const long long in_off = strided ? (long long)b * a.in_stride[0] + (long long)h * a.in_stride[1] : (long long)head_off;
+  const long long in_rs = strided ? a.in_stride[2] : D;
+  const T* gQ = reinterpret_cast<const T*>(a.q) + in_off;
+  const T* gK = reinterpret_cast<const T*>(a.k) + in_off;
+  const T* gV = reinterpret_cast<const T*>(a.v) + in_off;
+  const T* gTQ = HAS_GT ? reinterpret_cast<const T*>(a.tq) + in_off : nullptr;
+  const T* gTK = HAS_GT ? reinterpret_cast<const T*>(a.tk) + in_off : nullptr;
+  const T* gTV = HAS_GT ? reinterpret_cast<const T*>(a.tv) + in_off : nullptr;
   const T* gGO = HAS_GO ? reinterpret_cast<const T*>(a.go) + head_off : nullptr;
   const T* gG = HAS_GT ? reinterpret_cast<const T*>(a.gto) + head_off : nullptr;
 
@@ -289,10 +293,10 @@ __global__ void __launch_bounds__(128) bwd_dkdv_kernel(const jvpfa_bwd_args a) {
   auto stage_loop = [&](int stage, int m0) {
     T* base = sLoop + (size_t)stage * LOOP_TILES * BM * LD;
     int k = 0;
-    stage_tile<T, BM, D, NT>(base + (k++) * BM * LD, gQ, m0, L, tid);
+    stage_tile<T, BM, D, NT>(base + (k++) * BM * LD, gQ, m0, L, tid, in_rs);
     if constexpr (HAS_GO) stage_tile<T, BM, D, NT>(base + (k++) * BM * LD, gGO, m0, L, tid);
     if constexpr (HAS_GT) {
-      stage_tile<T, BM, D, NT>(base + (k++) * BM * LD, gTQ, m0, L, tid);
+      stage_tile<T, BM, D, NT>(base + (k++) * BM * LD, gTQ, m0, L, tid, in_rs);
       stage_tile<T, BM, D, NT>(base + (k++) * BM * LD, gG, m0, L, tid);
     }
     if (tid < BM) {
@@ -309,11 +313,11 @@ __global__ void __launch_bounds__(128) bwd_dkdv_kernel(const jvpfa_bwd_args a) {
     }
   };
 
-  stage_tile<T, BN, D, NT>(sK, gK, n0, L, tid);
-  stage_tile<T, BN, D, NT>(sV, gV, n0, L, tid);
+  stage_tile<T, BN, D, NT>(sK, gK, n0, L, tid, in_rs);
+  stage_tile<T, BN, D, NT>(sV, gV, n0, L, tid, in_rs);
   if constexpr (HAS_GT) {
-    stage_tile<T, BN, D, NT>(sTK, gTK, n0, L, tid);
-    stage_tile<T, BN, D, NT>(sTV, gTV, n0, L, tid);
+    stage_tile<T, BN, D, NT>(sTK, gTK, n0, L, tid, in_rs);
+    stage_tile<T, BN, D, NT>(sTV, gTV, n0, L, tid, in_rs);
   }
   if (STAGES == 2 && n_tiles > 0) stage_loop(0, m_begin);
   cp_async_commit();
@@ -463,12 +467,16 @@ __global__ void __launch_bounds__(128) bwd_dq_kernel(const jvpfa_bwd_args a) {
   const size_t head_off = (size_t)bh * L * D;
   const size_t stat_off = (size_t)bh * L;
 
-  const T* gQ = reinterpret_cast<const T*>(a.q) + head_off;
-  const T* gK = reinterpret_cast<const T*>(a.k) + head_off;
-  const T* gV = reinterpret_cast<const T*>(a.v) + head_off;
-  const T* gTQ = HAS_GT ? reinterpret_cast<const T*>(a.tq) + head_off : nullptr;
-  const T* gTK = HAS_GT ? reinterpret_cast<const T*>(a.tk) + head_off : nullptr;
-  const T* gTV = HAS_GT ? reinterpret_cast<const T*>(a.tv) + head_off : nullptr;
+  // the six inputs may share a strided (batch, head, row) layout (in_stride, elements; all zero = row-major)
+  const bool strided = (a.in_stride[0] | a.in_stride[1] | a.in_stride[2]) != 0;
+  const long long in_off = strided ? (long long)b * a.in_stride[0] + (long long)h * a.in_stride[1] : (long long)head_off;
+  const long long in_rs = strided ? a.in_stride[2] : D;
+  const T* gQ = reinterpret_cast<const T*>(a.q) + in_off;
+  const T* gK = reinterpret_cast<const T*>(a.k) + in_off;
+  const T* gV = reinterpret_cast<const T*>(a.v) + in_off;
+  const T* gTQ = HAS_GT ? reinterpret_cast<const T*>(a.tq) + in_off : nullptr;
+  const T* gTK = HAS_GT ? reinterpret_cast<const T*>(a.tk) + in_off : nullptr;
+  const T* gTV = HAS_GT ? reinterpret_cast<const T*>(a.tv) + in_off : nullptr;
   const T* gGO = HAS_GO ? reinterpret_cast<const T*>(a.go) + head_off : nullptr;
   const T* gG = HAS_GT ? reinterpret_cast<const T*>(a.gto) + head_off : nullptr;
 
@@ -481,18 +489,18 @@ __global__ void __launch_bounds__(128) bwd_dq_kernel(const jvpfa_bwd_args a) {
 
   auto stage_loop = [&](int stage, int n0) {
     T* base = sLoop + (size_t)stage * LOOP_TILES * BN * LD;
-    stage_tile<T, BN, D, NT>(base, gK, n0, L, tid);
-    stage_tile<T, BN, D, NT>(base + BN * LD, gV, n0, L, tid);
+    stage_tile<T, BN, D, NT>(base, gK, n0, L, tid, in_rs);
+    stage_tile<T, BN, D, NT>(base + BN * LD, gV, n0, L, tid, in_rs);
     if constexpr (HAS_GT) {
-      stage_tile<T, BN, D, NT>(base + 2 * BN * LD, gTK, n0, L, tid);
-      stage_tile<T, BN, D, NT>(base + 3 * BN * LD, gTV, n0, L, tid);
+      stage_tile<T, BN, D, NT>(base + 2 * BN * LD, gTK, n0, L, tid, in_rs);
+      stage_tile<T, BN, D, NT>(base + 3 * BN * LD, gTV, n0, L, tid, in_rs);
     }
   };
 
-  stage_tile<T, BM, D, NT>(sQ, gQ, m0, L, tid);
+  stage_tile<T, BM, D, NT>(sQ, gQ, m0, L, tid, in_rs);
   if constexpr (HAS_GO) stage_tile<T, BM, D, NT>(sGO, gGO, m0, L, tid);
   if constexpr (HAS_GT) {
-    stage_tile<T, BM, D, NT>(sTQ, gTQ, m0, L, tid);
+    stage_tile<T, BM, D, NT>(sTQ, gTQ, m0, L, tid, in_rs);
     stage_tile<T, BM, D, NT>(sG, gG, m0, L, tid);
   }
   if (STAGES == 2 && n_tiles > 0) stage_loop(0, 0);

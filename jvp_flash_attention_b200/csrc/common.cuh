@@ -238,7 +238,7 @@ __device__ __forceinline__ void a_from_acc(FragA<T, false>& f, const float (*acc
 }
 
 // ----------------------------------------------------------------------------------------------
-// cp.async staging of a [ROWS][D] tile (rows row0.. of a (L, D) row-major head) into padded smem.
+// cp.async staging of a [ROWS][D] tile (rows row0.. of one head) into padded smem.
 // Rows at or beyond L are zero-filled.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int src_bytes) {
@@ -251,8 +251,10 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
+// row_stride: elements between consecutive rows of the head in global memory (D for a row-major head; the row stride of
+// a strided (batch, head, row) layout otherwise; the row itself is contiguous).
 template <typename T, int ROWS, int D, int NTHREADS>
-__device__ __forceinline__ void stage_tile(T* s, const T* head, int row0, int L, int tid) {
+__device__ __forceinline__ void stage_tile(T* s, const T* head, int row0, int L, int tid, long long row_stride = D) {
   constexpr int LD = D + Elem<T>::kPad;
   constexpr int VEC = 16 / (int)sizeof(T);
   constexpr int VPR = D / VEC;
@@ -261,7 +263,7 @@ __device__ __forceinline__ void stage_tile(T* s, const T* head, int row0, int L,
     const int c = (idx - r * VPR) * VEC;
     const int gr = row0 + r;
     const bool ok = gr < L;
-    cp_async16(s + r * LD + c, head + (size_t)(ok ? gr : 0) * D + c, ok ? 16 : 0);
+    cp_async16(s + r * LD + c, head + (long long)(ok ? gr : 0) * row_stride + c, ok ? 16 : 0);
   }
 }
 

@@ -51,12 +51,16 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const jvpfa_fwd_args a
   const int m0 = mt * BM;
 
   const size_t head_off = (size_t)bh * L * D;
-  const T* gQ = reinterpret_cast<const T*>(a.q) + head_off;
-  const T* gK = reinterpret_cast<const T*>(a.k) + head_off;
-  const T* gV = reinterpret_cast<const T*>(a.v) + head_off;
-  const T* gTQ = DUAL ? reinterpret_cast<const T*>(a.tq) + head_off : nullptr;
-  const T* gTK = DUAL ? reinterpret_cast<const T*>(a.tk) + head_off : nullptr;
-  const T* gTV = DUAL ? reinterpret_cast<const T*>(a.tv) + head_off : nullptr;
+  // the six inputs may share a strided (batch, head, row) layout (in_stride, elements; all zero = row-major)
+  const bool strided = (a.in_stride[0] | a.in_stride[1] | a.in_stride[2]) != 0;
+  const long long in_off = strided ? (long long)b * a.in_stride[0] + (long long)h * a.in_stride[1] : (long long)head_off;
+  const long long in_rs = strided ? a.in_stride[2] : D;
+  const T* gQ = reinterpret_cast<const T*>(a.q) + in_off;
+  const T* gK = reinterpret_cast<const T*>(a.k) + in_off;
+  const T* gV = reinterpret_cast<const T*>(a.v) + in_off;
+  const T* gTQ = DUAL ? reinterpret_cast<const T*>(a.tq) + in_off : nullptr;
+  const T* gTK = DUAL ? reinterpret_cast<const T*>(a.tk) + in_off : nullptr;
+  const T* gTV = DUAL ? reinterpret_cast<const T*>(a.tv) + in_off : nullptr;
 
   const MaskView mv = make_mask_view(a.mask, b, h, L);
 
@@ -67,17 +71,17 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const jvpfa_fwd_args a
 
   auto stage_kv = [&](int stage, int n0) {
     T* base = sKV + (size_t)stage * NKV * BN * LD;
-    stage_tile<T, BN, D, NT>(base, gK, n0, L, tid);
-    stage_tile<T, BN, D, NT>(base + BN * LD, gV, n0, L, tid);
+    stage_tile<T, BN, D, NT>(base, gK, n0, L, tid, in_rs);
+    stage_tile<T, BN, D, NT>(base + BN * LD, gV, n0, L, tid, in_rs);
     if constexpr (DUAL) {
-      stage_tile<T, BN, D, NT>(base + 2 * BN * LD, gTK, n0, L, tid);
-      stage_tile<T, BN, D, NT>(base + 3 * BN * LD, gTV, n0, L, tid);
+      stage_tile<T, BN, D, NT>(base + 2 * BN * LD, gTK, n0, L, tid, in_rs);
+      stage_tile<T, BN, D, NT>(base + 3 * BN * LD, gTV, n0, L, tid, in_rs);
     }
   };
 
   // Prologue: Q (+tQ) and the first K/V tile in one cp.async group.
-  stage_tile<T, BM, D, NT>(sQ, gQ, m0, L, tid);
-  if constexpr (DUAL) stage_tile<T, BM, D, NT>(sTQ, gTQ, m0, L, tid);
+  stage_tile<T, BM, D, NT>(sQ, gQ, m0, L, tid, in_rs);
+  if constexpr (DUAL) stage_tile<T, BM, D, NT>(sTQ, gTQ, m0, L, tid, in_rs);
   if (n_tiles > 0) stage_kv(0, 0);
   cp_async_commit();
 

@@ -794,6 +794,45 @@ def test_strided_views_are_read_in_place(dt, kind, D):
     assert orc.rel_err(o32, ro) < 1e-5
 
 
+@pytest.mark.parametrize("dt,kind,D", [("fp32", "causal", 64), ("fp32", "bias", 128), ("bf16", "kvlen", 32), ("fp32", "none", 32)])
+def test_register_tiled_family_reads_strided_views_in_place(dt, kind, D):
+    """The same (B,H,L,D) views of (B,L,H,D) tensors through the register-tiled kernels (fp32, D = 32, anything forced
+    there): their tile loads take the row stride, so nothing is copied; results equal those from contiguous copies bit
+    for bit, forward and backward."""
+    dtype, dev = DT[dt], torch.device("cuda:0")
+    B, H, L = 2, 3, 200
+    g = torch.Generator().manual_seed(12)
+    base = [torch.randn(B, L, H, D, generator=g) for _ in range(8)]
+    for i in (3, 4, 5):
+        base[i] = base[i] * 0.1
+    q, k, v, tq, tk, tv, w1, w2 = [x.to(dtype).to(dev).transpose(1, 2) for x in base]
+    mask, causal = _mask(kind, B, H, L, dtype, seed=4)
+    spec, _, _ = ja.classify_mask(None if mask is None else mask.to(dev), causal, B, H, L, dtype, False)
+
+    def run_abi(ins, st):
+        o, to = torch.empty(B, H, L, D, device=dev, dtype=dtype), torch.empty(B, H, L, D, device=dev, dtype=dtype)
+        lse, mu = torch.empty(B, H, L, device=dev), torch.empty(B, H, L, device=dev)
+        _lib.fwd(*ins, o, to, lse, mu, spec, D**-0.5, _lib.IMPL_GENERIC, in_stride=st)
+        go, gto = w1.contiguous(), w2.contiguous()
+        stats = torch.empty(3, B, H, L, device=dev)
+        _lib.bwd_preprocess(o, to, go, gto, mu, stats[0], stats[1], stats[2])
+        dq, dk, dv = (torch.empty(B, H, L, D, device=dev, dtype=dtype) for _ in range(3))
+        _lib.bwd(*ins, go, gto, lse, mu, stats[0], stats[1], stats[2], dq, dk, dv, spec, D**-0.5, _lib.IMPL_GENERIC,
+                 in_stride=st)
+        torch.cuda.synchronize()
+        return o, to, lse, mu, dq, dk, dv
+
+    st = _lib.common_strides(q, k, v, tq, tk, tv)
+    assert st == (L * H * D, D, H * D)
+    strided = run_abi([q, k, v, tq, tk, tv], st)
+    dense = run_abi([x.contiguous() for x in (q, k, v, tq, tk, tv)], None)
+    for name, a_, b_ in zip(("o", "to", "lse", "mu", "dq", "dk", "dv"), strided, dense):
+        assert torch.equal(a_, b_), name
+    ro, rto = orc.sdpa_jvp(*(x.float().cpu() for x in (q, k, v, tq, tk, tv)), attn_mask=mask, causal=causal)
+    _close(strided[0], ro, dtype, "O")
+    _close(strided[1], rto, dtype, "tO")
+
+
 def test_mask_verification_is_one_device_pass():
     """`verify_attn_mask=True` (the default, as upstream: jvp_attention.py:2438-2457) raises what upstream raises,
     from the flags of one jvpfa_mask_check pass: a boolean head without a True, an inf, a NaN, a float head that
