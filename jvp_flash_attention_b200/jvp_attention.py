@@ -36,6 +36,9 @@ from . import _lib
 
 MASK_CONST = -100.0  # same constant as upstream (jvp_attention.py:48-50)
 MIN_SEQUENCE_LENGTH = 32  # jvp_attention.py:51
+# Upstream refuses sequence lengths that are odd or below 32 (its block sizes); the kernels here take any length >= 1.
+# The check is kept so that the same calls fail the same way; set this to False to lift it.
+STRICT_SEQUENCE_LENGTH = True
 
 _SUPPORTED_HEAD_DIMS = (32, 64, 128)
 _UPSTREAM_HEAD_DIMS = {16, 32, 64, 128, 256}
@@ -411,7 +414,7 @@ def _forward_impl(q, k, v, q_t, k_t, v_t, attn_mask, dropout_p, causal, sm_scale
         raise NotImplementedError(
             f"HEAD_DIM_K={HEAD_DIM_K} has no sm_100a kernel in this build (supported: {_SUPPORTED_HEAD_DIMS})"
         )
-    assert N_CTX % 2 == 0 and N_CTX >= MIN_SEQUENCE_LENGTH, (
+    assert not STRICT_SEQUENCE_LENGTH or (N_CTX % 2 == 0 and N_CTX >= MIN_SEQUENCE_LENGTH), (
         "JVP attention requires N_CTX to be a multiple of 2 and >= 32,"
         f" but got N_CTX={N_CTX}"
     )

@@ -833,6 +833,26 @@ def test_register_tiled_family_reads_strided_views_in_place(dt, kind, D):
     _close(strided[1], rto, dtype, "tO")
 
 
+@pytest.mark.parametrize("dt,D,L", [("bf16", 64, 33), ("fp16", 128, 7), ("fp32", 64, 31), ("bf16", 64, 1)])
+def test_any_sequence_length_through_the_api_when_the_upstream_check_is_lifted(dt, D, L, monkeypatch):
+    """Upstream's "multiple of 2 and >= 32" is a property of its block sizes, not of the kernels here: with
+    STRICT_SEQUENCE_LENGTH = False odd and short lengths go through the public API, forward with tangents and backward."""
+    dtype, dev = DT[dt], "cuda:0"
+    q, k, v, tq, tk, tv, w1, w2 = _make(2, 2, L, D, dtype, seed=L)
+    with pytest.raises(AssertionError, match="multiple of 2"):
+        ja.attention(q.to(dev), k.to(dev), v.to(dev), causal=True)
+    monkeypatch.setattr(ja, "STRICT_SEQUENCE_LENGTH", False)
+    a = [x.to(dev).requires_grad_() for x in (q, k, v)]
+    o, to = torch.func.jvp(lambda x, y, z: ja.JVPAttn.fwd_dual(x, y, z, causal=True), tuple(a),
+                           (tq.to(dev), tk.to(dev), tv.to(dev)))
+    g = torch.autograd.grad((o.float() * w1.to(dev).float()).sum() + (to.float() * w2.to(dev).float()).sum(), a)
+    ro, rto, rdq, rdk, rdv = orc.grads_through_both(q, k, v, tq, tk, tv, w1, w2, causal=True)
+    _close(o, ro, dtype, "O")
+    _close(to, rto, dtype, "tO")
+    for name, x, r in zip(("dq", "dk", "dv"), g, (rdq, rdk, rdv)):
+        _close(x, r, dtype, name)
+
+
 def test_mask_verification_is_one_device_pass():
     """`verify_attn_mask=True` (the default, as upstream: jvp_attention.py:2438-2457) raises what upstream raises,
     from the flags of one jvpfa_mask_check pass: a boolean head without a True, an inf, a NaN, a float head that
