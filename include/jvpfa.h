@@ -179,8 +179,8 @@ typedef struct {
   const void* mask_tile_live;
   const void* mask_tile_live_t;
   /* Optional caller-owned scratch: B*H*L*D floats, 16-byte aligned, contents irrelevant on entry.  With it (D = 64,
-   * 16-bit types, mask kinds NONE / CAUSAL / KVLEN, or BOOL without the two bitmaps above) the backward runs as ONE pass
-   * that forms every score tile once:
+   * 16-bit types, mask kinds NONE / CAUSAL / KVLEN, BOOL without the two bitmaps above, or - through O alone - BIAS of
+   * the tensors' type) the backward runs as ONE pass that forms every score tile once:
    * dK and dV accumulate on chip, dQ is summed into this buffer with floating-point reductions and converted at the
    * end, so dQ is reproducible to rounding but not bitwise from run to run.  NULL: the two-launch kernels, which
    * recompute the score tiles for dQ (as upstream does, jvp_attention.py:1415-1707) and are bitwise reproducible. */

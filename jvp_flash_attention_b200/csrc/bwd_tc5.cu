@@ -1,7 +1,7 @@
 // Backward of <gO, O> + <gtO, tO> for bf16 / fp16 on tcgen05 tensor cores: which requests the tcgen05 kernels take,
 // and which of them.
 //   head dimension 64 : bwd_tc5_fused64.cu (one pass; needs the dQ accumulation buffer; index masks, boolean masks
-//                       without tile bitmaps) or bwd_tc5_d64.cu (two launches; every mask kind, steps over dead tiles)
+//                       without tile bitmaps, bias through O alone) or bwd_tc5_d64.cu (two launches; every mask kind, steps over dead tiles)
 //   head dimension 128: bwd_tc5_pipe128.cu (two launches; every mask kind)
 #include "tc5_common.cuh"
 

@@ -114,7 +114,8 @@ struct FItem {
 };
 
 // MK: 0 = none / causal / key padding (index comparisons); 1 = uint8 mask with any strides (each elementwise thread
-// reads the 32 mask bytes of its key row and the sub-tile's queries before it waits for the scores).
+// reads the 32 mask bytes of its key row and the sub-tile's queries before it waits for the scores); 2 = additive bias of
+// the element type, read the same way (HAS_GT == false only).
 template <typename T, bool HAS_GO, bool HAS_GT, int MK>
 __global__ void __launch_bounds__(512, 1)
 bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps maps, float* dq_acc, int* status) {
@@ -531,12 +532,19 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
         const int l0 = it.loop_begin + s * BL + 32 * wg;  // first query of this group's columns
         // MK = 1: this key's mask bytes for the 32 queries, requested before the waits (indices clamped into the
         // tensor; what lies outside is switched off by col_hi and by lse = +inf of the padding queries)
-        uint32_t mraw[MK == 1 ? 32 : 1];
-        if constexpr (MK == 1) {
-          const unsigned char* pm = reinterpret_cast<const unsigned char*>(a.mask.ptr) + (long long)it.b * a.mask.stride[0] +
-                                    (long long)it.h * a.mask.stride[1] + (long long)min(own_idx, L - 1) * a.mask.stride[3];
+        // MK = 2 (backward through O alone: the variants with tangents have no registers to spare): the bias elements
+        // of the same positions, 16 bit each, of the tensors' type.
+        uint32_t mraw[MK != 0 ? 32 : 1];
+        if constexpr (MK != 0) {
+          constexpr int MESZ = MK == 1 ? 1 : 2;
+          const unsigned char* pm = reinterpret_cast<const unsigned char*>(a.mask.ptr) +
+                                    ((long long)it.b * a.mask.stride[0] + (long long)it.h * a.mask.stride[1] +
+                                     (long long)min(own_idx, L - 1) * a.mask.stride[3]) * MESZ;
 #pragma unroll
-          for (int col = 0; col < 32; ++col) mraw[col] = ldg_nc_u8(pm + (long long)min(l0 + col, L - 1) * a.mask.stride[2]);
+          for (int col = 0; col < 32; ++col) {
+            const unsigned char* el = pm + (long long)min(l0 + col, L - 1) * a.mask.stride[2] * MESZ;
+            mraw[col] = MK == 1 ? ldg_nc_u8(el) : ldg_nc_u16(el);
+          }
         }
         if (!mbar_wait(stat_full + st, (g / STAGES) & 1, ab, kAbortBwdLoopFull) ||
             !mbar_wait(s_full, g & 1, ab, kAbortBwdSFull)) {
@@ -575,7 +583,9 @@ bwd_tc5_fused64_kernel(const jvpfa_bwd_args a, const __grid_constant__ BwdFMaps 
           const float4 sa = stat[2 * x], sb = stat[2 * x + 1];
           const float2 nl = make_float2(sa.x, sa.y), nmu = make_float2(sa.z, sa.w);
           const float2 neps = make_float2(sb.x, sb.y), nsub = make_float2(sb.z, sb.w);
-          const float2 xs = __ffma2_rn(ff(sv[2 * x], sv[2 * x + 1]), c2, nl);
+          float2 xs = __ffma2_rn(ff(sv[2 * x], sv[2 * x + 1]), c2, nl);
+          if constexpr (MK == 2)  // scores are in log2 units: + bias * log2(e)
+            xs = __ffma2_rn(unpack2<T>(mraw[2 * x] | (mraw[2 * x + 1] << 16)), make_float2(kLog2e, kLog2e), xs);
           float2 p = make_float2(fast_exp2(xs.x), fast_exp2(xs.y));
           if constexpr (MASKED) {
             if constexpr (MK == 1) {
@@ -815,6 +825,7 @@ static int launch_fused64(const jvpfa_bwd_args& a, cudaStream_t stream) {
 template <typename T>
 static int launch_fused64_t(const jvpfa_bwd_args& a, cudaStream_t s) {
   const bool go = a.go != nullptr, gt = a.gto != nullptr;
+  if (a.mask.kind == JVPFA_MASK_BIAS) return launch_fused64<T, true, false, 2>(a, s);  // eligible only through O alone
   if (a.mask.kind == JVPFA_MASK_BOOL) {
     if (go && gt) return launch_fused64<T, true, true, 1>(a, s);
     if (gt) return launch_fused64<T, false, true, 1>(a, s);
@@ -836,6 +847,8 @@ bool bwd_tc5_fused64_eligible(const jvpfa_bwd_args& a) {
   // A boolean mask without tile bitmaps (dense, or not looked at beforehand): with them the two-launch kernels, which
   // step over dead tiles, are the better choice.
   if (k == JVPFA_MASK_BOOL) return a.mask_tile_live == nullptr && a.mask_tile_live_t == nullptr;
+  // An additive bias of the tensors' type: only the backward through O alone has the registers for it.
+  if (k == JVPFA_MASK_BIAS) return a.gto == nullptr && a.mask.bias_dtype == a.dtype;
   return k == JVPFA_MASK_NONE || k == JVPFA_MASK_CAUSAL || k == JVPFA_MASK_KVLEN;
 }
 

@@ -272,7 +272,9 @@ def _launch_bwd(q, k, v, tq, tk, tv, o, to, lse, mu, go, gto, spec: _lib.MaskSpe
     # boolean mask without dead tiles)
     acc = None
     dense_bool = spec.kind == _lib.MASK_BOOL and spec.tile_live is None and spec.tile_live_t is None  # no tiles to step over
-    if SINGLE_PASS_BACKWARD and q.shape[-1] == 64 and q.dtype != torch.float32 and (spec.kind in _lib.INDEX_MASKS or dense_bool):
+    bias_o = spec.kind == _lib.MASK_BIAS and gto is None and spec.bias_dtype == _lib.DTYPE_ENUM.get(q.dtype)  # through O alone
+    if SINGLE_PASS_BACKWARD and q.shape[-1] == 64 and q.dtype != torch.float32 and (
+            spec.kind in _lib.INDEX_MASKS or dense_bool or bias_o):
         acc = torch.empty(q.shape, device=q.device, dtype=torch.float32)
     if st is not None:
         try:

@@ -248,6 +248,8 @@ SINGLE_PASS_CASES = [c for c in PERSISTENT_CASES if c[1] in ("none", "causal", "
     # boolean masks without tile bitmaps (full, broadcast over the batch, one row of keys per batch entry)
     ("gt", "bool", "bf16", 2, 3, 256), ("both", "bool_bcast", "fp16", 2, 4, 320), ("go", "bool_keys", "bf16", 3, 2, 192),
     ("both", "bool", "bf16", 3, 20, 1024),
+    # additive bias of the tensors' type, backward through O alone
+    ("go", "bias", "bf16", 2, 3, 256), ("go", "bias", "fp16", 3, 5, 448),
 ]
 
 
