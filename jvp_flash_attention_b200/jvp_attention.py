@@ -157,7 +157,11 @@ def classify_mask(attn_mask: Tensor | None, causal: bool, Z: int, H: int, N: int
     if len(_MASK_MEMO) >= _MASK_MEMO_MAX:
         _MASK_MEMO.clear()
     try:
-        _MASK_MEMO[id(attn_mask)] = (weakref.ref(attn_mask), key, (copy.copy(spec), mask_type))
+        # the entry goes when the caller's tensor object does (the description holds a view of the mask's storage and
+        # must not keep it alive)
+        k_id = id(attn_mask)
+        _MASK_MEMO[k_id] = (weakref.ref(attn_mask, lambda _r, k_id=k_id: _MASK_MEMO.pop(k_id, None)), key,
+                            (copy.copy(spec), mask_type))
     except TypeError:  # an object that cannot be weakly referenced: no memo
         pass
     return spec, mask_type, attn_mask

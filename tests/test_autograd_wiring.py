@@ -87,6 +87,15 @@ def test_mask_verification_is_remembered_per_tensor_object_and_version(cpu_kerne
     for _ in range(2):
         with pytest.raises(AssertionError, match="all False"):
             ja.attention(q, k, v, attn_mask=bad)
+    # the memo does not outlive the caller's tensor object
+    tmp = mask.clone()
+    ja.attention(q, k, v, attn_mask=tmp)
+    assert id(tmp) in ja._MASK_MEMO
+    key_id = id(tmp)
+    del tmp
+    import gc
+    gc.collect()
+    assert key_id not in ja._MASK_MEMO
     monkeypatch.setattr(ja, "MASK_MEMO_ENABLED", False)
     n = len(calls)
     ja.attention(q, k, v, attn_mask=mask)
